@@ -1,0 +1,81 @@
+"""ctypes binding of libaiehlc_b200.so -- the C ABI declared in include/aiehlc_b200.h.
+
+Loading fails loudly: if the shared library is missing it is built with nvcc, and if that is
+impossible an ImportError is raised.  There is no Python or CPU implementation behind these
+calls.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+from . import build as _build
+
+OK = 0
+ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE, ERR_NOMEM = -1, -2, -3, -4, -5
+
+_i32p = C.POINTER(C.c_int32)
+_vp = C.c_void_p
+
+# name -> (restype, argtypes); every symbol include/aiehlc_b200.h declares
+SIGNATURES = {
+    "aiehlc_create": (C.c_int, [C.c_int, C.POINTER(_vp)]),
+    "aiehlc_destroy": (C.c_int, [_vp]),
+    "aiehlc_last_error": (C.c_char_p, []),
+    "aiehlc_sm_count": (C.c_int, [_vp]),
+    "aiehlc_sync": (C.c_int, [_vp, _vp, _i32p]),
+    "aiehlc_mm_i32_dev": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
+    "aiehlc_mm_i32_host": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int]),
+    "aiehlc_gemm_i8_i32_dev": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
+    "aiehlc_gemm_i8_i32_host": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int]),
+    "aiehlc_gemm_i8_srs_dev": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp,
+                                         C.c_int, _vp]),
+    "aiehlc_gemm_i8_srs_host": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.c_int]),
+    "aiehlc_srs_i32_i8_dev": (C.c_int, [_vp, _vp, _vp, C.c_longlong, C.c_longlong, C.c_int, _vp, _vp]),
+    "aiehlc_gemm_bf16_dev": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
+    "aiehlc_gemm_bf16_host": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int]),
+    "aiehlc_conv2d_i8_srs_dev": (C.c_int, [_vp, _vp, _vp, _vp] + [C.c_int] * 8 + [_vp, _vp]),
+    "aiehlc_conv2d_i8_srs_host": (C.c_int, [_vp, _vp, _vp, _vp] + [C.c_int] * 8 + [_vp]),
+    "aiehlc_set_tile_n": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_launch_count": (C.c_longlong, [_vp]),
+}
+
+_lib = None
+
+
+def library_path() -> Path:
+    return _build.LIB_PATH
+
+
+def load() -> C.CDLL:
+    """Returns the loaded library, building it first if needed."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if not path.exists():
+        try:
+            _build.build()
+        except Exception as exc:  # noqa: BLE001
+            raise ImportError(
+                f"aiehlc_b200: {path} is missing and could not be built ({exc}); "
+                "the CUDA extension is required, there is no fallback") from exc
+    lib = C.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+class AiehlcError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"aiehlc error {code}: {message}")
+        self.code = code
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        msg = load().aiehlc_last_error()
+        raise AiehlcError(rc, msg.decode() if msg else "")

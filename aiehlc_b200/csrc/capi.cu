@@ -1,0 +1,360 @@
+// extern "C" entry points declared in include/aiehlc_b200.h.
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "context.h"
+#include "gemm_tcgen05.cuh"
+
+namespace aiehlc {
+
+static thread_local std::string g_last_error;
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+int fail(int rc, const std::string& msg) {
+  g_last_error = msg;
+  return rc;
+}
+int cuda_fail(cudaError_t e, const char* what) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return AIEHLC_ERR_CUDA;
+}
+
+int DevBuf::reserve(size_t need) {
+  if (need <= bytes) return 0;
+  if (ptr) cudaFree(ptr);
+  ptr = nullptr;
+  bytes = 0;
+  const size_t want = (need + (1u << 20) - 1) & ~static_cast<size_t>((1u << 20) - 1);
+  cudaError_t e = cudaMalloc(&ptr, want);
+  if (e != cudaSuccess) {
+    cuda_fail(e, "cudaMalloc(workspace)");
+    ptr = nullptr;
+    return AIEHLC_ERR_NOMEM;
+  }
+  bytes = want;
+  return 0;
+}
+void DevBuf::release() {
+  if (ptr) cudaFree(ptr);
+  ptr = nullptr;
+  bytes = 0;
+}
+
+static int check_ctx(aiehlc_ctx* ctx) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  return AIEHLC_OK;
+}
+
+static int check_shift(int shift, const uint8_t* /*shift_vec*/) {
+  if (shift < 0 || shift > 31) return fail(AIEHLC_ERR_INVALID, "srs shift must be in [0, 31]");
+  return AIEHLC_OK;
+}
+
+}  // namespace aiehlc
+
+using namespace aiehlc;
+
+extern "C" {
+
+const char* aiehlc_last_error(void) { return g_last_error.c_str(); }
+
+int aiehlc_create(int device, aiehlc_ctx** out) {
+  if (!out) return fail(AIEHLC_ERR_INVALID, "aiehlc_create: null out pointer");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return fail(AIEHLC_ERR_CUDA, std::string("aiehlc_create: no CUDA device (") +
+                                     (e != cudaSuccess ? cudaGetErrorString(e) : "count = 0") +
+                                     "); this library has no CPU path");
+  if (device < 0 || device >= count) return fail(AIEHLC_ERR_INVALID, "aiehlc_create: device out of range");
+  AIEHLC_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  AIEHLC_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(AIEHLC_ERR_UNSUPPORTED, "aiehlc_create: kernels are built for sm_100a only (found sm_" +
+                                            std::to_string(prop.major) + std::to_string(prop.minor) + ")");
+  aiehlc_ctx* ctx = new aiehlc_ctx();
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+    delete ctx;
+    return fail(AIEHLC_ERR_CUDA, "aiehlc_create: cuTensorMapEncodeTiled not available from the driver");
+  }
+  ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(&ctx->d_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost(&ctx->h_status, sizeof(int));
+  if (e != cudaSuccess) {
+    cuda_fail(e, "aiehlc_create");
+    aiehlc_destroy(ctx);
+    return AIEHLC_ERR_CUDA;
+  }
+  *ctx->h_status = 0;
+  *out = ctx;
+  return AIEHLC_OK;
+}
+
+int aiehlc_destroy(aiehlc_ctx* ctx) {
+  if (!ctx) return AIEHLC_OK;
+  cudaSetDevice(ctx->device);
+  if (ctx->stream) {
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamDestroy(ctx->stream);
+  }
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  ctx->buf_a.release(); ctx->buf_b.release(); ctx->buf_c.release(); ctx->buf_aux.release();
+  ctx->pack_a.release(); ctx->pack_b.release();
+  delete ctx;
+  return AIEHLC_OK;
+}
+
+int aiehlc_sm_count(const aiehlc_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+long long aiehlc_launch_count(const aiehlc_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256)
+    return fail(AIEHLC_ERR_INVALID, "tile_n must be 0, 64, 128 or 256");
+  ctx->force_tile_n = tile_n;
+  return AIEHLC_OK;
+}
+
+int aiehlc_sync(aiehlc_ctx* ctx, void* stream, int* status) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  cudaStream_t st = pick_stream(ctx, stream);
+  AIEHLC_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, st));
+  AIEHLC_CUDA(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), st));
+  AIEHLC_CUDA(cudaStreamSynchronize(st));
+  const int s = *ctx->h_status;
+  if (status) *status = s;
+  if (s != 0) return fail(AIEHLC_ERR_DEVICE, "kernel status word = " + std::to_string(s) + " (a bounded wait ran out)");
+  return AIEHLC_OK;
+}
+
+// ------------------------------------------------------------------ device-pointer entry points
+int aiehlc_mm_i32_dev(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K, void* stream) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "mm_i32: negative size");
+  if (M == 0 || N == 0) return AIEHLC_OK;
+  if (!in || !out) return fail(AIEHLC_ERR_INVALID, "mm_i32: null pointer");
+  return launch_mm_i32(ctx, in, out, M, N, K, pick_stream(ctx, stream));
+}
+
+int aiehlc_gemm_i8_i32_dev(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int32_t* C, int M, int N, int K,
+                           int accumulate, void* stream) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32: negative size");
+  if (M == 0 || N == 0) return AIEHLC_OK;
+  if (!C) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32: null C");
+  cudaStream_t st = pick_stream(ctx, stream);
+  if (K == 0) {
+    if (accumulate) return AIEHLC_OK;
+    return launch_fill_i32(ctx, C, static_cast<long long>(M) * N, 0, st);
+  }
+  if (!A || !B) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32: null operand");
+  GemmCall c{};
+  c.kind = KIND_I8; c.epi = accumulate ? EPI_I32_ACC : EPI_I32;
+  c.A = A; c.B = B; c.C = C; c.M = M; c.N = N; c.K = K; c.lda = K; c.ldb = K; c.ldc = N;
+  return launch_gemm(ctx, c, st);
+}
+
+int aiehlc_srs_i32_i8_dev(aiehlc_ctx* ctx, const int32_t* in, int8_t* out, long long rows, long long cols,
+                          int shift, const uint8_t* shift_vec, void* stream) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (rows < 0 || cols < 0) return fail(AIEHLC_ERR_INVALID, "srs: negative size");
+  if ((rc = check_shift(shift, shift_vec))) return rc;
+  if (rows == 0 || cols == 0) return AIEHLC_OK;
+  if (!in || !out) return fail(AIEHLC_ERR_INVALID, "srs: null pointer");
+  return launch_srs(ctx, in, out, rows, cols, shift, shift_vec, pick_stream(ctx, stream));
+}
+
+int aiehlc_gemm_i8_srs_dev(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                           int shift, const uint8_t* shift_vec, const int32_t* acc_in, int splitk,
+                           void* stream) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: negative size");
+  if ((rc = check_shift(shift, shift_vec))) return rc;
+  if (splitk < 1 || (K > 0 && K % splitk != 0))
+    return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: splitk must be >= 1 and divide K");
+  if (M == 0 || N == 0) return AIEHLC_OK;
+  if (!C) return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: null C");
+  cudaStream_t st = pick_stream(ctx, stream);
+  if (K == 0) {
+    // empty contraction: the result is srs(acc_in) or srs(0) = 0
+    if (acc_in) return launch_srs(ctx, acc_in, C, M, N, shift, shift_vec, st);
+    AIEHLC_CUDA(cudaMemsetAsync(C, 0, static_cast<size_t>(M) * N, st));
+    return AIEHLC_OK;
+  }
+  if (!A || !B) return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: null operand");
+  // The K loop of one launch visits the splitk slices in order and keeps the running sum in
+  // TMEM, so the slice count does not change the schedule: it only has to divide K.
+  GemmCall c{};
+  c.kind = KIND_I8; c.epi = EPI_I8_SRS;
+  c.A = A; c.B = B; c.C = C; c.M = M; c.N = N; c.K = K; c.lda = K; c.ldb = K; c.ldc = N;
+  c.acc_in = acc_in; c.ld_acc = N; c.shift_vec = shift_vec; c.shift = shift;
+  return launch_gemm(ctx, c, st);
+}
+
+int aiehlc_gemm_bf16_dev(aiehlc_ctx* ctx, const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N,
+                         int K, void* stream) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_bf16: negative size");
+  if (M == 0 || N == 0) return AIEHLC_OK;
+  if (!C) return fail(AIEHLC_ERR_INVALID, "gemm_bf16: null C");
+  cudaStream_t st = pick_stream(ctx, stream);
+  if (K == 0) {
+    AIEHLC_CUDA(cudaMemsetAsync(C, 0, static_cast<size_t>(M) * N * 2, st));
+    return AIEHLC_OK;
+  }
+  if (!A || !B) return fail(AIEHLC_ERR_INVALID, "gemm_bf16: null operand");
+  GemmCall c{};
+  c.kind = KIND_BF16; c.epi = EPI_BF16;
+  c.A = A; c.B = B; c.C = C; c.M = M; c.N = N; c.K = K; c.lda = K; c.ldb = K; c.ldc = N;
+  return launch_gemm(ctx, c, st);
+}
+
+int aiehlc_conv2d_i8_srs_dev(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
+                             int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec,
+                             void* stream) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (n < 0 || h < 0 || wd < 0 || cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0 || pad < 0)
+    return fail(AIEHLC_ERR_INVALID, "conv2d: bad size");
+  if (kh != 2 * pad + 1 || kw != 2 * pad + 1)
+    return fail(AIEHLC_ERR_UNSUPPORTED, "conv2d: only stride 1 with kh = kw = 2*pad+1 (same-size output)");
+  if (n == 0 || h == 0 || wd == 0) return AIEHLC_OK;
+  if (!x || !w || !y || !shift_vec) return fail(AIEHLC_ERR_INVALID, "conv2d: null pointer");
+  return launch_conv2d(ctx, x, w, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec, pick_stream(ctx, stream));
+}
+
+// ------------------------------------------------------------------ host-pointer entry points
+// H2D copy of the operands, the same kernels, D2H copy of the result, one synchronisation.
+static int finish_host(aiehlc_ctx* ctx) {
+  int status = 0;
+  return aiehlc_sync(ctx, ctx->stream, &status);
+}
+
+int aiehlc_mm_i32_host(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "mm_i32: negative size");
+  if (M == 0 || N == 0) return AIEHLC_OK;
+  if (!in || !out) return fail(AIEHLC_ERR_INVALID, "mm_i32: null pointer");
+  const size_t in_bytes = (static_cast<size_t>(M) + N) * K * 4, out_bytes = static_cast<size_t>(M) * N * 4;
+  if (ctx->buf_a.reserve(in_bytes ? in_bytes : 4) || ctx->buf_c.reserve(out_bytes)) return AIEHLC_ERR_NOMEM;
+  AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_a.ptr, in, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  rc = aiehlc_mm_i32_dev(ctx, static_cast<const int32_t*>(ctx->buf_a.ptr), static_cast<int32_t*>(ctx->buf_c.ptr),
+                         M, N, K, ctx->stream);
+  if (rc) return rc;
+  AIEHLC_CUDA(cudaMemcpyAsync(out, ctx->buf_c.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return finish_host(ctx);
+}
+
+static int stage_ab(aiehlc_ctx* ctx, const void* A, const void* B, size_t a_bytes, size_t b_bytes,
+                    size_t c_bytes) {
+  if (ctx->buf_a.reserve(a_bytes ? a_bytes : 16) || ctx->buf_b.reserve(b_bytes ? b_bytes : 16) ||
+      ctx->buf_c.reserve(c_bytes ? c_bytes : 16))
+    return AIEHLC_ERR_NOMEM;
+  if (a_bytes) AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_a.ptr, A, a_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  if (b_bytes) AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_b.ptr, B, b_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return AIEHLC_OK;
+}
+
+int aiehlc_gemm_i8_i32_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int32_t* C, int M, int N, int K) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32: negative size");
+  if (M == 0 || N == 0) return AIEHLC_OK;
+  if (!C || (K > 0 && (!A || !B))) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32: null pointer");
+  const size_t cb = static_cast<size_t>(M) * N * 4;
+  if ((rc = stage_ab(ctx, A, B, static_cast<size_t>(M) * K, static_cast<size_t>(N) * K, cb))) return rc;
+  rc = aiehlc_gemm_i8_i32_dev(ctx, static_cast<const int8_t*>(ctx->buf_a.ptr),
+                              static_cast<const int8_t*>(ctx->buf_b.ptr), static_cast<int32_t*>(ctx->buf_c.ptr),
+                              M, N, K, 0, ctx->stream);
+  if (rc) return rc;
+  AIEHLC_CUDA(cudaMemcpyAsync(C, ctx->buf_c.ptr, cb, cudaMemcpyDeviceToHost, ctx->stream));
+  return finish_host(ctx);
+}
+
+int aiehlc_gemm_i8_srs_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                            int shift, const uint8_t* shift_vec, int splitk) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: negative size");
+  if (M == 0 || N == 0) return AIEHLC_OK;
+  if (!C || (K > 0 && (!A || !B))) return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: null pointer");
+  const size_t cb = static_cast<size_t>(M) * N;
+  if ((rc = stage_ab(ctx, A, B, static_cast<size_t>(M) * K, static_cast<size_t>(N) * K, cb))) return rc;
+  const uint8_t* dsv = nullptr;
+  if (shift_vec) {
+    if (ctx->buf_aux.reserve(N)) return AIEHLC_ERR_NOMEM;
+    AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_aux.ptr, shift_vec, N, cudaMemcpyHostToDevice, ctx->stream));
+    dsv = static_cast<const uint8_t*>(ctx->buf_aux.ptr);
+    for (int j = 0; j < N; ++j)
+      if (shift_vec[j] > 31) return fail(AIEHLC_ERR_INVALID, "srs shift must be in [0, 31]");
+  }
+  rc = aiehlc_gemm_i8_srs_dev(ctx, static_cast<const int8_t*>(ctx->buf_a.ptr),
+                              static_cast<const int8_t*>(ctx->buf_b.ptr), static_cast<int8_t*>(ctx->buf_c.ptr),
+                              M, N, K, shift, dsv, nullptr, splitk, ctx->stream);
+  if (rc) return rc;
+  AIEHLC_CUDA(cudaMemcpyAsync(C, ctx->buf_c.ptr, cb, cudaMemcpyDeviceToHost, ctx->stream));
+  return finish_host(ctx);
+}
+
+int aiehlc_gemm_bf16_host(aiehlc_ctx* ctx, const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N,
+                          int K) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_bf16: negative size");
+  if (M == 0 || N == 0) return AIEHLC_OK;
+  if (!C || (K > 0 && (!A || !B))) return fail(AIEHLC_ERR_INVALID, "gemm_bf16: null pointer");
+  const size_t cb = static_cast<size_t>(M) * N * 2;
+  if ((rc = stage_ab(ctx, A, B, static_cast<size_t>(M) * K * 2, static_cast<size_t>(N) * K * 2, cb))) return rc;
+  rc = aiehlc_gemm_bf16_dev(ctx, static_cast<const uint16_t*>(ctx->buf_a.ptr),
+                            static_cast<const uint16_t*>(ctx->buf_b.ptr), static_cast<uint16_t*>(ctx->buf_c.ptr),
+                            M, N, K, ctx->stream);
+  if (rc) return rc;
+  AIEHLC_CUDA(cudaMemcpyAsync(C, ctx->buf_c.ptr, cb, cudaMemcpyDeviceToHost, ctx->stream));
+  return finish_host(ctx);
+}
+
+int aiehlc_conv2d_i8_srs_host(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
+                              int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (n < 0 || h < 0 || wd < 0 || cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0 || pad < 0)
+    return fail(AIEHLC_ERR_INVALID, "conv2d: bad size");
+  if (n == 0 || h == 0 || wd == 0) return AIEHLC_OK;
+  if (!x || !w || !y || !shift_vec) return fail(AIEHLC_ERR_INVALID, "conv2d: null pointer");
+  for (int j = 0; j < cout; ++j)
+    if (shift_vec[j] > 31) return fail(AIEHLC_ERR_INVALID, "srs shift must be in [0, 31]");
+  const size_t xb = static_cast<size_t>(n) * h * wd * cin, wb = static_cast<size_t>(kh) * kw * cin * cout,
+               yb = static_cast<size_t>(n) * h * wd * cout;
+  if ((rc = stage_ab(ctx, x, w, xb, wb, yb))) return rc;
+  if (ctx->buf_aux.reserve(cout)) return AIEHLC_ERR_NOMEM;
+  AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_aux.ptr, shift_vec, cout, cudaMemcpyHostToDevice, ctx->stream));
+  rc = aiehlc_conv2d_i8_srs_dev(ctx, static_cast<const int8_t*>(ctx->buf_a.ptr),
+                                static_cast<const int8_t*>(ctx->buf_b.ptr), static_cast<int8_t*>(ctx->buf_c.ptr),
+                                n, h, wd, cin, cout, kh, kw, pad, static_cast<const uint8_t*>(ctx->buf_aux.ptr),
+                                ctx->stream);
+  if (rc) return rc;
+  AIEHLC_CUDA(cudaMemcpyAsync(y, ctx->buf_c.ptr, yb, cudaMemcpyDeviceToHost, ctx->stream));
+  return finish_host(ctx);
+}
+
+}  // extern "C"

@@ -1,0 +1,83 @@
+// Per-device context behind the C ABI: stream, status word, grow-only device workspaces.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "../../include/aiehlc_b200.h"
+
+namespace aiehlc {
+
+void set_error(const std::string& msg);
+int fail(int rc, const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define AIEHLC_CUDA(call)                                         \
+  do {                                                            \
+    cudaError_t e__ = (call);                                     \
+    if (e__ != cudaSuccess) return ::aiehlc::cuda_fail(e__, #call); \
+  } while (0)
+
+// A device buffer that only ever grows (cudaMalloc on demand, freed with the context).
+struct DevBuf {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  int reserve(size_t need);
+  void release();
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace aiehlc
+
+struct aiehlc_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  int* d_status = nullptr;      // device status word
+  int* h_status = nullptr;      // pinned mirror
+  aiehlc::EncodeTiledFn encode = nullptr;
+  int force_tile_n = 0;
+  long long launches = 0;
+  // staging for *_host entry points and for operands that TMA cannot address directly
+  aiehlc::DevBuf buf_a, buf_b, buf_c, buf_aux, pack_a, pack_b;
+};
+
+namespace aiehlc {
+
+// `_dev` entry points run on exactly the stream they are given (NULL is CUDA's default stream).
+inline cudaStream_t pick_stream(aiehlc_ctx* /*ctx*/, void* stream) {
+  return static_cast<cudaStream_t>(stream);
+}
+
+// tcgen05 tile GEMM launcher (gemm_launch.cu).  kind: KIND_I8 / KIND_BF16; epi: EPI_*.
+struct GemmCall {
+  int kind, epi;
+  const void* A; const void* B; void* C;
+  int M, N, K;
+  long long lda, ldb, ldc;      // elements
+  const int32_t* acc_in; long long ld_acc;
+  const uint8_t* shift_vec; int shift;
+};
+int launch_gemm(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st);
+
+// SIMT helpers (simt_kernels.cu)
+int launch_mm_i32(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K, cudaStream_t st);
+int launch_srs(aiehlc_ctx* ctx, const int32_t* in, int8_t* out, long long rows, long long cols, int shift,
+               const uint8_t* shift_vec, cudaStream_t st);
+int launch_fill_i32(aiehlc_ctx* ctx, int32_t* out, long long n, int value, cudaStream_t st);
+// Copy a rows x cols matrix of `esize`-byte elements from leading dimension ld_src to ld_dst.
+int launch_repack(aiehlc_ctx* ctx, const void* src, void* dst, long long rows, long long cols,
+                  long long ld_src, long long ld_dst, int esize, cudaStream_t st);
+
+// implicit-GEMM conv (conv_tcgen05.cu)
+int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
+                  int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st);
+
+}  // namespace aiehlc

@@ -1,0 +1,321 @@
+// int8 conv2d (NHWC x HWIO, stride 1, "same" zero padding) as an implicit GEMM on tcgen05,
+// with the per-output-channel shift-round-saturate stage fused into the epilogue.
+//
+//   GEMM view:  M = n*h*w output pixels, N = cout, K = kh*kw*cin in (kh, kw, ci) order.
+//   A tile   :  for one filter tap (kh,kw) the 128 x cin operand is simply the input image
+//               shifted by the tap offset, so one 4-D TMA box {cin, Wt, R, 1} fetches it and the
+//               hardware's out-of-bounds zero fill *is* the padding -- no im2col buffer exists.
+//   B tile   :  the weights re-laid once per call as [tap][cout][cin] (K-major) by a small
+//               pre-pass, then fetched by 2-D TMA boxes.
+//
+// One CTA computes one output tile of R image rows x Wt columns (R*Wt <= 128 = TMEM lanes) for
+// up to 256 output channels.  The reference has no convolution; the kernel follows the tiling
+// vocabulary of its matmul path (K loop, accumulate, flush once: tiling.py:299-333).
+#include <cstdio>
+
+#include "context.h"
+#include "gemm_tcgen05.cuh"
+
+namespace aiehlc {
+
+constexpr int kConvMaxStages = 12;
+constexpr int kConvThreads = 192;
+
+struct ConvParams {
+  int n, h, w, cin, cout, kh, kw, pad;
+  int wt, rows_per_tile;           // output tile: rows_per_tile image rows x wt columns
+  int tiles_w, tiles_h;            // tiles per image
+  int chunk;                       // K bytes per stage (cin chunk): 32, 64 or 128
+  int chunks_per_tap;              // cin / chunk
+  int cout_tile;                   // N of the MMA (multiple of 16, <= 256)
+  int stages, stage_bytes, a_bytes;
+  uint32_t tx_bytes;               // bytes one stage's two TMA boxes deliver
+  uint32_t swizzle_code, sbo_bytes;
+  uint32_t tmem_cols;
+  int8_t* y;
+  const uint8_t* shift_vec;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                 const ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* bar_mem = smem + p.stages * p.stage_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);
+  uint64_t* empty_bar = full_bar + kConvMaxStages;
+  uint64_t* tmem_full_bar = empty_bar + kConvMaxStages;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(tmem_full_bar), 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(tmem_base_slot), p.tmem_cols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  // tile -> (image, first output row, first output column, first output channel)
+  int t = blockIdx.x;
+  const int tw = t % p.tiles_w; t /= p.tiles_w;
+  const int th = t % p.tiles_h; t /= p.tiles_h;
+  const int img = t;
+  const int oh0 = th * p.rows_per_tile;
+  const int ow0 = tw * p.wt;
+  const int co0 = blockIdx.y * p.cout_tile;
+  const int taps = p.kh * p.kw;
+  const int num_kb = taps * p.chunks_per_tap;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
+        if (!ok) break;
+        const int tap = kb / p.chunks_per_tap;
+        const int c0 = (kb - tap * p.chunks_per_tap) * p.chunk;
+        const int fh = tap / p.kw, fw = tap - fh * p.kw;
+        const uint32_t fb = smem_u32(&full_bar[stage]);
+        mbar_expect_tx(fb, p.tx_bytes);
+        uint8_t* sa = smem + stage * p.stage_bytes;
+        uint8_t* sb = sa + p.a_bytes;
+        // Innermost coordinate (channel) is a multiple of the chunk size, hence 16-byte aligned;
+        // the spatial coordinates may be negative or past the edge: those elements read as zero.
+        tma_load_4d(smem_u32(sa), &tmap_x, fb, c0, ow0 + fw - p.pad, oh0 + fh - p.pad, img);
+        tma_load_2d(smem_u32(sb), &tmap_w, fb, c0, tap * p.cout + co0);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+      if (!ok)
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc<KIND_I8>(kBlockM, p.cout_tile);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + stage * p.stage_bytes);
+        const uint32_t sb = sa + p.a_bytes;
+        const uint64_t adesc = make_kmajor_desc(sa, p.sbo_bytes, p.swizzle_code);
+        const uint64_t bdesc = make_kmajor_desc(sb, p.sbo_bytes, p.swizzle_code);
+        for (int k = 0; k < p.chunk / kUmmaKBytes; ++k)
+          umma_ss<KIND_I8, 1>(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        umma_commit(smem_u32(&empty_bar[stage]));
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+      if (ok) umma_commit(smem_u32(tmem_full_bar));
+    }
+  } else {
+    const int quad = warp & 3;
+    bool ok = mbar_wait(smem_u32(tmem_full_bar), 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    ok = __all_sync(0xFFFFFFFFu, ok);
+    if (ok) {
+      tc_fence_after();
+      const int m = quad * 32 + lane;
+      const int oh = oh0 + m / p.wt, ow = ow0 + m % p.wt;
+      const bool pix_ok = m < p.rows_per_tile * p.wt && oh < p.h && ow < p.w;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+      int8_t* yrow = p.y + ((static_cast<long long>(img) * p.h + oh) * p.w + ow) * p.cout;
+      const bool vec = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && (p.cout % 16 == 0);
+      for (int c = 0; c < p.cout_tile; c += 32) {
+        __syncwarp();
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c, r);
+        tmem_ld_wait();
+        const int col0 = co0 + c;
+        if (!pix_ok || col0 >= p.cout) continue;
+        const int ncols = min(32, min(p.cout_tile - c, p.cout - col0));
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          uint32_t wv = 0;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const int s = (j + b < ncols) ? static_cast<int>(p.shift_vec[col0 + j + b]) : 0;
+            wv |= (static_cast<uint32_t>(srs_i8(static_cast<int>(r[j + b]), s)) & 0xFFu) << (8 * b);
+          }
+          packed[j >> 2] = wv;
+        }
+        if (vec && ncols == 32) {
+          *reinterpret_cast<uint4*>(yrow + col0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(yrow + col0 + 16) =
+              make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < ncols) yrow[col0 + j] = static_cast<int8_t>((packed[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, p.tmem_cols);
+  }
+}
+
+// HWIO [tap][cin][cout] -> [tap][cout][cin]: makes the weights K-major like every other operand.
+__global__ void conv_weight_prepack_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ wp,
+                                           int taps, int cin, int cout) {
+  const long long n = static_cast<long long>(taps) * cin * cout;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int ci = static_cast<int>(i % cin);
+    const long long r = i / cin;
+    const int co = static_cast<int>(r % cout);
+    const int tap = static_cast<int>(r / cout);
+    wp[i] = w[(static_cast<long long>(tap) * cin + ci) * cout + co];
+  }
+}
+
+// Direct form for shapes the tensor-core tiling does not cover (cin not a multiple of 32, ...).
+__global__ void conv2d_i8_direct_kernel(const int8_t* __restrict__ x, const int8_t* __restrict__ w,
+                                        int8_t* __restrict__ y, int n, int h, int wd, int cin, int cout,
+                                        int kh, int kw, int pad, const uint8_t* __restrict__ shift_vec) {
+  const long long total = static_cast<long long>(n) * h * wd * cout;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int co = static_cast<int>(i % cout);
+    long long r = i / cout;
+    const int ow = static_cast<int>(r % wd); r /= wd;
+    const int oh = static_cast<int>(r % h);
+    const int img = static_cast<int>(r / h);
+    int acc = 0;
+    for (int fh = 0; fh < kh; ++fh) {
+      const int ih = oh + fh - pad;
+      if (ih < 0 || ih >= h) continue;
+      for (int fw = 0; fw < kw; ++fw) {
+        const int iw = ow + fw - pad;
+        if (iw < 0 || iw >= wd) continue;
+        const int8_t* xp = x + ((static_cast<long long>(img) * h + ih) * wd + iw) * cin;
+        const int8_t* wp = w + (static_cast<long long>(fh * kw + fw) * cin) * cout + co;
+        for (int ci = 0; ci < cin; ++ci) acc += static_cast<int>(xp[ci]) * static_cast<int>(wp[static_cast<long long>(ci) * cout]);
+      }
+    }
+    y[i] = static_cast<int8_t>(srs_i8(acc, shift_vec[co]));
+  }
+}
+
+int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
+                  int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
+  const bool tensor_ok = (cin % 32 == 0) && (cin == 32 || cin == 64 || cin % 128 == 0) &&
+                         (cout % 16 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+  if (!tensor_ok) {
+    const long long total = static_cast<long long>(n) * h * wd * cout;
+    long long g = (total + 255) / 256;
+    if (g > ctx->sm_count * 16LL) g = ctx->sm_count * 16LL;
+    conv2d_i8_direct_kernel<<<static_cast<int>(g), 256, 0, st>>>(x, w, y, n, h, wd, cin, cout, kh, kw,
+                                                                 pad, shift_vec);
+    AIEHLC_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return AIEHLC_OK;
+  }
+
+  const int taps = kh * kw;
+  const size_t wbytes = static_cast<size_t>(taps) * cin * cout;
+  if (ctx->pack_b.reserve(wbytes)) return AIEHLC_ERR_NOMEM;
+  {
+    long long g = (static_cast<long long>(wbytes) + 255) / 256;
+    if (g > ctx->sm_count * 8LL) g = ctx->sm_count * 8LL;
+    conv_weight_prepack_kernel<<<static_cast<int>(g), 256, 0, st>>>(
+        w, static_cast<int8_t*>(ctx->pack_b.ptr), taps, cin, cout);
+    AIEHLC_CUDA(cudaGetLastError());
+    ctx->launches++;
+  }
+
+  ConvParams p{};
+  p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
+  p.wt = wd <= kBlockM ? wd : kBlockM;
+  p.rows_per_tile = wd <= kBlockM ? kBlockM / wd : 1;
+  if (p.rows_per_tile > h) p.rows_per_tile = h;
+  p.tiles_w = (wd + p.wt - 1) / p.wt;
+  p.tiles_h = (h + p.rows_per_tile - 1) / p.rows_per_tile;
+  p.chunk = cin >= 128 ? 128 : cin;
+  p.chunks_per_tap = cin / p.chunk;
+  p.cout_tile = cout <= 256 ? cout : 256;
+  if (cout > 256 && cout % 256 != 0) {
+    // keep every channel tile a legal MMA N: use the largest multiple of 16 that divides cout
+    int ct = 256;
+    while (ct > 16 && cout % ct != 0) ct -= 16;
+    p.cout_tile = ct;
+  }
+  const int n_tiles = (cout + p.cout_tile - 1) / p.cout_tile;
+  p.swizzle_code = p.chunk == 128 ? 2u : (p.chunk == 64 ? 4u : 6u);
+  p.sbo_bytes = 8u * p.chunk;
+  p.a_bytes = kBlockM * p.chunk;                       // 128 rows reserved, R*Wt of them written
+  const int b_bytes = (p.cout_tile * p.chunk + 1023) / 1024 * 1024;
+  p.stage_bytes = p.a_bytes + b_bytes;
+  p.tx_bytes = static_cast<uint32_t>(p.chunk) * (p.wt * p.rows_per_tile + p.cout_tile);
+  const int budget = 200 * 1024;
+  int stages = budget / p.stage_bytes;
+  if (stages > kConvMaxStages) stages = kConvMaxStages;
+  const int num_kb = taps * p.chunks_per_tap;
+  if (stages > num_kb) stages = num_kb;
+  p.stages = stages;
+  uint32_t cols = 32;
+  while (cols < static_cast<uint32_t>(p.cout_tile)) cols <<= 1;
+  p.tmem_cols = cols;
+  p.y = y; p.shift_vec = shift_vec; p.status = ctx->d_status;
+
+  // x as a 4-D tensor {cin, w, h, n}; box {chunk, wt, rows_per_tile, 1}
+  CUtensorMap mx, mw;
+  {
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(wd),
+                                static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(n)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cin) * wd,
+                                   static_cast<cuuint64_t>(cin) * wd * h};
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.wt),
+                               static_cast<cuuint32_t>(p.rows_per_tile), 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUtensorMapSwizzle sw = p.chunk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : p.chunk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                  : CU_TENSOR_MAP_SWIZZLE_32B;
+    CUresult r = ctx->encode(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(x), dims, strides,
+                             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv input");
+    const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(taps) * cout};
+    const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(cin)};
+    const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.cout_tile)};
+    r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, ctx->pack_b.ptr, wdims, wstrides, wbox, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
+  }
+
+  const int smem_bytes = p.stages * p.stage_bytes + 512 + 1024;
+  AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   smem_bytes));
+  dim3 grid(n * p.tiles_h * p.tiles_w, n_tiles);
+  conv2d_i8_kernel<<<grid, kConvThreads, smem_bytes, st>>>(mx, mw, p);
+  AIEHLC_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return AIEHLC_OK;
+}
+
+}  // namespace aiehlc

@@ -1,0 +1,138 @@
+// Host side of the tcgen05 tile GEMM: tensor-map construction, tile-shape choice, launch.
+#include <cstdio>
+#include <cstdlib>
+
+#include "context.h"
+#include "gemm_tcgen05.cuh"
+
+namespace aiehlc {
+
+namespace {
+
+int encode_kmajor_map(aiehlc_ctx* ctx, CUtensorMap* map, int kind, const void* base, long long rows,
+                      long long k, long long ld_elems, int box_rows) {
+  const int esize = kind == KIND_I8 ? 1 : 2;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * esize};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockKBytes / esize),
+                             static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = ctx->encode(
+      map, kind == KIND_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char msg[160];
+    snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled failed (CUresult %d) rows=%lld k=%lld ld=%lld",
+             static_cast<int>(r), rows, k, ld_elems);
+    return fail(AIEHLC_ERR_CUDA, msg);
+  }
+  return AIEHLC_OK;
+}
+
+// Tile-N choice: fewest "tile-time units" over whole waves of `sms` persistent CTAs.  Narrow
+// tiles re-read A from shared memory more often per MMA, hence the efficiency factors.
+int choose_tile_n(int M, int N, int sms) {
+  const int cand[3] = {256, 128, 64};
+  const double eff[3] = {1.0, 0.90, 0.60};
+  const long long mblocks = (M + kBlockM - 1) / kBlockM;
+  double best = 0;
+  int best_bn = 64;
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cand[i];
+    const long long tiles = mblocks * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    const double cost = static_cast<double>(waves) * bn / eff[i];
+    if (i == 0 || cost < best) { best = cost; best_bn = bn; }
+  }
+  return best_bn;
+}
+
+template <int kKind, int kBN, int kEpi>
+int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
+  using S = GemmSmem<kBN>;
+  CUtensorMap ma, mb;
+  int rc = encode_kmajor_map(ctx, &ma, kKind, c.A, c.M, c.K, c.lda, kBlockM);
+  if (rc) return rc;
+  rc = encode_kmajor_map(ctx, &mb, kKind, c.B, c.N, c.K, c.ldb, kBN > 128 ? 128 : kBN);
+  if (rc) return rc;
+
+  const int esize = kKind == KIND_I8 ? 1 : 2;
+  const int cesize = kEpi == EPI_I8_SRS ? 1 : (kEpi == EPI_BF16 ? 2 : 4);
+  GemmParams p{};
+  p.M = c.M; p.N = c.N; p.K = c.K;
+  p.C = c.C; p.ldc = c.ldc;
+  p.acc_in = c.acc_in; p.ld_acc = c.ld_acc;
+  p.shift_vec = c.shift_vec; p.shift = c.shift;
+  p.num_m_blocks = (c.M + kBlockM - 1) / kBlockM;
+  p.num_n_blocks = (c.N + kBN - 1) / kBN;
+  p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
+  p.group_m = 8;
+  // 32 consecutive outputs per thread are written with 16-byte stores when every row start is aligned.
+  bool vec = (reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0);
+  p.vec_ok = vec ? 1 : 0;
+  p.status = ctx->d_status;
+
+  auto kern = gemm_tn_kernel<kKind, kBN, kEpi>;
+  // Per device and cheap, so simply repeated on every launch.
+  AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  kern<<<grid, kGemmThreads, S::kTotal, st>>>(ma, mb, p);
+  AIEHLC_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return AIEHLC_OK;
+}
+
+template <int kKind, int kEpi>
+int dispatch_bn(aiehlc_ctx* ctx, const GemmCall& c, int bn, cudaStream_t st) {
+  switch (bn) {
+    case 256: return launch_one<kKind, 256, kEpi>(ctx, c, st);
+    case 128: return launch_one<kKind, 128, kEpi>(ctx, c, st);
+    default: return launch_one<kKind, 64, kEpi>(ctx, c, st);
+  }
+}
+
+}  // namespace
+
+int launch_gemm(aiehlc_ctx* ctx, const GemmCall& call, cudaStream_t st) {
+  GemmCall c = call;
+  if (c.M <= 0 || c.N <= 0 || c.K <= 0) return fail(AIEHLC_ERR_INVALID, "gemm: M, N, K must be positive");
+  const int esize = c.kind == KIND_I8 ? 1 : 2;
+
+  // TMA wants 16-byte aligned bases and row pitches.  Operands that do not comply are first
+  // copied to a pitched workspace (the K tail beyond the true extent is never read: the
+  // tensor map keeps K as its inner extent and the hardware zero-fills past it).
+  auto needs_pack = [&](const void* ptr, long long ld) {
+    return reinterpret_cast<uintptr_t>(ptr) % 16 != 0 || (ld * esize) % 16 != 0;
+  };
+  if (needs_pack(c.A, c.lda)) {
+    const long long ld = (static_cast<long long>(c.K) * esize + 15) / 16 * 16 / esize;
+    if (ctx->pack_a.reserve(static_cast<size_t>(c.M) * ld * esize)) return AIEHLC_ERR_NOMEM;
+    int rc = launch_repack(ctx, c.A, ctx->pack_a.ptr, c.M, c.K, c.lda, ld, esize, st);
+    if (rc) return rc;
+    c.A = ctx->pack_a.ptr; c.lda = ld;
+  }
+  if (needs_pack(c.B, c.ldb)) {
+    const long long ld = (static_cast<long long>(c.K) * esize + 15) / 16 * 16 / esize;
+    if (ctx->pack_b.reserve(static_cast<size_t>(c.N) * ld * esize)) return AIEHLC_ERR_NOMEM;
+    int rc = launch_repack(ctx, c.B, ctx->pack_b.ptr, c.N, c.K, c.ldb, ld, esize, st);
+    if (rc) return rc;
+    c.B = ctx->pack_b.ptr; c.ldb = ld;
+  }
+
+  int bn = ctx->force_tile_n ? ctx->force_tile_n : choose_tile_n(c.M, c.N, ctx->sm_count);
+  if (c.kind == KIND_I8) {
+    switch (c.epi) {
+      case EPI_I32: return dispatch_bn<KIND_I8, EPI_I32>(ctx, c, bn, st);
+      case EPI_I32_ACC: return dispatch_bn<KIND_I8, EPI_I32_ACC>(ctx, c, bn, st);
+      case EPI_I8_SRS: return dispatch_bn<KIND_I8, EPI_I8_SRS>(ctx, c, bn, st);
+      default: return fail(AIEHLC_ERR_INVALID, "gemm: bad output stage for int8");
+    }
+  }
+  if (c.epi != EPI_BF16) return fail(AIEHLC_ERR_INVALID, "gemm: bad output stage for bf16");
+  return dispatch_bn<KIND_BF16, EPI_BF16>(ctx, c, bn, st);
+}
+
+}  // namespace aiehlc

@@ -1,0 +1,329 @@
+// Persistent, warp-specialised tile GEMM for sm_100a:  C[M][N] = A[M][K] . B[N][K]^T
+//
+// This is the B200 counterpart of the reference's per-tile matmul kernels
+// (example/perf/aieml_perf.cc:61-83 `perf`, example/matrixmultiply/aieml_mm.cc:41-93 `mm`):
+// A row-major, B stored [N][K] ("column-major B"), C row-major, exactly the
+// layout of the reference's CPU golden loop (aieml_perf.cc:199-231).  Both
+// operands are K-major, which is the native operand layout of tcgen05.mma.
+//
+//   warp 0   TMA producer   : cp.async.bulk.tensor tiles of A and B into a kStages-deep smem ring
+//   warp 1   MMA issuer     : tcgen05.mma (kind::i8 -> s32, kind::f16 -> f32) into TMEM; owns TMEM
+//   warps 2-5 epilogue      : tcgen05.ld the accumulator, fused output stage, global stores
+//
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps
+// the K loop of tile i+1.  The whole K range (all split-K slices of the
+// reference's "cascade" formulation) is accumulated in TMEM before one flush.
+//
+// Output stages (kEpi):
+//   EPI_I32      C(int32)  = acc
+//   EPI_I32_ACC  C(int32) += acc                       (stage s>0 of a multi-launch cascade)
+//   EPI_I8_SRS   C(int8)   = srs(acc [+ acc_in], shift[col])   shift-round(half-even)-saturate
+//   EPI_BF16     C(bf16)   = rn(acc)                    (kind::f16, fp32 accumulate)
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "sm100_ptx.cuh"
+
+namespace aiehlc {
+
+enum : int { KIND_I8 = 0, KIND_BF16 = 1 };
+enum : int { EPI_I32 = 0, EPI_I32_ACC = 1, EPI_I8_SRS = 2, EPI_BF16 = 3 };
+
+constexpr int kBlockM = 128;        // rows of C per tile = TMEM lanes
+constexpr int kBlockKBytes = 128;   // one 128B swizzle span of K per stage
+constexpr int kUmmaKBytes = 32;     // K bytes consumed by one tcgen05.mma (32 x i8, 16 x bf16)
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;                 // int32 / int8 / bf16, row-major, leading dimension ldc (elements)
+  long long ldc;
+  const int32_t* acc_in;   // EPI_I8_SRS: optional int32 partial sums [M][ld_acc] added before srs
+  long long ld_acc;
+  const uint8_t* shift_vec;  // EPI_I8_SRS: optional per-output-column shift
+  int shift;                 // EPI_I8_SRS: shift used when shift_vec == nullptr
+  int num_m_blocks, num_n_blocks, num_k_blocks;
+  int group_m;             // rasterisation: tiles walk group_m row-blocks before the next column
+  int vec_ok;              // C (and acc_in) rows are 16-byte aligned: vector stores allowed
+  int* status;             // device status word (0 = ok)
+};
+
+// Shift-round-saturate, pure integer: round half to even on the dropped bits, saturate to int8.
+__host__ __device__ __forceinline__ int srs_i8(int acc, int s) {
+  int q = acc;
+  if (s > 0) {
+    q = acc >> s;  // arithmetic shift: floor
+    const unsigned mask = (s >= 32) ? 0xFFFFFFFFu : ((1u << s) - 1u);
+    const unsigned r = static_cast<unsigned>(acc) & mask;
+    const unsigned h = 1u << (s - 1);
+    if (r > h || (r == h && (q & 1))) q += 1;
+  }
+  return q > 127 ? 127 : (q < -128 ? -128 : q);
+}
+
+template <int kBN>
+struct GemmSmem {
+  static constexpr int kABytes = kBlockM * kBlockKBytes;
+  static constexpr int kBBytes = kBN * kBlockKBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBudget = 227 * 1024 - 2048;  // keep room for barriers + 1 KB alignment
+  static constexpr int kStagesRaw = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kBarBytes = 512;
+  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;
+};
+
+__device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb, int& nb) {
+  const int per_group = p.group_m * p.num_n_blocks;
+  const int g = t / per_group;
+  const int first_m = g * p.group_m;
+  const int rows = min(p.group_m, p.num_m_blocks - first_m);
+  const int r = t - g * per_group;
+  mb = first_m + r % rows;
+  nb = r / rows;
+}
+
+template <int kKind, int kBN, int kEpi>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmParams p) {
+  using S = GemmSmem<kBN>;
+  constexpr int kStages = S::kStages;
+  constexpr int kBBoxRows = kBN > 128 ? 128 : kBN;     // B arrives in boxes of at most 128 rows
+  constexpr int kBBoxes = kBN / kBBoxRows;
+  constexpr uint32_t kTmemCols = (2 * kBN) < 32 ? 32 : 2 * kBN;  // two accumulators
+  constexpr int kElemBytes = kKind == KIND_I8 ? 1 : 2;
+  constexpr int kBlockKElems = kBlockKBytes / kElemBytes;
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns");
+  static_assert(kBN % 16 == 0 && kBN >= 16 && kBN <= 256, "UMMA N");
+
+  extern __shared__ uint8_t smem_raw[];
+  // 128B-swizzled tiles need 1024-byte aligned bases.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* bar_mem = smem + kStages * S::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full_bar = empty_bar + kStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(tmem_base_slot), kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mb, nb;
+        tile_coords(t, p, mb, nb);
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status,
+                         ST_TIMEOUT_EMPTY);
+          if (!ok) break;
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          mbar_expect_tx(fb, S::kStageBytes);
+          uint8_t* sa = smem + stage * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          tma_load_2d(smem_u32(sa), &tmap_a, fb, kb * kBlockKElems, mb * kBlockM);
+#pragma unroll
+          for (int b = 0; b < kBBoxes; ++b)
+            tma_load_2d(smem_u32(sb + b * kBBoxRows * kBlockKBytes), &tmap_b, fb,
+                        kb * kBlockKElems, nb * kBN + b * kBBoxRows);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Aborting: give copies already in flight time to land before the CTA retires.
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<kKind>(kBlockM, kBN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status,
+                       ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+          const uint64_t adesc = make_kmajor_desc(sa, 1024, 2);
+          const uint64_t bdesc = make_kmajor_desc(sb, 1024, 2);
+#pragma unroll
+          for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
+            // K-step inside the swizzle span: advance the start-address field by 32 B (>>4 = 2).
+            umma_ss<kKind, 1>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc,
+                              (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));  // frees the stage when these MMAs retire
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      int mb, nb;
+      tile_coords(t, p, mb, nb);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status,
+                     ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = mb * kBlockM + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
+#pragma unroll 1
+      for (int c = 0; c < kBN; c += 32) {
+        __syncwarp();  // lanes that skipped the stores of the previous chunk rejoin here
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c, r);
+        tmem_ld_wait();
+        const int col0 = nb * kBN + c;
+        if (!row_ok || col0 >= p.N) continue;
+        const int ncols = min(32, p.N - col0);
+        if constexpr (kEpi == EPI_I32 || kEpi == EPI_I32_ACC) {
+          int32_t* dst = static_cast<int32_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+          if (p.vec_ok && ncols == 32) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              int4 v = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+              if constexpr (kEpi == EPI_I32_ACC) {
+                const int4 o = *reinterpret_cast<const int4*>(dst + j);
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              *reinterpret_cast<int4*>(dst + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) {
+                if constexpr (kEpi == EPI_I32_ACC) dst[j] += static_cast<int32_t>(r[j]);
+                else dst[j] = static_cast<int32_t>(r[j]);
+              }
+          }
+        } else if constexpr (kEpi == EPI_I8_SRS) {
+          int8_t* dst = static_cast<int8_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+          if (p.acc_in != nullptr) {
+            const int32_t* ai = p.acc_in + static_cast<long long>(row) * p.ld_acc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) r[j] += static_cast<uint32_t>(ai[j]);
+          }
+          uint32_t packed[8];
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const int s = (p.shift_vec != nullptr)
+                                ? (j + b < ncols ? static_cast<int>(p.shift_vec[col0 + j + b]) : 0)
+                                : p.shift;
+              w |= (static_cast<uint32_t>(srs_i8(static_cast<int>(r[j + b]), s)) & 0xFFu) << (8 * b);
+            }
+            packed[j >> 2] = w;
+          }
+          if (p.vec_ok && ncols == 32) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            *reinterpret_cast<uint4*>(dst + 16) =
+                make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) dst[j] = static_cast<int8_t>((packed[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+          }
+        } else {  // EPI_BF16
+          __nv_bfloat16* dst =
+              static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const __nv_bfloat162 h =
+                __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          if (p.vec_ok && ncols == 32) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<uint4*>(dst + 2 * j) =
+                  make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) {
+                const uint16_t bits = static_cast<uint16_t>(packed[j >> 1] >> (16 * (j & 1)));
+                reinterpret_cast<uint16_t*>(dst)[j] = bits;
+              }
+          }
+        }
+      }
+      // Accumulator drained: hand it back to the MMA issuer.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace aiehlc

@@ -1,0 +1,125 @@
+/*
+ * aiehlc_b200 -- C ABI of the B200 kernel-call path.
+ *
+ * These entry points are what a host program written against aiehlc's kernel-call
+ * surface binds to when the AIE tile kernels are replaced by sm_100a kernels.  Each one
+ * cites the reference construct it stands in for (paths relative to the aiehlc tree).
+ *
+ * Layout contract (the reference's CPU golden loop, example/perf/aieml_perf.cc:199-231):
+ *   A[M][K] row-major, B stored [N][K] ("column-major B": the K-vector of every output
+ *   column is contiguous), C[M][N] row-major, integer accumulation in 32 bits:
+ *       C[i][j] = sum_k A[i][k] * B[j][k]
+ *
+ * Conventions
+ *   - every function returns AIEHLC_OK (0) or a negative error code; no exceptions cross
+ *     the boundary; aiehlc_last_error() gives the message of the calling thread's last failure;
+ *   - `_dev` functions take device pointers, enqueue on `stream` (a cudaStream_t passed as
+ *     void*; NULL is CUDA's default stream) and return without synchronising;
+ *   - `_host` functions take host pointers, stage through context-owned device buffers on the
+ *     context's own stream (H2D copy, kernel, D2H copy) and return after the result is in the
+ *     host buffer;
+ *   - there is no CPU fallback: without a usable CUDA device aiehlc_create() fails.
+ *   - one context per host thread / stream: calls on one context must not overlap.
+ */
+#ifndef AIEHLC_B200_H
+#define AIEHLC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AIEHLC_OK 0
+#define AIEHLC_ERR_INVALID (-1)     /* bad argument (null pointer, negative size, shift > 31 ...) */
+#define AIEHLC_ERR_CUDA (-2)        /* a CUDA runtime / driver call failed */
+#define AIEHLC_ERR_UNSUPPORTED (-3) /* shape outside what the kernel family covers */
+#define AIEHLC_ERR_DEVICE (-4)      /* a kernel reported a non-zero status word (bounded wait ran out) */
+#define AIEHLC_ERR_NOMEM (-5)
+
+typedef struct aiehlc_ctx aiehlc_ctx;
+
+/* Device bring-up.  Stands in for the XAie_CfgInitialize / XAie_PartitionInitialize sequence
+ * of every example's main() (example/perf/aieml_perf.cc:265-313): selects CUDA device `device`,
+ * creates the context's stream and its status word. */
+int aiehlc_create(int device, aiehlc_ctx** out);
+/* XAie_PartitionTeardown (aieml_perf.cc:321): frees every buffer the context owns. */
+int aiehlc_destroy(aiehlc_ctx* ctx);
+const char* aiehlc_last_error(void);
+int aiehlc_sm_count(const aiehlc_ctx* ctx);
+/* Waits for `stream`, then reads and clears the device status word.
+ * Non-zero *status means a kernel gave up on a bounded wait; results of that launch are invalid.
+ * Plays the part of the XAie_CoreWaitForDone poll (aieml_perf.cc:174-184). */
+int aiehlc_sync(aiehlc_ctx* ctx, void* stream, int* status);
+
+/* ---- the reference's own kernel: int32 x int32 -> int32 (wrap-around) ----------------------
+ * `perf` (example/perf/aieml_perf.cc:61-83) and `mm` (example/matrixmultiply/aieml_mm.cc:41-93),
+ * generalised from 16x16x16 to M,N,K.  `in` is the packed window the examples fill: A (M*K
+ * words) followed by B (N*K words); `out` is C (M*N words).  Arithmetic is uint32 wrap-around
+ * exactly as the kernel's `ret += vec1[..] * vec2[..]` (aieml_perf.cc:74-82). */
+int aiehlc_mm_i32_dev(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K,
+                      void* stream);
+int aiehlc_mm_i32_host(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K);
+
+/* ---- int8 x int8 -> int32 tile GEMM (tcgen05 kind::i8, int32 accumulators in TMEM) ---------
+ * The golden loop of aieml_perf.cc:199-231 with int8 operands sign-extended to 32 bits; the
+ * tile shape / K-loop-then-flush structure follows the compiler's matmul tiling
+ * (src/mlir/mlirfront/tilinglinalg/tilinglinalg.cpp:101-129, tiling.py:299-333).
+ * accumulate != 0: C += A.B^T, i.e. stage s>0 of a multi-launch cascade over K slices (the
+ * chained-kernel pattern of example/multi/multi_tile.cpp:105-145, seq_full_col.cpp:132-153). */
+int aiehlc_gemm_i8_i32_dev(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int32_t* C, int M,
+                           int N, int K, int accumulate, void* stream);
+int aiehlc_gemm_i8_i32_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int32_t* C, int M,
+                            int N, int K);
+
+/* ---- int8 GEMM with the fused shift-round-saturate output stage ---------------------------
+ * C(int8)[i][j] = srs( sum_k A[i][k]*B[j][k] + (acc_in ? acc_in[i][j] : 0), s_j )
+ *   s_j = shift_vec ? shift_vec[j] : shift,   0 <= s <= 31
+ *   srs(x, s): q = x >> s (arithmetic); r = x & (2^s - 1); q += (r > 2^(s-1)) || (r == 2^(s-1) && q odd);
+ *              result = clamp(q, -128, 127)            -- round half to even, saturate; s = 0: clamp only
+ * `splitk` (>= 1, must divide K): the K range is walked as `splitk` consecutive equal slices that are
+ * accumulated in slice order inside TMEM and flushed once -- the cascade formulation executed
+ * within one launch.  Integer addition is associative, so the result equals the unsplit one.
+ * The reference has no srs stage of its own; this definition is the contract (no counterpart file). */
+int aiehlc_gemm_i8_srs_dev(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
+                           int K, int shift, const uint8_t* shift_vec, const int32_t* acc_in,
+                           int splitk, void* stream);
+int aiehlc_gemm_i8_srs_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int8_t* C, int M,
+                            int N, int K, int shift, const uint8_t* shift_vec, int splitk);
+
+/* Flush of a cascade kept in an int32 buffer: out(int8) = srs(in, shift) element-wise over a
+ * rows x cols row-major matrix (shift_vec indexes columns).  The last hop of the chain in
+ * example/multi/seq_full_col.cpp:156-159 (tile -> external memory). */
+int aiehlc_srs_i32_i8_dev(aiehlc_ctx* ctx, const int32_t* in, int8_t* out, long long rows,
+                          long long cols, int shift, const uint8_t* shift_vec, void* stream);
+
+/* ---- bf16 x bf16 -> bf16 GEMM (tcgen05 kind::f16, fp32 accumulators in TMEM) ---------------
+ * Same loop nest and layout as above; operands and result are raw bf16 bit patterns.
+ * No counterpart kernel in the reference (its kernels are integer). */
+int aiehlc_gemm_bf16_dev(aiehlc_ctx* ctx, const uint16_t* A, const uint16_t* B, uint16_t* C, int M,
+                         int N, int K, void* stream);
+int aiehlc_gemm_bf16_host(aiehlc_ctx* ctx, const uint16_t* A, const uint16_t* B, uint16_t* C, int M,
+                          int N, int K);
+
+/* ---- int8 conv2d as an implicit GEMM, per-output-channel srs ------------------------------
+ * x: NHWC int8 [n][h][w][cin]; w: HWIO int8 [kh][kw][cin][cout]; y: NHWC int8 [n][h][w][cout]
+ * stride 1, zero padding `pad` on every side, output spatial size = input spatial size
+ * (requires kh = kw = 2*pad + 1).  y = srs( sum_{kh,kw,ci} x[n][oh+kh-pad][ow+kw-pad][ci] * w[kh][kw][ci][co], shift_vec[co] ).
+ * No counterpart kernel in the reference. */
+int aiehlc_conv2d_i8_srs_dev(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n,
+                             int h, int wd, int cin, int cout, int kh, int kw, int pad,
+                             const uint8_t* shift_vec, void* stream);
+int aiehlc_conv2d_i8_srs_host(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n,
+                              int h, int wd, int cin, int cout, int kh, int kw, int pad,
+                              const uint8_t* shift_vec);
+
+/* Tuning knob for experiments: force the N extent of the GEMM tile (64, 128 or 256; 0 = choose). */
+int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n);
+/* Number of kernel launches this context has enqueued since creation. */
+long long aiehlc_launch_count(const aiehlc_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AIEHLC_B200_H */
