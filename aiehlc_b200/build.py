@@ -85,6 +85,32 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+EXAMPLES_DIR = PKG.parent / "examples"
+EXAMPLES_BIN = EXAMPLES_DIR / "_bin"
+
+
+def build_examples() -> list[Path]:
+    """Compiles examples/*.cc (C++ host programs on the XAie_* surface) against the library."""
+    build()
+    EXAMPLES_BIN.mkdir(exist_ok=True)
+    outs = []
+    for src in sorted(EXAMPLES_DIR.glob("*.cc")):
+        out = EXAMPLES_BIN / src.stem
+        if out.exists() and out.stat().st_mtime > max(src.stat().st_mtime, LIB_PATH.stat().st_mtime):
+            outs.append(out)
+            continue
+        cmd = ["g++", "-std=c++17", "-O2", "-I", str(INCLUDE), "-I", str(INCLUDE / "bsp"), str(src),
+               "-L", str(LIB_DIR), "-laiehlc_b200", "-Wl,-rpath,$ORIGIN/../../aiehlc_b200/lib", "-o", str(out)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"example {src.name} failed to build:\n{res.stderr}")
+        outs.append(out)
+    return outs
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    if "--examples" in sys.argv:
+        for e in build_examples():
+            print(e)

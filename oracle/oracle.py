@@ -6,21 +6,37 @@ TEST INFRASTRUCTURE: the checker for the CUDA path and the timed CPU baseline.  
 from __future__ import annotations
 
 import ctypes as C
+import hashlib
 import subprocess
 from pathlib import Path
 
 import numpy as np
 
 HERE = Path(__file__).resolve().parent
-LIB = HERE / "_build" / "liboracle.so"
 _lib = None
+
+
+def _cpu_tag() -> str:
+    """Hash of this CPU's feature flags: the library is compiled with -march=native."""
+    try:
+        for line in Path("/proc/cpuinfo").read_text().splitlines():
+            if line.startswith("flags"):
+                return hashlib.sha1(line.encode()).hexdigest()[:10]
+    except OSError:
+        pass
+    return "generic"
+
+
+LIB = HERE / "_build" / f"liboracle-{_cpu_tag()}.so"
 
 
 def build(force: bool = False) -> Path:
     src = HERE / "oracle.c"
     if force or not LIB.exists() or LIB.stat().st_mtime < src.stat().st_mtime:
-        subprocess.run(["make", "-C", str(HERE), "-B" if force else "-s", "_build/liboracle.so"], check=True,
-                       capture_output=True)
+        cmd = ["make", "-C", str(HERE), "-s", f"OUT=_build/{LIB.name}"] + (["-B"] if force else [])
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"oracle build failed:\n{res.stdout}\n{res.stderr}")
     return LIB
 
 

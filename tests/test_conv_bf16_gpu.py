@@ -1,0 +1,89 @@
+"""conv2d (bit-exact) and bf16 GEMM (tolerance) against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from aiehlc_b200 import synth
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+BF16_TOL = 1e-2   # max |got - ref| / max(|ref|, 1): the benchmark's stated tolerance
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+CONV_SHAPES = [(1, 56, 56, 64, 64),      # the benchmark configuration
+               (2, 14, 14, 32, 48), (1, 20, 150, 128, 64), (1, 9, 9, 256, 32), (3, 5, 7, 64, 16),
+               (1, 1, 1, 64, 64), (1, 130, 3, 32, 16), (1, 6, 6, 128, 272),
+               (1, 8, 8, 24, 16), (2, 5, 5, 3, 8), (1, 4, 4, 64, 10)]   # the last three take the direct kernel
+
+
+@pytest.mark.parametrize("shape", CONV_SHAPES)
+def test_conv2d_matches_oracle(ctx, shape):
+    n, h, w, cin, cout = shape
+    x = synth.int8_uniform(4, (n, h, w, cin))
+    wt = synth.int8_uniform(1004, (3, 3, cin, cout))
+    sv = np.full(cout, 6, np.uint8)
+    exp = O.conv2d_i8_srs(x, wt, sv, pad=1)
+    got = ctx.conv2d_i8_srs(_dev(x), _dev(wt), _dev(sv), pad=1).cpu().numpy()
+    assert ctx.sync() == 0
+    assert np.array_equal(got, exp)
+
+
+def test_conv2d_per_channel_shifts_5x5_and_host_entry(ctx):
+    x = synth.int8_uniform(4, (1, 12, 12, 64))
+    wt = synth.int8_uniform(1004, (5, 5, 64, 32))
+    sv = (np.arange(32) % 14).astype(np.uint8)
+    exp = O.conv2d_i8_srs(x, wt, sv, pad=2)
+    assert np.array_equal(ctx.conv2d_i8_srs_host(x, wt, sv, pad=2), exp)
+    x1 = synth.int8_uniform(4, (1, 10, 10, 32))
+    w1 = synth.int8_uniform(1004, (1, 1, 32, 32))
+    assert np.array_equal(ctx.conv2d_i8_srs_host(x1, w1, sv, pad=0), O.conv2d_i8_srs(x1, w1, sv, pad=0))
+
+
+def _bf16_err(got_bits, ref32):
+    got = synth.bf16_bits_to_f32(got_bits).astype(np.float64)
+    return float(np.max(np.abs(got - ref32) / np.maximum(np.abs(ref32), 1.0)))
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 256, 512), (300, 200, 136), (64, 72, 8), (33, 17, 20),
+                                   (1024, 1024, 1024)])
+def test_gemm_bf16_within_tolerance(ctx, shape):
+    M, N, K = shape
+    A = synth.normal_bf16_bits(3, (M, K))
+    B = synth.normal_bf16_bits(1003, (N, K))
+    ref = O.gemm_bf16(A, B).astype(np.float64)
+    got = ctx.gemm_bf16_host(A, B)
+    assert _bf16_err(got, ref) <= BF16_TOL
+    dA = _dev(A.view(np.int16)).view(torch.bfloat16)
+    dB = _dev(B.view(np.int16)).view(torch.bfloat16)
+    got_dev = ctx.gemm_bf16(dA, dB).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got_dev, got)
+
+
+def test_gemm_bf16_8192_sampled(ctx):
+    """bf16 8192^3: 64 full rows + 64 full columns + 4096 random elements against the fp32-accumulated
+    oracle, tolerance 1e-2 (abs-or-rel with eps = 1)."""
+    M = N = K = 8192
+    A = synth.normal_bf16_bits(3, (M, K))
+    B = synth.normal_bf16_bits(1003, (N, K))
+    dA = _dev(A.view(np.int16)).view(torch.bfloat16)
+    dB = _dev(B.view(np.int16)).view(torch.bfloat16)
+    C = ctx.gemm_bf16(dA, dB)
+    assert ctx.sync() == 0
+    rng = np.random.default_rng(3)
+    rows = np.sort(rng.choice(M, 64, replace=False))
+    cols = np.sort(rng.choice(N, 64, replace=False))
+    got_rows = C[torch.from_numpy(rows).to(DEV)].view(torch.int16).cpu().numpy().view(np.uint16)
+    assert _bf16_err(got_rows, O.gemm_bf16(A[rows], B).astype(np.float64)) <= BF16_TOL
+    got_cols = C[:, torch.from_numpy(cols).to(DEV)].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    assert _bf16_err(got_cols, O.gemm_bf16(A, B[cols]).astype(np.float64)) <= BF16_TOL
+    ii, jj = rng.integers(0, M, 4096), rng.integers(0, N, 4096)
+    a32 = synth.bf16_bits_to_f32(A[ii]).astype(np.float64)
+    b32 = synth.bf16_bits_to_f32(B[jj]).astype(np.float64)
+    ref = np.einsum("ik,ik->i", a32, b32)
+    got = C[torch.from_numpy(ii).to(DEV), torch.from_numpy(jj).to(DEV)].float().cpu().numpy().astype(np.float64)
+    assert float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0))) <= BF16_TOL

@@ -1,0 +1,164 @@
+"""Parity of the CUDA GEMM path with the CPU oracle, through the C ABI.  Integer results are
+compared bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from aiehlc_b200 import _capi, synth
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+# ---------------------------------------------------------------- the reference's own kernel (int32)
+def test_perf_fixture_matches_reference_output(ctx, golden):
+    packed = np.arange(1, 513, dtype=np.int32)                      # example/perf/aieml_perf.cc:141-144
+    got = ctx.mm_i32(_dev(packed), 16, 16, 16).cpu().numpy()
+    assert np.array_equal(got.ravel(), np.array(golden["aieml_perf"]["words_read_back"][:256], dtype=np.int32))
+    assert np.array_equal(ctx.mm_i32_host(packed, 16, 16, 16), got)
+
+
+def test_mm_fixtures_known_answers(ctx):
+    c = ctx.mm_i32_host(np.arange(0, 512, dtype=np.int32), 16, 16, 16)    # aieml_mm.cc:137-140
+    assert (c[0, 0], c[0, 15], c[15, 0], c[15, 15], int(c.sum(dtype=np.int64))) == (31960, 60760, 1043800, 1994200, 200366080)
+    c = ctx.mm_i32_host(np.arange(0, 128, dtype=np.int32), 8, 8, 8)       # aieoob.c:83-86
+    assert np.array_equal(c, O.mm_i32(np.arange(0, 128, dtype=np.int32), 8, 8, 8))
+
+
+@pytest.mark.parametrize("shape", [(16, 16, 16), (1, 1, 1), (100, 70, 33), (257, 129, 65)])
+def test_mm_i32_wraparound(ctx, shape):
+    M, N, K = shape
+    rng = np.random.default_rng(7)
+    inp = rng.integers(-2**31, 2**31 - 1, size=(M + N) * K, dtype=np.int64).astype(np.int32)
+    assert np.array_equal(ctx.mm_i32_host(inp, M, N, K), O.mm_i32(inp, M, N, K))
+
+
+# ---------------------------------------------------------------- int8 -> int32
+SHAPES = [(64, 64, 64),            # the single-tile configuration
+          (128, 256, 128), (256, 512, 1024), (1024, 1024, 1024),
+          (1, 1, 16), (1, 16, 1), (130, 70, 48), (300, 200, 400),        # ragged M, N
+          (100, 60, 50), (33, 17, 7), (5, 3, 1),                         # K not a multiple of 16: repack path
+          (127, 255, 4096), (129, 257, 144)]
+
+
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_gemm_i8_i32_matches_oracle(ctx, shape, tile_n):
+    M, N, K = shape
+    A = synth.int8_uniform(1, (M, K))
+    B = synth.int8_uniform(1001, (N, K))
+    ctx.set_tile_n(tile_n)
+    try:
+        got = ctx.gemm_i8_i32(_dev(A), _dev(B)).cpu().numpy()
+    finally:
+        ctx.set_tile_n(0)
+    assert ctx.sync() == 0
+    assert np.array_equal(got, O.gemm_i8_i32(A, B))
+
+
+def test_extreme_values_and_host_entry_point(ctx):
+    M, N, K = 192, 160, 8192                                            # |acc| reaches 2^27
+    A = np.full((M, K), -128, np.int8)
+    B = np.full((N, K), -128, np.int8)
+    B[::2] = 127
+    assert np.array_equal(ctx.gemm_i8_i32_host(A, B), O.gemm_i8_i32(A, B))
+
+
+def test_empty_and_zero_sizes(ctx):
+    e = torch.empty((0, 64), dtype=torch.int8, device=DEV)
+    b = _dev(synth.int8_uniform(1, (32, 64)))
+    assert ctx.gemm_i8_i32(e, b).shape == (0, 32)
+    a0 = torch.empty((8, 0), dtype=torch.int8, device=DEV)
+    b0 = torch.empty((4, 0), dtype=torch.int8, device=DEV)
+    assert not ctx.gemm_i8_i32(a0, b0).any()                             # empty contraction: zeros
+    assert not ctx.gemm_i8_srs(a0, b0, shift=3).any()
+    with pytest.raises(_capi.AiehlcError):
+        ctx.gemm_i8_srs(b, b, shift=32)
+    with pytest.raises(_capi.AiehlcError):
+        ctx.gemm_i8_srs(b, b, shift=1, splitk=7)                         # 7 does not divide 64
+    with pytest.raises(ValueError):
+        ctx.gemm_i8_i32(b, _dev(synth.int8_uniform(1, (32, 48))))
+
+
+# ---------------------------------------------------------------- srs epilogue, split-K, cascade
+@pytest.mark.parametrize("shape,shift", [((256, 256, 256), 8), ((300, 200, 400), 6), ((512, 384, 1024), 0),
+                                         ((128, 128, 2048), 12), ((64, 48, 80), 1), ((96, 80, 72), 31)])
+def test_gemm_i8_srs_matches_oracle(ctx, shape, shift):
+    M, N, K = shape
+    A = synth.int8_uniform(2, (M, K))
+    B = synth.int8_uniform(1002, (N, K))
+    exp = O.gemm_i8_srs(A, B, shift=shift)
+    assert np.array_equal(ctx.gemm_i8_srs(_dev(A), _dev(B), shift=shift).cpu().numpy(), exp)
+    assert np.array_equal(ctx.gemm_i8_srs_host(A, B, shift=shift), exp)
+    sv = ((np.arange(N) * 7) % 13).astype(np.uint8)
+    assert np.array_equal(ctx.gemm_i8_srs(_dev(A), _dev(B), shift_vec=_dev(sv)).cpu().numpy(),
+                          O.gemm_i8_srs(A, B, shift_vec=sv))
+    assert np.array_equal(ctx.gemm_i8_srs_host(A, B, shift_vec=sv), O.gemm_i8_srs(A, B, shift_vec=sv))
+
+
+def test_srs_rounding_ties_through_the_kernel(ctx):
+    # rows of A select one value per row: C[i][j] = a_i * b_j with K = 16 -> products hit exact .5 ties
+    K = 16
+    A = np.zeros((128, K), np.int8)
+    B = np.zeros((128, K), np.int8)
+    A[:, 0] = np.arange(-64, 64)
+    B[:, 0] = np.arange(-64, 64)[::-1]
+    for s in (1, 2, 3, 7):
+        assert np.array_equal(ctx.gemm_i8_srs_host(A, B, shift=s), O.gemm_i8_srs(A, B, shift=s))
+
+
+@pytest.mark.parametrize("splitk", [1, 2, 4, 8])
+def test_split_k_in_one_launch_and_as_cascade(ctx, splitk):
+    M, N, K = 384, 320, 1024
+    A = synth.int8_uniform(2, (M, K))
+    B = synth.int8_uniform(1002, (N, K))
+    unsplit = O.gemm_i8_srs(A, B, shift=8)
+    assert np.array_equal(O.gemm_i8_srs(A, B, shift=8, splitk=splitk), unsplit)
+    dA, dB = _dev(A), _dev(B)
+    assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift=8, splitk=splitk).cpu().numpy(), unsplit)
+    assert np.array_equal(ctx.gemm_i8_srs_cascade(dA, dB, splitk, shift=8).cpu().numpy(), unsplit)
+
+
+def test_accumulate_and_flush(ctx):
+    M, N, K = 200, 136, 512
+    A = synth.int8_uniform(2, (M, K))
+    B = synth.int8_uniform(1002, (N, K))
+    acc = ctx.gemm_i8_i32(_dev(A[:, :256].copy()), _dev(B[:, :256].copy()))
+    ctx.gemm_i8_i32(_dev(A[:, 256:].copy()), _dev(B[:, 256:].copy()), out=acc, accumulate=True)
+    assert np.array_equal(acc.cpu().numpy(), O.gemm_i8_i32(A, B))
+    sv = ((np.arange(N) * 3) % 9).astype(np.uint8)
+    assert np.array_equal(ctx.srs_i32_i8(acc, shift=5).cpu().numpy(), O.gemm_i8_srs(A, B, shift=5))
+    assert np.array_equal(ctx.srs_i32_i8(acc, shift_vec=_dev(sv)).cpu().numpy(), O.gemm_i8_srs(A, B, shift_vec=sv))
+
+
+# ---------------------------------------------------------------- full benchmark size
+def test_cfg2_full_size_properties_and_sampled_rows(ctx):
+    """int8 4096^3, srs shift 8, split-K 4: sampled rows bit-exact against the oracle, the whole
+    matrix checked through size-independent properties."""
+    M = N = K = 4096
+    dA = synth.int8_uniform_torch(2, (M, K), DEV)
+    dB = synth.int8_uniform_torch(1002, (N, K), DEV)
+    c8 = ctx.gemm_i8_srs(dA, dB, shift=8, splitk=4)
+    c32 = ctx.gemm_i8_i32(dA, dB)
+    assert ctx.sync() == 0
+    # (1) sampled rows, full width, against the oracle
+    rows = np.r_[0:64, 2037:2101, 4032:4096]
+    A_rows = synth.int8_uniform(2, (M, K))[rows]
+    B = synth.int8_uniform(1002, (N, K))
+    assert np.array_equal(c32[torch.from_numpy(rows).to(DEV)].cpu().numpy(), O.gemm_i8_i32(A_rows, B))
+    assert np.array_equal(c8[torch.from_numpy(rows).to(DEV)].cpu().numpy(), O.gemm_i8_srs(A_rows, B, shift=8, splitk=4))
+    # (2) the epilogue is consistent with the int32 result everywhere: srs(C32) == C8
+    assert torch.equal(ctx.srs_i32_i8(c32, shift=8), c8)
+    # (3) checksum of checksums: sum_j C[i][j] == A[i] . (sum_j B[j]) for every row i (exact in int64)
+    colsum = dB.to(torch.float64).sum(dim=0)
+    assert torch.equal(c32.to(torch.float64).sum(dim=1), dA.to(torch.float64) @ colsum)
+    # (4) linearity in A: C(A with rows negated) == -C
+    neg = ctx.gemm_i8_i32((-dA.clamp(min=-127)).contiguous(), dB)
+    assert torch.equal(neg, -ctx.gemm_i8_i32(dA.clamp(min=-127).contiguous(), dB))
+    # (5) cascade over 4 launches equals the single launch
+    assert torch.equal(ctx.gemm_i8_srs_cascade(dA, dB, 4, shift=8), c8)

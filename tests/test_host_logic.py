@@ -1,0 +1,108 @@
+"""Host-side logic that needs no GPU: seeded inputs, sharding, and the 2-rank split-K exchange on gloo."""
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from aiehlc_b200 import shard, synth
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_synth_is_counter_based_and_matches_its_torch_twin():
+    a = synth.int8_uniform(5, (8, 32))
+    assert np.array_equal(a[3:5], synth.int8_uniform(5, (2, 32), start=3 * 32))   # any shard on its own
+    t = synth.int8_uniform_torch(5, (8, 32), "cpu")
+    assert np.array_equal(t.numpy(), a)
+    big = synth.int8_uniform(7, (256, 1024))
+    assert big.min() == -128 and big.max() == 127 and abs(float(big.mean())) < 1.0
+    x = synth.normal_f32(3, (512, 512))
+    assert abs(float(x.mean())) < 0.01 and abs(float(x.std()) - 1.0) < 0.01
+
+
+def test_bf16_rounding_is_nearest_even():
+    import torch
+    x = synth.normal_f32(9, (4096,))
+    assert np.array_equal(synth.f32_to_bf16_bits(x), torch.from_numpy(x).bfloat16().view(torch.int16).numpy().view(np.uint16))
+    assert np.array_equal(synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(x)), torch.from_numpy(x).bfloat16().float().numpy())
+
+
+@pytest.mark.parametrize("m,world", [(65536, 8), (65536, 1), (4096, 2), (10, 4), (3, 4), (0, 2)])
+def test_row_shards_cover_m_exactly(m, world):
+    spans = [shard.row_shard(m, world, r) for r in range(world)]
+    assert spans[0][0] == 0 and sum(n for _, n in spans) == m
+    for (f0, n0), (f1, _) in zip(spans, spans[1:]):
+        assert f0 + n0 == f1
+    assert max(n for _, n in spans) - min(n for _, n in spans) <= 1
+
+
+def test_k_slices():
+    assert [list(shard.k_slices(8, 2, r)) for r in range(2)] == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert shard.k_range(8192, 8, 8, 3) == (3072, 1024)
+    assert shard.k_range(8192, 8, 2, 1) == (4096, 4096)
+    with pytest.raises(ValueError):
+        shard.k_slices(8, 3, 0)
+    with pytest.raises(ValueError):
+        shard.row_shard(8, 2, 2)
+
+
+_WORKER = textwrap.dedent("""
+    import os, sys
+    import numpy as np, torch, torch.distributed as dist
+    sys.path.insert(0, os.environ["AIEHLC_ROOT"])
+    from aiehlc_b200 import shard, synth
+    from oracle import oracle as O
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    M, N, K, splitk = 64, 48, 256, 8
+    A = synth.int8_uniform(5, (M, K)); B = synth.int8_uniform(1005, (N, K))
+    full = O.gemm_i8_i32(A, B)
+    # row-sharded: every rank computes its rows only, no exchange; the gather is for the check
+    r0, nr = shard.row_shard(M, world, rank)
+    mine = torch.from_numpy(O.gemm_i8_i32(A[r0:r0 + nr], B))
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    assert np.array_equal(torch.cat(parts).numpy(), full)
+    # split-K: rank-local partial over its K slices, then one reduce-scatter of int32 partials
+    k0, nk = shard.k_range(K, splitk, world, rank)
+    partial = torch.from_numpy(O.gemm_i8_i32(A[:, k0:k0 + nk], B[:, k0:k0 + nk]))
+    out = torch.empty((M // world, N), dtype=torch.int32)
+    chunks = list(partial.chunk(world, dim=0))
+    dist.reduce_scatter(out, chunks, op=dist.ReduceOp.SUM) if dist.get_backend() != "gloo" else None
+    if dist.get_backend() == "gloo":   # gloo has no reduce_scatter: all_reduce then keep the own row block
+        dist.all_reduce(partial, op=dist.ReduceOp.SUM)
+        out = partial[rank * (M // world):(rank + 1) * (M // world)]
+    assert np.array_equal(out.numpy(), full[rank * (M // world):(rank + 1) * (M // world)])
+    dist.barrier()
+    dist.destroy_process_group()
+    print("rank", rank, "ok")
+""")
+
+
+def test_two_rank_sharding_on_gloo(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, AIEHLC_ROOT=str(ROOT), OMP_NUM_THREADS="2")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+                         capture_output=True, text=True, env=env, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert res.stdout.count("ok") == 2
+
+
+def test_reference_arm_prints_one_json_line():
+    import json
+    res = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "2", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "TOPS" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0

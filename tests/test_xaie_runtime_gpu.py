@@ -1,0 +1,197 @@
+"""The XAie_* run-time surface on the GPU: the reference's own host programs (compiled unmodified
+against libaiehlc_b200.so), this repository's C++ examples, and failure paths driven through
+ctypes.  No test here faults, traps or hangs the GPU: failures are made on the host."""
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from aiehlc_b200 import _capi, build, synth
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+REF = ROOT / "oracle" / "_ref"
+
+
+# ------------------------------------------------------------------ compiled programs
+@pytest.mark.parametrize("name,expect,count", [
+    ("aieml_perf_b200", "CPU result matches vmem_out.", 1),
+    ("multi_tile_b200", "Sucess: CPU result matches AIE.", 1),
+    ("seq_full_col_b200", "Sucess: CPU result matches AIE.", 1),
+    ("multi_kernel_b200", "Sucess: CPU result matches AIE.", 2),
+    ("tutorial_example_b200", "Sucess: CPU result matches AIE.", 1),
+])
+def test_unmodified_reference_host_program_on_b200(name, expect, count):
+    """aiehlc's example sources, compiled as they are plus a binding file (examples/bindings/), pass
+    their own in-file checks when the run-time underneath is this library."""
+    exe = REF / name
+    if not exe.exists():
+        pytest.skip("oracle/_ref was not built (needs the aiehlc source tree at build time)")
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert res.stdout.count(expect) == count, res.stdout[-2000:] + res.stderr[-2000:]
+    assert "Mismatch" not in res.stdout and "mismatches." not in res.stdout
+
+
+def test_cpp_examples():
+    exes = {p.name: p for p in build.build_examples()}
+    res = subprocess.run([str(exes["perf_host"])], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "CPU result matches vmem_out." in res.stdout, res.stdout + res.stderr
+    assert "C[0]=36312 C[255]=2006232" in res.stdout
+    for argv in ([], ["300", "200", "400", "6"], ["128", "64", "64", "0"]):
+        res = subprocess.run([str(exes["cascade_gemm"]), *argv], capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0 and "CPU result matches device output." in res.stdout, res.stdout + res.stderr
+        assert "kernel launches: 4" in res.stdout
+
+
+# ------------------------------------------------------------------ the same surface through ctypes
+class Loc(C.Structure):
+    _fields_ = [("Row", C.c_uint8), ("Col", C.c_uint8)]
+
+
+class Backend(C.Structure):
+    _fields_ = [("Type", C.c_int)]
+
+
+class Config(C.Structure):
+    _fields_ = [("AieGen", C.c_uint8), ("BaseAddr", C.c_uint64), ("ColShift", C.c_uint8), ("RowShift", C.c_uint8),
+                ("NumRows", C.c_uint8), ("NumCols", C.c_uint8), ("ShimRowNum", C.c_uint8),
+                ("MemTileRowStart", C.c_uint8), ("MemTileNumRows", C.c_uint8), ("AieTileRowStart", C.c_uint8),
+                ("AieTileNumRows", C.c_uint8)]
+
+
+class DevInst(C.Structure):
+    _fields_ = [("Cfg", Config), ("IsReady", C.c_uint8), ("StartCol", C.c_uint8), ("PartNumCols", C.c_uint8),
+                ("PartBaseAddr", C.c_uint64), ("Backend", C.POINTER(Backend)), ("BackendStorage", Backend),
+                ("Priv", C.c_void_p)]
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("M", "N", "K", "shift", "has_shift_vec", "splitk", "accumulate", "use_acc")]
+
+
+class MmArgs(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("M", "N", "K")]
+
+
+XAIE_OK, XAIE_INVALID_ELF, XAIE_CORE_STATUS_TIMEOUT = 0, 5, 6
+
+
+@pytest.fixture()
+def xaie():
+    lib = _capi.load()
+    vp, u32, u64 = C.c_void_p, C.c_uint32, C.c_uint64
+    sig = {
+        "XAie_CfgInitialize": (C.c_int, [C.POINTER(DevInst), C.POINTER(Config)]),
+        "XAie_PartitionTeardown": (C.c_int, [C.POINTER(DevInst)]),
+        "XAie_LoadElfMem": (C.c_int, [C.POINTER(DevInst), Loc, vp]),
+        "XAie_KernelSetArgs": (C.c_int, [C.POINTER(DevInst), Loc, vp, u32]),
+        "XAie_MemAllocate": (vp, [C.POINTER(DevInst), u64, C.c_int]),
+        "XAie_MemGetVAddr": (vp, [vp]),
+        "XAie_MemGetDevAddr": (u64, [vp]),
+        "XAie_InitRoutingHandler": (vp, [C.POINTER(DevInst)]),
+        "XAie_Route": (C.c_int, [vp, vp, Loc, Loc]),
+        "XAie_MoveDataExternal2Aie": (C.c_int, [vp, Loc, vp, u32, u32, Loc]),
+        "XAie_MoveDataAie2External": (C.c_int, [vp, Loc, u32, u32, vp, Loc]),
+        "XAie_Run": (C.c_int, [vp, u32]),
+        "XAie_CoreWaitForDone": (C.c_int, [C.POINTER(DevInst), Loc, u32]),
+        "XAie_CoreGetStatus": (C.c_int, [C.POINTER(DevInst), Loc, C.POINTER(u32)]),
+        "XAie_DataMemBlockRead": (C.c_int, [C.POINTER(DevInst), Loc, u64, vp, u32]),
+        "XAie_DataMemBlockWrite": (C.c_int, [C.POINTER(DevInst), Loc, u64, vp, u32]),
+        "XAie_DebugInjectStatus": (C.c_int, [C.POINTER(DevInst), u32, u32]),
+        "XAie_LastError": (C.c_char_p, []),
+        "XAie_LaunchCount": (u64, [C.POINTER(DevInst)]),
+        "aiehlc_window_offset_b": (u64, [vp, u32]),
+    }
+    for n, (r, a) in sig.items():
+        getattr(lib, n).restype = r
+        getattr(lib, n).argtypes = a
+    dev = DevInst()
+    cfg = Config(2, 0x20000000000, 25, 20, 11, 38, 0, 1, 2, 3, 8)
+    assert lib.XAie_CfgInitialize(C.byref(dev), C.byref(cfg)) == XAIE_OK, lib.XAie_LastError()
+    yield lib, dev
+    assert lib.XAie_PartitionTeardown(C.byref(dev)) == XAIE_OK
+
+
+def _kernel(lib, name):
+    return C.cast(getattr(lib, name), C.c_void_p)
+
+
+def _host_array(lib, mem, nbytes, dtype):
+    addr = lib.XAie_MemGetVAddr(mem)
+    return np.ctypeslib.as_array((C.c_uint8 * nbytes).from_address(addr)).view(dtype)
+
+
+def test_gmio_buffers_sit_below_4gib(xaie):
+    lib, dev = xaie
+    mem = lib.XAie_MemAllocate(C.byref(dev), 4096, 0)
+    assert mem and lib.XAie_MemGetDevAddr(mem) == lib.XAie_MemGetVAddr(mem) < 2**32
+    assert lib.XAie_MemAllocate(C.byref(dev), 0, 0) is None
+
+
+def test_int8_gemm_srs_through_the_runtime_matches_oracle(xaie):
+    lib, dev = xaie
+    M, N, K = 200, 136, 320
+    A = synth.int8_uniform(2, (M, K))
+    B = synth.int8_uniform(1002, (N, K))
+    tile, shim = Loc(4, 4), Loc(0, 2)
+    assert lib.XAie_LoadElfMem(C.byref(dev), tile, _kernel(lib, "aiehlc_k_gemm_i8_srs")) == XAIE_OK
+    args = GemmArgs(M, N, K, 7, 0, 4, 0, 0)
+    assert lib.XAie_KernelSetArgs(C.byref(dev), tile, C.byref(args), C.sizeof(args)) == XAIE_OK
+    ri = lib.XAie_InitRoutingHandler(C.byref(dev))
+    assert lib.XAie_Route(ri, None, shim, tile) == XAIE_OK and lib.XAie_Route(ri, None, tile, shim) == XAIE_OK
+    off_b = lib.aiehlc_window_offset_b(C.byref(args), 1)
+    win = off_b + N * K
+    mem_in = lib.XAie_MemAllocate(C.byref(dev), win, 0)
+    mem_out = lib.XAie_MemAllocate(C.byref(dev), M * N, 0)
+    buf = _host_array(lib, mem_in, win, np.int8)
+    buf[:M * K] = A.ravel()
+    buf[off_b:off_b + N * K] = B.ravel()
+    assert lib.XAie_CoreWaitForDone(C.byref(dev), tile, 0) == XAIE_CORE_STATUS_TIMEOUT      # wait before run
+    assert lib.XAie_MoveDataExternal2Aie(ri, shim, mem_in, win, 0x1000, tile) == XAIE_OK
+    assert lib.XAie_Run(ri, 1) == XAIE_OK, lib.XAie_LastError()
+    assert lib.XAie_CoreWaitForDone(C.byref(dev), tile, 5_000_000) == XAIE_OK, lib.XAie_LastError()
+    assert lib.XAie_MoveDataAie2External(ri, tile, 0x6000, M * N, mem_out, shim) == XAIE_OK
+    got = _host_array(lib, mem_out, M * N, np.int8).reshape(M, N)
+    assert np.array_equal(got, O.gemm_i8_srs(A, B, shift=7, splitk=4))
+    assert lib.XAie_LaunchCount(C.byref(dev)) == 1
+    # debug peek of the result window agrees with the DMA path
+    peek = np.empty(64, np.int8)
+    assert lib.XAie_DataMemBlockRead(C.byref(dev), tile, 0x6000, peek.ctypes.data, 64) == XAIE_OK
+    assert np.array_equal(peek, got.ravel()[:64])
+
+
+def test_failure_paths_return_codes(xaie):
+    lib, dev = xaie
+    tile, shim, other = Loc(4, 4), Loc(0, 2), Loc(5, 5)
+    # unknown kernel symbol
+    bogus = C.c_int(0)
+    assert lib.XAie_LoadElfMem(C.byref(dev), tile, C.cast(C.byref(bogus), C.c_void_p)) == XAIE_INVALID_ELF
+    assert b"not a registered kernel" in lib.XAie_LastError()
+    assert lib.XAie_LoadElfMem(C.byref(dev), shim, _kernel(lib, "aiehlc_k_mm_i32")) != XAIE_OK   # shim row
+    assert lib.XAie_LoadElfMem(C.byref(dev), Loc(200, 4), _kernel(lib, "aiehlc_k_mm_i32")) != XAIE_OK
+    ri = lib.XAie_InitRoutingHandler(C.byref(dev))
+    assert lib.XAie_Run(ri, 1) != XAIE_OK                                     # nothing loaded
+    assert lib.XAie_LoadElfMem(C.byref(dev), tile, _kernel(lib, "aiehlc_k_mm_i32")) == XAIE_OK
+    lib.XAie_Route(ri, None, shim, tile)
+    mem = lib.XAie_MemAllocate(C.byref(dev), 2048, 0)
+    assert lib.XAie_MoveDataExternal2Aie(ri, shim, mem, 4096, 0x1000, tile) != XAIE_OK     # larger than the buffer
+    assert lib.XAie_MoveDataExternal2Aie(ri, shim, mem, 2048, 0x1000, other) != XAIE_OK    # no such route
+    assert lib.XAie_MoveDataAie2External(ri, tile, 0x6000, 1024, mem, shim) != XAIE_OK     # no route back
+    # input window too short for the kernel's arguments: the launch is refused on the host
+    args = MmArgs(64, 64, 64)
+    lib.XAie_KernelSetArgs(C.byref(dev), tile, C.byref(args), C.sizeof(args))
+    assert lib.XAie_MoveDataExternal2Aie(ri, shim, mem, 2048, 0x1000, tile) == XAIE_OK
+    assert lib.XAie_Run(ri, 1) != XAIE_OK and b"input window" in lib.XAie_LastError()
+    # an injected device status surfaces once at the completion poll, then the poll reports done
+    args = MmArgs(16, 16, 16)
+    lib.XAie_KernelSetArgs(C.byref(dev), tile, C.byref(args), C.sizeof(args))
+    assert lib.XAie_Run(ri, 1) == XAIE_OK
+    lib.XAie_DebugInjectStatus(C.byref(dev), 104, 1)
+    assert lib.XAie_CoreWaitForDone(C.byref(dev), tile, 0) not in (XAIE_OK, XAIE_CORE_STATUS_TIMEOUT)
+    assert lib.XAie_CoreWaitForDone(C.byref(dev), tile, 5_000_000) == XAIE_OK
+    st = C.c_uint32(9)
+    assert lib.XAie_CoreGetStatus(C.byref(dev), Loc(4, 4), C.byref(st)) == XAIE_OK and st.value == 1
+    assert lib.XAie_CoreGetStatus(C.byref(dev), Loc(1, 4), C.byref(st)) == XAIE_OK and st.value == 0
