@@ -128,6 +128,26 @@ int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n) {
   return AIEHLC_OK;
 }
 
+int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (mode < -1 || mode > 1) return fail(AIEHLC_ERR_INVALID, "pair mode must be -1, 0 or 1");
+  ctx->pair_mode = mode;
+  return AIEHLC_OK;
+}
+
+int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->trace = device_buffer;
+  return AIEHLC_OK;
+}
+
+int aiehlc_set_debug(aiehlc_ctx* ctx, int mode) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (mode < 0 || mode > 2) return fail(AIEHLC_ERR_INVALID, "debug mode must be 0, 1 or 2");
+  ctx->debug_mode = mode;
+  return AIEHLC_OK;
+}
+
 int aiehlc_sync(aiehlc_ctx* ctx, void* stream, int* status) {
   int rc = check_ctx(ctx);
   if (rc) return rc;

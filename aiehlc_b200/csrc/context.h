@@ -44,6 +44,9 @@ struct aiehlc_ctx {
   int* h_status = nullptr;      // pinned mirror
   aiehlc::EncodeTiledFn encode = nullptr;
   int force_tile_n = 0;
+  int pair_mode = -1;           // -1: choose per shape, 0: single-CTA tiles only, 1: CTA pairs wherever M > 128
+  int debug_mode = 0;           // see GemmParams::debug
+  long long* trace = nullptr;   // see GemmParams::trace (device pointer owned by the caller)
   long long launches = 0;
   // staging for *_host entry points and for operands that TMA cannot address directly
   aiehlc::DevBuf buf_a, buf_b, buf_c, buf_aux, pack_a, pack_b;

@@ -4,6 +4,7 @@
 
 #include "context.h"
 #include "gemm_tcgen05.cuh"
+#include "gemm_tcgen05_pair.cuh"
 
 namespace aiehlc {
 
@@ -31,22 +32,34 @@ int encode_kmajor_map(aiehlc_ctx* ctx, CUtensorMap* map, int kind, const void* b
   return AIEHLC_OK;
 }
 
-// Tile-N choice: fewest "tile-time units" over whole waves of `sms` persistent CTAs.  Narrow
-// tiles re-read A from shared memory more often per MMA, hence the efficiency factors.
-int choose_tile_n(int M, int N, int sms) {
+// Tile choice: fewest "tile-time units" over whole waves of persistent CTAs (or CTA pairs).
+// A narrow tile fetches more operand bytes per MMA and the kernels are bound by the shared-memory
+// feed, hence the efficiency factors (measured on int8 4096^3: N = 256 / 128 / 64 tiles take
+// 56.8 / 82.0 / 143.9 us).  A CTA pair does the work of two single-CTA tiles with two thirds of
+// the operand traffic per SM (measured on int8 8192^3: 373 us against 391 us).
+struct TileChoice { int bn; bool pair; };
+TileChoice choose_tile(int M, int N, int sms, int force_bn, int pair_mode) {
   const int cand[3] = {256, 128, 64};
-  const double eff[3] = {1.0, 0.90, 0.60};
-  const long long mblocks = (M + kBlockM - 1) / kBlockM;
-  double best = 0;
-  int best_bn = 64;
-  for (int i = 0; i < 3; ++i) {
-    const int bn = cand[i];
-    const long long tiles = mblocks * ((N + bn - 1) / bn);
-    const long long waves = (tiles + sms - 1) / sms;
-    const double cost = static_cast<double>(waves) * bn / eff[i];
-    if (i == 0 || cost < best) { best = cost; best_bn = bn; }
+  const double eff[3] = {1.0, 0.60, 0.35};
+  TileChoice best{256, false};
+  double best_cost = -1;
+  for (int pr = 0; pr < 2; ++pr) {
+    if (pr == 1 && pair_mode == 0) continue;      // pairs switched off
+    if (pr == 0 && pair_mode == 1 && M > kBlockM) continue;  // pairs forced where they apply
+    for (int i = 0; i < 3; ++i) {
+      const int bn = cand[i];
+      if (force_bn && bn != force_bn) continue;
+      if (pr == 1 && bn == 64) continue;
+      const long long mblocks = pr ? (M + kPairM - 1) / kPairM : (M + kBlockM - 1) / kBlockM;
+      const long long tiles = mblocks * ((N + bn - 1) / bn);
+      const long long slots = pr ? sms / 2 : sms;
+      const long long waves = (tiles + slots - 1) / slots;
+      // rows of the last row-block that fall outside M are computed all the same
+      const double cost = static_cast<double>(waves) * bn / eff[i] * (pr ? 0.97 : 1.0);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = TileChoice{bn, pr == 1}; }
+    }
   }
-  return best_bn;
+  return best;
 }
 
 template <int kKind, int kBN, int kEpi>
@@ -65,6 +78,8 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.C = c.C; p.ldc = c.ldc;
   p.acc_in = c.acc_in; p.ld_acc = c.ld_acc;
   p.shift_vec = c.shift_vec; p.shift = c.shift;
+  // 32-bit rounding needs |acc| + 2^shift < 2^31; |acc| <= K * 2^14 unless partial sums are added
+  p.srs_wide = (c.acc_in != nullptr || c.K > 32768 || c.shift > 29) ? 1 : 0;
   p.num_m_blocks = (c.M + kBlockM - 1) / kBlockM;
   p.num_n_blocks = (c.N + kBN - 1) / kBN;
   p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
@@ -73,6 +88,8 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   bool vec = (reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0);
   p.vec_ok = vec ? 1 : 0;
   p.status = ctx->d_status;
+  p.debug = ctx->debug_mode;
+  p.trace = ctx->trace;
 
   auto kern = gemm_tn_kernel<kKind, kBN, kEpi>;
   // Per device and cheap, so simply repeated on every launch.
@@ -85,8 +102,69 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   return AIEHLC_OK;
 }
 
+
+// CTA-pair kernel: a 1-D grid of 2-CTA clusters, one cluster per 256 x kBN tile in flight.
+template <int kKind, int kBN, int kEpi>
+int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
+  using S = PairSmem<kBN>;
+  CUtensorMap ma, mb;
+  int rc = encode_kmajor_map(ctx, &ma, kKind, c.A, c.M, c.K, c.lda, kBlockM);
+  if (rc) return rc;
+  rc = encode_kmajor_map(ctx, &mb, kKind, c.B, c.N, c.K, c.ldb, kBN / 2);
+  if (rc) return rc;
+
+  const int esize = kKind == KIND_I8 ? 1 : 2;
+  const int cesize = kEpi == EPI_I8_SRS ? 1 : (kEpi == EPI_BF16 ? 2 : 4);
+  GemmParams p{};
+  p.M = c.M; p.N = c.N; p.K = c.K;
+  p.C = c.C; p.ldc = c.ldc;
+  p.acc_in = c.acc_in; p.ld_acc = c.ld_acc;
+  p.shift_vec = c.shift_vec; p.shift = c.shift;
+  // 32-bit rounding needs |acc| + 2^shift < 2^31; |acc| <= K * 2^14 unless partial sums are added
+  p.srs_wide = (c.acc_in != nullptr || c.K > 32768 || c.shift > 29) ? 1 : 0;
+  p.num_m_blocks = (c.M + kPairM - 1) / kPairM;
+  p.num_n_blocks = (c.N + kBN - 1) / kBN;
+  p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
+  p.group_m = 4;
+  p.vec_ok = ((reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0)) ? 1 : 0;
+  p.status = ctx->d_status;
+  p.debug = ctx->debug_mode;
+  p.trace = ctx->trace;
+
+  auto kern = gemm_tn_pair_kernel<kKind, kBN, kEpi>;
+  AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  int max_pairs = ctx->sm_count / 2;
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(2 * max_pairs);
+  int active = 0;
+  if (cudaOccupancyMaxActiveClusters(&active, kern, &cfg) == cudaSuccess && active > 0 && active < max_pairs)
+    max_pairs = active;  // every cluster of the persistent grid must be resident at once
+  else
+    cudaGetLastError();
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cfg.gridDim = dim3(2 * pairs);
+  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
+  ctx->launches++;
+  return AIEHLC_OK;
+}
+
 template <int kKind, int kEpi>
-int dispatch_bn(aiehlc_ctx* ctx, const GemmCall& c, int bn, cudaStream_t st) {
+int dispatch_bn(aiehlc_ctx* ctx, const GemmCall& c, int bn, bool pair, cudaStream_t st) {
+  if (pair) {
+    if (bn == 256) return launch_pair<kKind, 256, kEpi>(ctx, c, st);
+    return launch_pair<kKind, 128, kEpi>(ctx, c, st);
+  }
   switch (bn) {
     case 256: return launch_one<kKind, 256, kEpi>(ctx, c, st);
     case 128: return launch_one<kKind, 128, kEpi>(ctx, c, st);
@@ -122,17 +200,19 @@ int launch_gemm(aiehlc_ctx* ctx, const GemmCall& call, cudaStream_t st) {
     c.B = ctx->pack_b.ptr; c.ldb = ld;
   }
 
-  int bn = ctx->force_tile_n ? ctx->force_tile_n : choose_tile_n(c.M, c.N, ctx->sm_count);
+  const TileChoice tc = choose_tile(c.M, c.N, ctx->sm_count, ctx->force_tile_n, ctx->pair_mode);
+  const int bn = tc.bn;
+  const bool pair = tc.pair;
   if (c.kind == KIND_I8) {
     switch (c.epi) {
-      case EPI_I32: return dispatch_bn<KIND_I8, EPI_I32>(ctx, c, bn, st);
-      case EPI_I32_ACC: return dispatch_bn<KIND_I8, EPI_I32_ACC>(ctx, c, bn, st);
-      case EPI_I8_SRS: return dispatch_bn<KIND_I8, EPI_I8_SRS>(ctx, c, bn, st);
+      case EPI_I32: return dispatch_bn<KIND_I8, EPI_I32>(ctx, c, bn, pair, st);
+      case EPI_I32_ACC: return dispatch_bn<KIND_I8, EPI_I32_ACC>(ctx, c, bn, pair, st);
+      case EPI_I8_SRS: return dispatch_bn<KIND_I8, EPI_I8_SRS>(ctx, c, bn, pair, st);
       default: return fail(AIEHLC_ERR_INVALID, "gemm: bad output stage for int8");
     }
   }
   if (c.epi != EPI_BF16) return fail(AIEHLC_ERR_INVALID, "gemm: bad output stage for bf16");
-  return dispatch_bn<KIND_BF16, EPI_BF16>(ctx, c, bn, st);
+  return dispatch_bn<KIND_BF16, EPI_BF16>(ctx, c, bn, pair, st);
 }
 
 }  // namespace aiehlc

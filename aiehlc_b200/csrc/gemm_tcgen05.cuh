@@ -46,10 +46,13 @@ struct GemmParams {
   long long ld_acc;
   const uint8_t* shift_vec;  // EPI_I8_SRS: optional per-output-column shift
   int shift;                 // EPI_I8_SRS: shift used when shift_vec == nullptr
+  int srs_wide;              // EPI_I8_SRS: |acc| may approach 2^31: round in 64-bit arithmetic
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int group_m;             // rasterisation: tiles walk group_m row-blocks before the next column
   int vec_ok;              // C (and acc_in) rows are 16-byte aligned: vector stores allowed
   int* status;             // device status word (0 = ok)
+  long long* trace;        // measurement aid: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
+  int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling)
 };
 
 // Shift-round-saturate, pure integer: round half to even on the dropped bits, saturate to int8.
@@ -63,6 +66,29 @@ __host__ __device__ __forceinline__ int srs_i8(int acc, int s) {
     if (r > h || (r == h && (q & 1))) q += 1;
   }
   return q > 127 ? 127 : (q < -128 ? -128 : q);
+}
+
+
+// The same rounding without branches, for the epilogue's inner loop:
+//   q = (acc + (2^(s-1) - 1) + bit_s(acc)) >> s        (s >= 1;  q = acc for s = 0)
+// bit_s(acc) is the parity of floor(acc / 2^s), so an exact half rounds to the even neighbour.
+// `hm1` = 2^(s-1) - 1 (0 for s = 0), `bmask` = 1 (0 for s = 0).  The 32-bit form needs
+// |acc| + 2^s < 2^31, which the host checks from K (|acc| <= K * 2^14); otherwise kWide.
+template <bool kWide>
+__device__ __forceinline__ int srs_round(int acc, int s, int hm1, int bmask) {
+  if constexpr (kWide) {
+    const long long t = static_cast<long long>(acc) + hm1 + ((acc >> s) & bmask);
+    return static_cast<int>(t >> s);
+  } else {
+    return (acc + hm1 + ((acc >> s) & bmask)) >> s;
+  }
+}
+// Saturate four 32-bit values to int8 and pack them, e0 in the low byte.
+__device__ __forceinline__ uint32_t pack_sat_s8x4(int e0, int e1, int e2, int e3) {
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(e3), "r"(e2), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(e1), "r"(e0), "r"(hi));
+  return out;
 }
 
 template <int kBN>
@@ -85,6 +111,116 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb,
   const int r = t - g * per_group;
   mb = first_m + r % rows;
   nb = r / rows;
+}
+
+// Output stage for 32 consecutive accumulator columns of one row (the caller has checked that
+// row < M and col0 < N).
+template <int kEpi>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[32], int row, int col0) {
+  const int ncols = min(32, p.N - col0);
+  if constexpr (kEpi == EPI_I32 || kEpi == EPI_I32_ACC) {
+    int32_t* dst = static_cast<int32_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (p.vec_ok && ncols == 32) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        int4 v = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        if constexpr (kEpi == EPI_I32_ACC) {
+          const int4 o = *reinterpret_cast<const int4*>(dst + j);
+          v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+        }
+        *reinterpret_cast<int4*>(dst + j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) {
+          if constexpr (kEpi == EPI_I32_ACC) dst[j] += static_cast<int32_t>(r[j]);
+          else dst[j] = static_cast<int32_t>(r[j]);
+        }
+    }
+  } else if constexpr (kEpi == EPI_I8_SRS) {
+    int8_t* dst = static_cast<int8_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (p.acc_in != nullptr) {
+      const int32_t* ai = p.acc_in + static_cast<long long>(row) * p.ld_acc + col0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) r[j] += static_cast<uint32_t>(ai[j]);
+    }
+    uint32_t packed[8];
+    if (p.shift_vec == nullptr) {
+      const int sh = p.shift;
+      const int hm1 = sh > 0 ? (1 << (sh - 1)) - 1 : 0;
+      const int bmask = sh > 0 ? 1 : 0;
+      if (p.srs_wide) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          packed[j >> 2] = pack_sat_s8x4(srs_round<true>(r[j], sh, hm1, bmask), srs_round<true>(r[j + 1], sh, hm1, bmask),
+                                         srs_round<true>(r[j + 2], sh, hm1, bmask), srs_round<true>(r[j + 3], sh, hm1, bmask));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          packed[j >> 2] = pack_sat_s8x4(srs_round<false>(r[j], sh, hm1, bmask), srs_round<false>(r[j + 1], sh, hm1, bmask),
+                                         srs_round<false>(r[j + 2], sh, hm1, bmask), srs_round<false>(r[j + 3], sh, hm1, bmask));
+      }
+    } else {
+      // per-column shifts: the 32 shift bytes of this chunk are the same for every row
+      int q[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int sh = j < ncols ? static_cast<int>(p.shift_vec[col0 + j]) : 0;
+        const int hm1 = max(static_cast<int>((1u << sh) >> 1) - 1, 0);
+        q[j] = srs_round<true>(r[j], sh, hm1, min(sh, 1));
+      }
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) packed[j >> 2] = pack_sat_s8x4(q[j], q[j + 1], q[j + 2], q[j + 3]);
+    }
+    if (p.vec_ok && ncols == 32) {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) dst[j] = static_cast<int8_t>((packed[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+    }
+  } else {  // EPI_BF16
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    uint32_t packed[16];
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+      packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    if (p.vec_ok && ncols == 32) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) {
+          const uint16_t bits = static_cast<uint16_t>(packed[j >> 1] >> (16 * (j & 1)));
+          reinterpret_cast<uint16_t*>(dst)[j] = bits;
+        }
+    }
+  }
+}
+
+// Drains kBN accumulator columns of this warp's 32 TMEM lanes through the output stage, 64 columns
+// per step: two TMEM loads are issued back to back, then waited for once.
+template <int kBN, int kEpi>
+__device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t taddr, int row, bool row_ok,
+                                                  int n0) {
+  static_assert(kBN % 64 == 0, "accumulator is drained 64 columns at a time");
+#pragma unroll 1
+  for (int c = 0; c < kBN; c += 64) {
+    __syncwarp();  // lanes that skipped stores rejoin before the warp-wide TMEM loads
+    uint32_t ra[32], rb[32];
+    tmem_ld_32x32b_x32(taddr + c, ra);
+    tmem_ld_32x32b_x32(taddr + c + 32, rb);
+    tmem_ld_wait();
+    if (row_ok && n0 + c < p.N) store_chunk<kEpi>(p, ra, row, n0 + c);
+    if (row_ok && n0 + c + 32 < p.N) store_chunk<kEpi>(p, rb, row, n0 + c + 32);
+  }
 }
 
 template <int kKind, int kBN, int kEpi>
@@ -115,6 +251,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+    p.trace[5] = clock64();
+    p.trace[7] = static_cast<long long>(globaltimer_ns());
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -157,6 +297,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                          ST_TIMEOUT_EMPTY);
           if (!ok) break;
           const uint32_t fb = smem_u32(&full_bar[stage]);
+          if (p.debug == 1) {
+            mbar_arrive(fb);
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+            continue;
+          }
           mbar_expect_tx(fb, S::kStageBytes);
           uint8_t* sa = smem + stage * S::kStageBytes;
           uint8_t* sb = sa + S::kABytes;
@@ -188,6 +333,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                        ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
+        if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
@@ -197,16 +343,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t sb = sa + S::kABytes;
           const uint64_t adesc = make_kmajor_desc(sa, 1024, 2);
           const uint64_t bdesc = make_kmajor_desc(sb, 1024, 2);
+          if (p.debug != 2) {
 #pragma unroll
-          for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
-            // K-step inside the swizzle span: advance the start-address field by 32 B (>>4 = 2).
-            umma_ss<kKind, 1>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc,
-                              (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
+              // K-step inside the swizzle span: advance the start-address field by 32 B (>>4 = 2).
+              umma_ss<kKind, 1>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc,
+                                (kb | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(smem_u32(&empty_bar[stage]));  // frees the stage when these MMAs retire
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));
+        if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 1] = clock64();
       }
     }
   } else {
@@ -219,101 +368,22 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tile_coords(t, p, mb, nb);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      const bool tracer = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0;
+      if (tracer) p.trace[it * 8 + 2] = clock64();
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status,
                      ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (tracer) p.trace[it * 8 + 3] = clock64();
       const int row = mb * kBlockM + quad * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
-#pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
-        __syncwarp();  // lanes that skipped the stores of the previous chunk rejoin here
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c, r);
-        tmem_ld_wait();
-        const int col0 = nb * kBN + c;
-        if (!row_ok || col0 >= p.N) continue;
-        const int ncols = min(32, p.N - col0);
-        if constexpr (kEpi == EPI_I32 || kEpi == EPI_I32_ACC) {
-          int32_t* dst = static_cast<int32_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-          if (p.vec_ok && ncols == 32) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              int4 v = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-              if constexpr (kEpi == EPI_I32_ACC) {
-                const int4 o = *reinterpret_cast<const int4*>(dst + j);
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-              }
-              *reinterpret_cast<int4*>(dst + j) = v;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < ncols) {
-                if constexpr (kEpi == EPI_I32_ACC) dst[j] += static_cast<int32_t>(r[j]);
-                else dst[j] = static_cast<int32_t>(r[j]);
-              }
-          }
-        } else if constexpr (kEpi == EPI_I8_SRS) {
-          int8_t* dst = static_cast<int8_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-          if (p.acc_in != nullptr) {
-            const int32_t* ai = p.acc_in + static_cast<long long>(row) * p.ld_acc + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < ncols) r[j] += static_cast<uint32_t>(ai[j]);
-          }
-          uint32_t packed[8];
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            uint32_t w = 0;
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              const int s = (p.shift_vec != nullptr)
-                                ? (j + b < ncols ? static_cast<int>(p.shift_vec[col0 + j + b]) : 0)
-                                : p.shift;
-              w |= (static_cast<uint32_t>(srs_i8(static_cast<int>(r[j + b]), s)) & 0xFFu) << (8 * b);
-            }
-            packed[j >> 2] = w;
-          }
-          if (p.vec_ok && ncols == 32) {
-            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            *reinterpret_cast<uint4*>(dst + 16) =
-                make_uint4(packed[4], packed[5], packed[6], packed[7]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < ncols) dst[j] = static_cast<int8_t>((packed[j >> 2] >> (8 * (j & 3))) & 0xFFu);
-          }
-        } else {  // EPI_BF16
-          __nv_bfloat16* dst =
-              static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-          uint32_t packed[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const __nv_bfloat162 h =
-                __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-            packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-          }
-          if (p.vec_ok && ncols == 32) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              *reinterpret_cast<uint4*>(dst + 2 * j) =
-                  make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < ncols) {
-                const uint16_t bits = static_cast<uint16_t>(packed[j >> 1] >> (16 * (j & 1)));
-                reinterpret_cast<uint16_t*>(dst)[j] = bits;
-              }
-          }
-        }
-      }
+      drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN);
       // Accumulator drained: hand it back to the MMA issuer.
       tc_fence_before();
       __syncwarp();
+      if (tracer) p.trace[it * 8 + 4] = clock64();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
   }
@@ -323,6 +393,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+    p.trace[6] = clock64();
+    p.trace[15] = static_cast<long long>(globaltimer_ns());
   }
 }
 

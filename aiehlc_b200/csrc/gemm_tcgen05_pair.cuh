@@ -1,0 +1,209 @@
+// CTA-pair variant of the tile GEMM (tcgen05 cta_group::2): two CTAs on neighbouring SMs share
+// one 256 x kBN output tile.
+//
+// Why: the single-CTA kernel is bound by the L2 -> shared-memory feed (a 128 x 256 int8 tile needs
+// 96 operand bytes per clock per SM at full MMA rate).  In a pair each CTA fetches its own 128 rows
+// of A and only HALF of the B tile (kBN/2 rows); the tensor cores of both SMs read both B halves
+// across the pair.  The feed drops to 64 bytes per clock per SM with no byte fetched twice.
+//
+//   both CTAs : warp 0 fetches this CTA's A rows and its B half; the byte counts of BOTH CTAs are
+//               credited to the leader's "full" barrier
+//   leader    : warp 1 issues tcgen05.mma.cta_group::2 (M = 256); each CTA's TMEM receives its
+//               128 rows of the accumulator; completion is signalled to both CTAs' barriers
+//   both CTAs : warps 2-5 drain their 128 accumulator rows through the fused output stage and
+//               tell the leader when the accumulator buffer is free
+//
+// The reference's formulation is unchanged: C = A . B^T with A[M][K], B[N][K], all K slices
+// accumulated in TMEM before one flush (example/perf/aieml_perf.cc:199-231; tiling.py:299-333).
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace aiehlc {
+
+constexpr int kPairM = 256;
+
+template <int kBN>
+struct PairSmem {
+  static constexpr int kABytes = kBlockM * kBlockKBytes;           // this CTA's 128 rows of A
+  static constexpr int kBBytes = (kBN / 2) * kBlockKBytes;         // this CTA's half of B
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBudget = 227 * 1024 - 2048;
+  static constexpr int kStagesRaw = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kBarBytes = 512;
+  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;
+};
+
+template <int kKind, int kBN, int kEpi>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+  using S = PairSmem<kBN>;
+  constexpr int kStages = S::kStages;
+  constexpr int kBHalf = kBN / 2;
+  constexpr uint32_t kTmemCols = 2 * kBN;
+  constexpr int kElemBytes = kKind == KIND_I8 ? 1 : 2;
+  constexpr int kBlockKElems = kBlockKBytes / kElemBytes;
+  static_assert(kBN == 128 || kBN == 256, "pair tile N");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* bar_mem = smem + kStages * S::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);   // used in the leader CTA
+  uint64_t* empty_bar = full_bar + kStages;                    // one set per CTA
+  uint64_t* tmem_full_bar = empty_bar + kStages;               // one set per CTA
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;                // used in the leader CTA
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = static_cast<int>(cluster_id_x());
+  const int num_pairs = static_cast<int>(cluster_count_x());
+  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+    p.trace[5] = clock64();
+    p.trace[7] = static_cast<long long>(globaltimer_ns());
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 8);  // 4 epilogue warps in each of the two CTAs
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(smem_u32(tmem_base_slot), kTmemCols);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // the partner's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;  // num_m_blocks counts 256-row blocks
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+        int mb, nb;
+        tile_coords(t, p, mb, nb);
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
+          if (!ok) break;
+          const uint32_t fb_local = smem_u32(&full_bar[stage]);
+          if (p.debug == 1) {
+            if (leader) mbar_arrive(fb_local);
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+            continue;
+          }
+          if (leader) mbar_expect_tx(fb_local, 2 * S::kStageBytes);  // both CTAs' bytes
+          const uint32_t fb = mapa_u32(fb_local, 0);  // the same barrier in the leader CTA
+          uint8_t* sa = smem + stage * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          tma_load_2d_pair(smem_u32(sa), &tmap_a, fb, kb * kBlockKElems,
+                           mb * kPairM + static_cast<int>(rank) * kBlockM);
+          tma_load_2d_pair(smem_u32(sb), &tmap_b, fb, kb * kBlockKElems,
+                           nb * kBN + static_cast<int>(rank) * kBHalf);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok)
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc<kKind>(kPairM, kBN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status,
+                       ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after();
+        if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+          const uint64_t adesc = make_kmajor_desc(sa, 1024, 2);
+          const uint64_t bdesc = make_kmajor_desc(sb, 1024, 2);
+          if (p.debug != 2) {
+#pragma unroll
+            for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
+              umma_ss<kKind, 2>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair_mask(smem_u32(&empty_bar[stage]), 3);  // frees the stage in both CTAs
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair_mask(smem_u32(&tmem_full_bar[acc]), 3);
+        if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 1] = clock64();
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs)
+    const int quad = warp & 3;
+    int it = 0;
+    bool ok = true;
+    for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+      int mb, nb;
+      tile_coords(t, p, mb, nb);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const bool tracer = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0;
+      if (tracer) p.trace[it * 8 + 2] = clock64();
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      if (tracer) p.trace[it * 8 + 3] = clock64();
+      const int row = mb * kPairM + static_cast<int>(rank) * kBlockM + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
+      drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN);
+      tc_fence_before();
+      __syncwarp();
+      if (tracer) p.trace[it * 8 + 4] = clock64();
+      if (lane == 0) mbar_arrive_remote(smem_u32(&tmem_empty_bar[acc]), 0);
+    }
+  }
+
+  // Neither CTA may retire (or free TMEM) while its partner can still read its shared memory,
+  // write its TMEM or signal its barriers.
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<2>(tmem_base, kTmemCols);
+  }
+  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+    p.trace[6] = clock64();
+    p.trace[15] = static_cast<long long>(globaltimer_ns());
+  }
+}
+
+}  // namespace aiehlc

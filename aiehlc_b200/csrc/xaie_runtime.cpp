@@ -130,40 +130,63 @@ struct Runtime {
   }
   Tile& tile(XAie_LocType l) { return tiles[loc_key(l)]; }
 
-  Region* find_region(Tile& t, u64 addr, size_t bytes) {
+  // Tile data memory is a set of WINDOWS, each starting at an address the kernel declares (input,
+  // accumulator, output) or at the first address something was moved to.  An address belongs to
+  // the window with the greatest start at or below it, whatever the sizes: on the AIE a window is a
+  // few KiB, here a GEMM operand window may hold hundreds of MiB, and it must not swallow the
+  // addresses of the windows declared above it.
+  u64 window_start(const Tile& t, u64 addr) const {
+    bool found = false;
+    u64 best = 0;
+    auto consider = [&](u64 s) {
+      if (s <= addr && (!found || s > best)) { best = s; found = true; }
+    };
+    if (t.loaded) {
+      consider(t.kernel.in_addr);
+      consider(t.kernel.out_addr);
+      if (t.kernel.acc_addr) consider(t.kernel.acc_addr);
+    }
+    for (const auto& r : t.regions) consider(r.addr);
+    return found ? best : addr;
+  }
+  Region* find_window(Tile& t, u64 start) {
     for (auto& r : t.regions)
-      if (addr >= r.addr && addr + bytes <= r.addr + r.cap) return &r;
+      if (r.addr == start) return &r;
     return nullptr;
   }
-  // Region that holds [addr, addr+bytes): reuse, grow in place (contents kept) or create.
+  // Existing bytes at [addr, addr+bytes): the window must exist and cover the start address.
+  Region* find_region(Tile& t, u64 addr, size_t bytes) {
+    Region* r = find_window(t, window_start(t, addr));
+    if (!r || addr + (bytes ? 1 : 0) > r->addr + r->cap) return nullptr;
+    return r;
+  }
+  // Window that holds [addr, addr+bytes): reuse, grow (contents kept) or create.
   AieRC ensure_region(Tile& t, u64 addr, size_t bytes, void** dptr) {
     if (bytes == 0) bytes = 1;
-    if (Region* r = find_region(t, addr, bytes)) {
-      *dptr = static_cast<uint8_t*>(r->dptr) + (addr - r->addr);
-      return XAIE_OK;
-    }
-    for (auto& r : t.regions) {
-      if (addr >= r.addr && addr < r.addr + r.cap) {  // starts inside an existing window: grow it
-        const size_t need = static_cast<size_t>(addr - r.addr) + bytes;
+    const u64 start = window_start(t, addr);
+    const size_t need = static_cast<size_t>(addr - start) + bytes;
+    if (Region* r = find_window(t, start)) {
+      if (need > r->cap) {
         void* p = nullptr;
         cudaError_t e = cudaMalloc(&p, need);
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(tile window)");
-        XCUDA(cudaMemcpyAsync(p, r.dptr, r.cap, cudaMemcpyDeviceToDevice, stream));
+        XCUDA(cudaMemcpyAsync(p, r->dptr, r->cap, cudaMemcpyDeviceToDevice, stream));
         XCUDA(cudaStreamSynchronize(stream));
-        cudaFree(r.dptr);
-        r.dptr = p;
-        r.cap = need;
-        *dptr = static_cast<uint8_t*>(p) + (addr - r.addr);
-        return XAIE_OK;
+        cudaFree(r->dptr);
+        r->dptr = p;
+        r->cap = need;
       }
+      *dptr = static_cast<uint8_t*>(r->dptr) + (addr - start);
+      return XAIE_OK;
     }
     Region r;
-    r.addr = addr;
-    r.cap = bytes;
-    cudaError_t e = cudaMalloc(&r.dptr, bytes);
+    r.addr = start;
+    r.cap = need;
+    cudaError_t e = cudaMalloc(&r.dptr, need);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(tile window)");
+    if (start != addr) XCUDA(cudaMemsetAsync(r.dptr, 0, need, stream));
     t.regions.push_back(r);
-    *dptr = r.dptr;
+    *dptr = static_cast<uint8_t*>(r.dptr) + (addr - start);
     return XAIE_OK;
   }
 };
@@ -205,7 +228,7 @@ AieRC h2t(Runtime* rt, XAie_LocType dst, u64 tile_addr, const void* src, size_t 
 AieRC t2h(Runtime* rt, XAie_LocType src, u64 tile_addr, void* dst, size_t bytes) {
   if (!rt->valid_loc(src) || rt->is_shim(src)) return fail(XAIE_INVALID_TILE, "source is not a tile");
   Tile& t = rt->tile(src);
-  Region* r = rt->find_region(t, tile_addr, bytes ? 1 : 0);
+  Region* r = rt->find_region(t, tile_addr, bytes);
   if (!r) return fail(XAIE_INVALID_ADDRESS, "tile address was never written or produced");
   const size_t avail = static_cast<size_t>(r->addr + r->cap - tile_addr);
   const size_t n = bytes < avail ? bytes : avail;
@@ -220,7 +243,8 @@ AieRC t2h(Runtime* rt, XAie_LocType src, u64 tile_addr, void* dst, size_t bytes)
 AieRC t2t(Runtime* rt, XAie_LocType src, u64 saddr, XAie_LocType dst, u64 daddr, size_t bytes) {
   Tile& ts = rt->tile(src);
   Region* r = rt->find_region(ts, saddr, bytes);
-  if (!r) return fail(XAIE_INVALID_ADDRESS, "source tile address range was never written or produced");
+  if (!r || saddr + bytes > r->addr + r->cap)
+    return fail(XAIE_INVALID_ADDRESS, "source tile address range was never written or produced");
   const void* sp = static_cast<uint8_t*>(r->dptr) + (saddr - r->addr);
   Tile& td = rt->tile(dst);
   void* dp = nullptr;

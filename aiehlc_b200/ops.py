@@ -55,6 +55,18 @@ class Context:
     def set_tile_n(self, tile_n: int) -> None:
         _capi.check(self._lib.aiehlc_set_tile_n(self._h, int(tile_n)))
 
+    def set_cta_pair(self, mode: int) -> None:
+        _capi.check(self._lib.aiehlc_set_cta_pair(self._h, int(mode)))
+
+    def set_debug(self, mode: int) -> None:
+        _capi.check(self._lib.aiehlc_set_debug(self._h, int(mode)))
+
+    def set_trace(self, buf) -> None:
+        """buf: int64 CUDA tensor (8 words per tile of one CTA) or None."""
+        import torch
+        ptr = C.c_void_p(None) if buf is None else self._dev(buf, torch.int64, "trace")
+        _capi.check(self._lib.aiehlc_set_trace(self._h, ptr))
+
     def sync(self, on_torch_stream: bool = True) -> int:
         """Waits for the stream and returns the device status word (raises if it is non-zero)."""
         st = C.c_int32(0)

@@ -116,6 +116,20 @@ int aiehlc_conv2d_i8_srs_host(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w,
 
 /* Tuning knob for experiments: force the N extent of the GEMM tile (64, 128 or 256; 0 = choose). */
 int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n);
+/* Tuning knob: 1 = run the GEMM tiles on CTA pairs (tcgen05 cta_group::2, 256-row tiles, each CTA
+ * fetching half of the B tile) wherever M > 128, 0 = one CTA per 128-row tile, -1 = choose per
+ * shape (the default). */
+int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode);
+/* Measurement aid for the GEMM kernels (results are then meaningless): 1 = skip the TMA loads and
+ * run the MMAs on whatever shared memory holds (tensor-pipe ceiling), 2 = skip the MMAs and only
+ * stream the operands (operand-feed ceiling), 0 = normal. */
+int aiehlc_set_debug(aiehlc_ctx* ctx, int mode);
+/* Measurement aid: while `device_buffer` is non-NULL, the first CTA of every GEMM launch writes
+ * clock64() stamps for each of its tiles into it, 8 int64 slots per tile: [0] MMA loop start,
+ * [1] MMA loop issued, [2] epilogue starts waiting, [3] accumulator ready, [4] epilogue done;
+ * tile 0 also holds [5] kernel entry, [6] kernel exit (clock64) and [7] / word 15 the global
+ * nanosecond timer at entry / exit.  The buffer must hold 8 * max(2, tiles per CTA) words.  NULL switches the stamps off. */
+int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer);
 /* Number of kernel launches this context has enqueued since creation. */
 long long aiehlc_launch_count(const aiehlc_ctx* ctx);
 

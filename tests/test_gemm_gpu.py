@@ -46,17 +46,21 @@ SHAPES = [(64, 64, 64),            # the single-tile configuration
           (127, 255, 4096), (129, 257, 144)]
 
 
+@pytest.mark.parametrize("pair", [-1, 0, 1])
 @pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
 @pytest.mark.parametrize("shape", SHAPES)
-def test_gemm_i8_i32_matches_oracle(ctx, shape, tile_n):
+def test_gemm_i8_i32_matches_oracle(ctx, shape, tile_n, pair):
+    """Every tile shape of both kernel families (one CTA per tile, CTA pair per tile)."""
     M, N, K = shape
     A = synth.int8_uniform(1, (M, K))
     B = synth.int8_uniform(1001, (N, K))
     ctx.set_tile_n(tile_n)
+    ctx.set_cta_pair(pair)
     try:
         got = ctx.gemm_i8_i32(_dev(A), _dev(B)).cpu().numpy()
     finally:
         ctx.set_tile_n(0)
+        ctx.set_cta_pair(-1)
     assert ctx.sync() == 0
     assert np.array_equal(got, O.gemm_i8_i32(A, B))
 
@@ -86,10 +90,13 @@ def test_empty_and_zero_sizes(ctx):
 
 
 # ---------------------------------------------------------------- srs epilogue, split-K, cascade
+@pytest.mark.parametrize("pair", [0, 1])
 @pytest.mark.parametrize("shape,shift", [((256, 256, 256), 8), ((300, 200, 400), 6), ((512, 384, 1024), 0),
-                                         ((128, 128, 2048), 12), ((64, 48, 80), 1), ((96, 80, 72), 31)])
-def test_gemm_i8_srs_matches_oracle(ctx, shape, shift):
+                                         ((128, 128, 2048), 12), ((64, 48, 80), 1), ((96, 80, 72), 31),
+                                         ((260, 520, 40000), 30), ((140, 100, 33000), 3)])
+def test_gemm_i8_srs_matches_oracle(ctx, shape, shift, pair):
     M, N, K = shape
+    ctx.set_cta_pair(pair)
     A = synth.int8_uniform(2, (M, K))
     B = synth.int8_uniform(1002, (N, K))
     exp = O.gemm_i8_srs(A, B, shift=shift)
@@ -99,6 +106,7 @@ def test_gemm_i8_srs_matches_oracle(ctx, shape, shift):
     assert np.array_equal(ctx.gemm_i8_srs(_dev(A), _dev(B), shift_vec=_dev(sv)).cpu().numpy(),
                           O.gemm_i8_srs(A, B, shift_vec=sv))
     assert np.array_equal(ctx.gemm_i8_srs_host(A, B, shift_vec=sv), O.gemm_i8_srs(A, B, shift_vec=sv))
+    ctx.set_cta_pair(-1)
 
 
 def test_srs_rounding_ties_through_the_kernel(ctx):
