@@ -27,6 +27,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures (profiles/)
+NCU_TRAFFIC_BYTES = {"cfg2": 33.7e6}
 
 WORKLOADS = {
     # name: (M per GPU or total, N, K, description)
@@ -348,7 +350,7 @@ def main() -> int:
     else:
         peak = peaks["bf16"] * (2.0 if dtype == "int8" else 1.0)
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                    "traffic": None,
+                    "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                     "note": ("peak = 2 x measured bf16 burst (kind::i8 has twice the K per instruction)"
                              if dtype == "int8" else "peak = measured bf16 burst") + f", {peaks['source']}"}
     extra.update(extra_measurements(args, wl, ctx, dev, kind, rank))
