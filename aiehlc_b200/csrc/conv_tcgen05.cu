@@ -12,6 +12,8 @@
 // up to 256 output channels.  The reference has no convolution; the kernel follows the tiling
 // vocabulary of its matmul path (K loop, accumulate, flush once: tiling.py:299-333).
 #include <cstdio>
+#include <mutex>
+#include <string>
 
 #include "context.h"
 #include "gemm_tcgen05.cuh"
@@ -319,3 +321,156 @@ int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, 
 }
 
 }  // namespace aiehlc
+
+// =====================================================================================
+// Allocation-free variant of the convolution.
+//
+// Some callers may not allocate device memory at the moment they call: code running while a
+// memory pool is frozen, inside a real-time loop that forbids the driver's allocator lock, or
+// under a host framework that owns every byte of the device and hands none out.  The regular
+// entry point keeps the re-laid weights ([tap][cout][cin]) in a context workspace that grows with
+// cudaMalloc; this one keeps them in a fixed array that is part of the library image instead.
+// Every GPU that loads the library carries the array until the process exits.
+namespace aiehlc {
+
+constexpr size_t kConvStaticScratchBytes = AIEHLC_CONV_STATIC_SCRATCH_BYTES;
+
+// In host code this name is only a handle for the symbol, not a device address: the address the
+// kernels need comes from cudaGetSymbolAddress (below).
+static __device__ __align__(256) int8_t g_conv_static_weights[kConvStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+int8_t* g_static_weights_ptr[kMaxDevices] = {};
+std::mutex g_static_weights_mu;
+
+// Once per device, with that device current: resolve the array's device address.
+int static_weights_address(int device, int8_t** out) {
+  if (device < 0 || device >= kMaxDevices) return fail(AIEHLC_ERR_UNSUPPORTED, "device index too large");
+  std::lock_guard<std::mutex> lk(g_static_weights_mu);
+  if (!g_static_weights_ptr[device]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_conv_static_weights);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_conv_static_weights)");
+    if (p == nullptr || reinterpret_cast<uintptr_t>(p) % 256 != 0)
+      return fail(AIEHLC_ERR_CUDA, "static conv scratch resolved to a null or misaligned address");
+    g_static_weights_ptr[device] = static_cast<int8_t*>(p);
+  }
+  *out = g_static_weights_ptr[device];
+  return AIEHLC_OK;
+}
+}  // namespace
+
+// Same two kernels as launch_conv2d, with the packed weights in the static array.
+int launch_conv2d_static(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
+                         int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
+  const int taps = kh * kw;
+  const size_t wbytes = static_cast<size_t>(taps) * cin * cout;
+  if (wbytes > kConvStaticScratchBytes)
+    return fail(AIEHLC_ERR_UNSUPPORTED,
+                "conv2d (static scratch): kh*kw*cin*cout = " + std::to_string(wbytes) + " bytes of weights exceed the " +
+                    std::to_string(kConvStaticScratchBytes) + "-byte static scratch; use aiehlc_conv2d_i8_srs_dev");
+  const bool tensor_ok = (cin % 32 == 0) && (cin == 32 || cin == 64 || cin % 128 == 0) && (cout % 16 == 0) &&
+                         (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+  if (!tensor_ok) {
+    // the direct kernel needs no scratch at all
+    const long long total = static_cast<long long>(n) * h * wd * cout;
+    long long g = (total + 255) / 256;
+    if (g > ctx->sm_count * 16LL) g = ctx->sm_count * 16LL;
+    conv2d_i8_direct_kernel<<<static_cast<int>(g), 256, 0, st>>>(x, w, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec);
+    AIEHLC_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return AIEHLC_OK;
+  }
+  int8_t* packed = nullptr;
+  int rc = static_weights_address(ctx->device, &packed);
+  if (rc) return rc;
+  {
+    // Every byte the second kernel reads ([0, wbytes)) is rewritten here, so nothing left by an
+    // earlier call can leak into this one and nothing has to be cleared.
+    long long g = (static_cast<long long>(wbytes) + 255) / 256;
+    if (g > ctx->sm_count * 8LL) g = ctx->sm_count * 8LL;
+    conv_weight_prepack_kernel<<<static_cast<int>(g), 256, 0, st>>>(w, packed, taps, cin, cout);
+    AIEHLC_CUDA(cudaGetLastError());
+    ctx->launches++;
+  }
+
+  ConvParams p{};
+  p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
+  p.wt = wd <= kBlockM ? wd : kBlockM;
+  p.rows_per_tile = wd <= kBlockM ? kBlockM / wd : 1;
+  if (p.rows_per_tile > h) p.rows_per_tile = h;
+  p.tiles_w = (wd + p.wt - 1) / p.wt;
+  p.tiles_h = (h + p.rows_per_tile - 1) / p.rows_per_tile;
+  p.chunk = cin >= 128 ? 128 : cin;
+  p.chunks_per_tap = cin / p.chunk;
+  p.cout_tile = cout <= 256 ? cout : 256;
+  if (cout > 256 && cout % 256 != 0) {
+    int ct = 256;
+    while (ct > 16 && cout % ct != 0) ct -= 16;
+    p.cout_tile = ct;
+  }
+  const int n_tiles = (cout + p.cout_tile - 1) / p.cout_tile;
+  p.swizzle_code = p.chunk == 128 ? 2u : (p.chunk == 64 ? 4u : 6u);
+  p.sbo_bytes = 8u * p.chunk;
+  p.a_bytes = kBlockM * p.chunk;
+  const int b_bytes = (p.cout_tile * p.chunk + 1023) / 1024 * 1024;
+  p.stage_bytes = p.a_bytes + b_bytes;
+  p.tx_bytes = static_cast<uint32_t>(p.chunk) * (p.wt * p.rows_per_tile + p.cout_tile);
+  int stages = (200 * 1024) / p.stage_bytes;
+  if (stages > kConvMaxStages) stages = kConvMaxStages;
+  if (stages > taps * p.chunks_per_tap) stages = taps * p.chunks_per_tap;
+  p.stages = stages;
+  uint32_t cols = 32;
+  while (cols < static_cast<uint32_t>(p.cout_tile)) cols <<= 1;
+  p.tmem_cols = cols;
+  p.y = y; p.shift_vec = shift_vec; p.status = ctx->d_status;
+
+  CUtensorMap mx, mw;
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapSwizzle sw = p.chunk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : p.chunk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(wd), static_cast<cuuint64_t>(h),
+                              static_cast<cuuint64_t>(n)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cin) * wd,
+                                 static_cast<cuuint64_t>(cin) * wd * h};
+  const cuuint32_t box[4] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.wt),
+                             static_cast<cuuint32_t>(p.rows_per_tile), 1};
+  CUresult r = ctx->encode(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(x), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv input");
+  const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(taps) * cout};
+  const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(cin)};
+  const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.cout_tile)};
+  r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, packed, wdims, wstrides, wbox, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
+
+  const int smem_bytes = p.stages * p.stage_bytes + 512 + 1024;
+  AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  dim3 grid(n * p.tiles_h * p.tiles_w, n_tiles);
+  conv2d_i8_kernel<<<grid, kConvThreads, smem_bytes, st>>>(mx, mw, p);
+  AIEHLC_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return AIEHLC_OK;
+}
+
+}  // namespace aiehlc
+
+extern "C" int aiehlc_conv2d_i8_srs_static_dev(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n,
+                                               int h, int wd, int cin, int cout, int kh, int kw, int pad,
+                                               const uint8_t* shift_vec, void* stream) {
+  using namespace aiehlc;
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  AIEHLC_CUDA(cudaSetDevice(ctx->device));
+  if (n < 0 || h < 0 || wd < 0 || cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0 || pad < 0)
+    return fail(AIEHLC_ERR_INVALID, "conv2d (static scratch): bad size");
+  if (kh != 2 * pad + 1 || kw != 2 * pad + 1)
+    return fail(AIEHLC_ERR_UNSUPPORTED, "conv2d (static scratch): only stride 1 with kh = kw = 2*pad+1");
+  if (n == 0 || h == 0 || wd == 0) return AIEHLC_OK;
+  if (!x || !w || !y || !shift_vec) return fail(AIEHLC_ERR_INVALID, "conv2d (static scratch): null pointer");
+  return launch_conv2d_static(ctx, x, w, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec,
+                              static_cast<cudaStream_t>(stream));
+}

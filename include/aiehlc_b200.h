@@ -114,6 +114,27 @@ int aiehlc_conv2d_i8_srs_host(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w,
                               int h, int wd, int cin, int cout, int kh, int kw, int pad,
                               const uint8_t* shift_vec);
 
+/* ---- the same convolution for callers that must not allocate -----------------------------
+ * (No counterpart in the reference: aiehlc has neither a convolution nor a device allocator.)
+ * Meant for callers that cannot reach the device allocator when they call: a frozen memory pool, a
+ * latency-critical loop that must not take the driver's allocation lock, a host that has handed
+ * the whole device to someone else.  Same arguments and bit-identical results as
+ * aiehlc_conv2d_i8_srs_dev, but the re-laid weights live in a fixed array inside the library
+ * (AIEHLC_CONV_STATIC_SCRATCH_BYTES, held by every GPU that loads the library until the process
+ * ends) instead of a workspace that grows with cudaMalloc.  The call performs no cudaMalloc /
+ * cudaFree and calls no allocating routine.
+ *   - kh*kw*cin*cout above AIEHLC_CONV_STATIC_SCRATCH_BYTES is refused with AIEHLC_ERR_UNSUPPORTED.
+ *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress); make
+ *     that first call before starting any stream capture.
+ *   - All calls on a GPU share the one array and it keeps what the last call left there; each call
+ *     rewrites every byte it later reads, so results never depend on earlier calls -- but two calls
+ *     that overlap on the GPU (different streams, or different contexts on one device) race on it.
+ *     Serialise them. */
+#define AIEHLC_CONV_STATIC_SCRATCH_BYTES (1u << 20)
+int aiehlc_conv2d_i8_srs_static_dev(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n,
+                                    int h, int wd, int cin, int cout, int kh, int kw, int pad,
+                                    const uint8_t* shift_vec, void* stream);
+
 /* Tuning knob for experiments: force the N extent of the GEMM tile (64, 128 or 256; 0 = choose). */
 int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n);
 /* Tuning knob: 1 = run the GEMM tiles on CTA pairs (tcgen05 cta_group::2, 256-row tiles, each CTA
