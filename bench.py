@@ -140,10 +140,19 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU legs
+def host_threads() -> int:
+    """Host threads this process may use (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_time_i8_srs(rows: int, n: int, k: int, shift: int, splitk: int, seed: int, reps: int = 1):
     """Times the oracle's GEMM+srs on `rows` rows of the workload; returns (seconds per rep, threads)."""
     from aiehlc_b200 import synth
     from oracle import oracle as O
+    O.set_threads(host_threads())
     A = synth.int8_uniform(seed, (rows, k))
     B = synth.int8_uniform(seed + 1000, (n, k))
     O.gemm_i8_srs(A[:8], B[:64], shift=shift, splitk=splitk)  # page in / warm up
@@ -165,6 +174,7 @@ def reference_arm(args, wl: dict) -> dict:
     rows = int(max(16, min(wl["M"], budget_s / total_steps / per_row)))
     from aiehlc_b200 import synth
     from oracle import oracle as O
+    O.set_threads(host_threads())
     A = synth.int8_uniform(2, (rows, k))
     B = synth.int8_uniform(1002, (n, k))
     for _ in range(args.warmup):
@@ -241,7 +251,6 @@ def main() -> int:
         ws = [synth.int8_uniform_torch(1004 + 10 * i, (3, 3, cin, cout), dev) for i in range(nsets)]
         sv = torch.full((cout,), wl["shift"], dtype=torch.uint8, device=dev)
         ys = [torch.empty((n, h, w, cout), dtype=torch.int8, device=dev) for _ in range(nsets)]
-        flush = torch.empty(L2_BYTES * 2, dtype=torch.uint8, device=dev)
         ops_per_step = 2.0 * n * h * w * cout * 9 * cin
         alg_bytes = n * h * w * cin + 9 * cin * cout + n * h * w * cout + cout
 
