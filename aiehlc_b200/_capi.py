@@ -40,6 +40,7 @@ SIGNATURES = {
     "aiehlc_set_tile_n": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_cta_pair": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_debug": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_set_pdl": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_trace": (C.c_int, [_vp, _vp]),
     "aiehlc_launch_count": (C.c_longlong, [_vp]),
 }

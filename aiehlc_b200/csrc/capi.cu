@@ -135,6 +135,12 @@ int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode) {
   return AIEHLC_OK;
 }
 
+int aiehlc_set_pdl(aiehlc_ctx* ctx, int on) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->pdl = on ? 1 : 0;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   ctx->trace = device_buffer;

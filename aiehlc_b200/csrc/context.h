@@ -6,6 +6,7 @@
 #include <cstddef>
 #include <cstdint>
 #include <string>
+#include <unordered_map>
 
 #include "../../include/aiehlc_b200.h"
 
@@ -36,6 +37,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 }  // namespace aiehlc
 
+namespace aiehlc {
+// What has been established once per kernel function on this context's device.
+struct KernelSetup {
+  int smem_attr = 0;     // dynamic shared memory limit already raised to this many bytes
+  int max_clusters = 0;  // co-resident clusters of the persistent pair kernel (0 = not queried)
+};
+}  // namespace aiehlc
+
 struct aiehlc_ctx {
   int device = 0;
   int sm_count = 0;
@@ -45,9 +54,11 @@ struct aiehlc_ctx {
   aiehlc::EncodeTiledFn encode = nullptr;
   int force_tile_n = 0;
   int pair_mode = -1;           // -1: choose per shape, 0: single-CTA tiles only, 1: CTA pairs wherever M > 128
+  int pdl = 1;                  // launch the tensor-core kernels with programmatic stream serialization
   int debug_mode = 0;           // see GemmParams::debug
   long long* trace = nullptr;   // see GemmParams::trace (device pointer owned by the caller)
   long long launches = 0;
+  std::unordered_map<const void*, aiehlc::KernelSetup> kernel_setup;
   // staging for *_host entry points and for operands that TMA cannot address directly
   aiehlc::DevBuf buf_a, buf_b, buf_c, buf_aux, pack_a, pack_b;
 };

@@ -72,6 +72,8 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // the weight pre-pass before this kernel has completed; global memory may be touched
 
   // tile -> (image, first output row, first output column, first output channel)
   int t = blockIdx.x;
@@ -311,11 +313,23 @@ int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, 
   }
 
   const int smem_bytes = p.stages * p.stage_bytes + 512 + 1024;
-  AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   smem_bytes));
+  KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(conv2d_i8_kernel)];
+  if (ks.smem_attr < smem_bytes) {
+    AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    ks.smem_attr = smem_bytes;
+  }
   dim3 grid(n * p.tiles_h * p.tiles_w, n_tiles);
-  conv2d_i8_kernel<<<grid, kConvThreads, smem_bytes, st>>>(mx, mw, p);
-  AIEHLC_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kConvThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, conv2d_i8_kernel, mx, mw, p));
   ctx->launches++;
   return AIEHLC_OK;
 }
@@ -451,8 +465,17 @@ int launch_conv2d_static(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8
   const int smem_bytes = p.stages * p.stage_bytes + 512 + 1024;
   AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid(n * p.tiles_h * p.tiles_w, n_tiles);
-  conv2d_i8_kernel<<<grid, kConvThreads, smem_bytes, st>>>(mx, mw, p);
-  AIEHLC_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kConvThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, conv2d_i8_kernel, mx, mw, p));
   ctx->launches++;
   return AIEHLC_OK;
 }

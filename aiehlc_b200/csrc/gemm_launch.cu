@@ -92,12 +92,24 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.trace = ctx->trace;
 
   auto kern = gemm_tn_kernel<kKind, kBN, kEpi>;
-  // Per device and cheap, so simply repeated on every launch.
-  AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
+  if (ks.smem_attr < S::kTotal) {
+    AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+    ks.smem_attr = S::kTotal;
+  }
   const int tiles = p.num_m_blocks * p.num_n_blocks;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  kern<<<grid, kGemmThreads, S::kTotal, st>>>(ma, mb, p);
-  AIEHLC_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
   ctx->launches++;
   return AIEHLC_OK;
 }
@@ -132,26 +144,41 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.trace = ctx->trace;
 
   auto kern = gemm_tn_pair_kernel<kKind, kBN, kEpi>;
-  AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
+  if (ks.smem_attr < S::kTotal) {
+    AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+    ks.smem_attr = S::kTotal;
+  }
   const int tiles = p.num_m_blocks * p.num_n_blocks;
   int max_pairs = ctx->sm_count / 2;
   cudaLaunchConfig_t cfg{};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = S::kTotal;
   cfg.stream = st;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cfg.gridDim = dim3(2 * max_pairs);
-  int active = 0;
-  if (cudaOccupancyMaxActiveClusters(&active, kern, &cfg) == cudaSuccess && active > 0 && active < max_pairs)
-    max_pairs = active;  // every cluster of the persistent grid must be resident at once
-  else
-    cudaGetLastError();
+  cfg.numAttrs = ctx->pdl ? 2 : 1;
+  if (ks.max_clusters == 0) {
+    // every cluster of the persistent grid must be resident at once
+    cfg.gridDim = dim3(2 * max_pairs);
+    int active = 0;
+    const int na = cfg.numAttrs;
+    cfg.numAttrs = 1;  // the cluster shape is what matters for occupancy
+    if (cudaOccupancyMaxActiveClusters(&active, kern, &cfg) == cudaSuccess && active > 0)
+      ks.max_clusters = active < max_pairs ? active : max_pairs;
+    else {
+      cudaGetLastError();
+      ks.max_clusters = max_pairs;
+    }
+    cfg.numAttrs = na;
+  }
+  max_pairs = ks.max_clusters;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   cfg.gridDim = dim3(2 * pairs);
   AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));

@@ -251,10 +251,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
-    p.trace[5] = clock64();
-    p.trace[7] = static_cast<long long>(globaltimer_ns());
-  }
+  const long long entry_clock = clock64();
+  const unsigned long long entry_ns = globaltimer_ns();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -280,6 +278,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // from here on global memory may be read and written
+  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+    p.trace[5] = entry_clock;
+    p.trace[7] = static_cast<long long>(entry_ns);
+  }
 
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
 

@@ -35,6 +35,16 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
+// ------------------------------------------------ programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still draining.  Everything before pdl_wait() (barrier set-up,
+// TMEM allocation, descriptor prefetch) then overlaps that tail; pdl_wait() returns once the
+// earlier kernel has completed and its memory is visible, so no global access may precede it.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ----------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

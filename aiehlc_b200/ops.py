@@ -58,6 +58,9 @@ class Context:
     def set_cta_pair(self, mode: int) -> None:
         _capi.check(self._lib.aiehlc_set_cta_pair(self._h, int(mode)))
 
+    def set_pdl(self, on: bool) -> None:
+        _capi.check(self._lib.aiehlc_set_pdl(self._h, 1 if on else 0))
+
     def set_debug(self, mode: int) -> None:
         _capi.check(self._lib.aiehlc_set_debug(self._h, int(mode)))
 
@@ -87,6 +90,42 @@ class Context:
         if not t.is_contiguous():
             raise ValueError(f"{name}: tensor must be contiguous")
         return C.c_void_p(t.data_ptr())
+
+    # ------------------------------------------------ pre-bound calls for launch-rate-bound loops
+    def bound_gemm_i8_srs(self, A, B, out, shift: int = 0, splitk: int = 1):
+        """Returns a zero-argument callable that issues aiehlc_gemm_i8_srs_dev on torch's current stream
+        with every argument converted once (the per-call Python work drops to one foreign call)."""
+        import torch
+        (M, K), N = A.shape, B.shape[0]
+        args = (self._h, self._dev(A, torch.int8, "A"), self._dev(B, torch.int8, "B"), self._dev(out, torch.int8, "C"),
+                M, N, K, int(shift), C.c_void_p(None), C.c_void_p(None), int(splitk), self._stream())
+        fn, check = self._lib.aiehlc_gemm_i8_srs_dev, _capi.check
+        return lambda: check(fn(*args))
+
+    def bound_gemm_i8_i32(self, A, B, out, accumulate: bool = False):
+        import torch
+        (M, K), N = A.shape, B.shape[0]
+        args = (self._h, self._dev(A, torch.int8, "A"), self._dev(B, torch.int8, "B"), self._dev(out, torch.int32, "C"),
+                M, N, K, 1 if accumulate else 0, self._stream())
+        fn, check = self._lib.aiehlc_gemm_i8_i32_dev, _capi.check
+        return lambda: check(fn(*args))
+
+    def bound_gemm_bf16(self, A, B, out):
+        import torch
+        (M, K), N = A.shape, B.shape[0]
+        args = (self._h, self._dev(A, torch.bfloat16, "A"), self._dev(B, torch.bfloat16, "B"),
+                self._dev(out, torch.bfloat16, "C"), M, N, K, self._stream())
+        fn, check = self._lib.aiehlc_gemm_bf16_dev, _capi.check
+        return lambda: check(fn(*args))
+
+    def bound_conv2d_i8_srs(self, x, w, shift_vec, out, pad: int = 1):
+        import torch
+        n, h, wd, cin = x.shape
+        kh, kw, _, cout = w.shape
+        args = (self._h, self._dev(x, torch.int8, "x"), self._dev(w, torch.int8, "w"), self._dev(out, torch.int8, "y"),
+                n, h, wd, cin, cout, kh, kw, int(pad), self._dev(shift_vec, torch.uint8, "shift_vec"), self._stream())
+        fn, check = self._lib.aiehlc_conv2d_i8_srs_dev, _capi.check
+        return lambda: check(fn(*args))
 
     # --------------------------------------------------------- device tensors
     def mm_i32(self, packed, M: int, N: int, K: int, out=None):

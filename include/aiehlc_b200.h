@@ -141,6 +141,11 @@ int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n);
  * fetching half of the B tile) wherever M > 128, 0 = one CTA per 128-row tile, -1 = choose per
  * shape (the default). */
 int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode);
+/* Tuning knob: 1 (default) = the tensor-core kernels are launched with programmatic stream
+ * serialization, so their set-up (barriers, TMEM allocation) overlaps the tail of the kernel before
+ * them in the stream; they still wait for that kernel to complete before touching global memory.
+ * 0 = plain stream-ordered launches. */
+int aiehlc_set_pdl(aiehlc_ctx* ctx, int on);
 /* Measurement aid for the GEMM kernels (results are then meaningless): 1 = skip the TMA loads and
  * run the MMAs on whatever shared memory holds (tensor-pipe ceiling), 2 = skip the MMAs and only
  * stream the operands (operand-feed ceiling), 0 = normal. */
