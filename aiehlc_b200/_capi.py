@@ -41,9 +41,26 @@ SIGNATURES = {
     "aiehlc_set_cta_pair": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_debug": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_pdl": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_set_group_m": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_trace": (C.c_int, [_vp, _vp]),
     "aiehlc_launch_count": (C.c_longlong, [_vp]),
 }
+
+
+
+class GemmPlan(C.Structure):
+    """aiehlc_gemm_plan of include/aiehlc_b200.h."""
+    _fields_ = [("tile_m", C.c_int), ("tile_n", C.c_int), ("tile_k_bytes", C.c_int), ("cta_pair", C.c_int),
+                ("grid_m", C.c_int), ("grid_n", C.c_int), ("tiles", C.c_longlong), ("slots", C.c_int),
+                ("waves", C.c_int), ("wave_efficiency", C.c_double), ("group_m", C.c_int), ("stages", C.c_int),
+                ("smem_bytes", C.c_int), ("tmem_columns", C.c_int), ("k_blocks", C.c_int), ("a_shared_by", C.c_int),
+                ("b_shared_by", C.c_int), ("wave_footprint_bytes", C.c_longlong), ("cost_units", C.c_double)]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+SIGNATURES["aiehlc_plan_gemm"] = (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(GemmPlan)])
 
 _lib = None
 

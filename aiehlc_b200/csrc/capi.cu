@@ -135,6 +135,26 @@ int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode) {
   return AIEHLC_OK;
 }
 
+int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* plan) {
+  if (!plan) return fail(AIEHLC_ERR_INVALID, "plan_gemm: null plan");
+  if (kind != KIND_I8 && kind != KIND_BF16) return fail(AIEHLC_ERR_INVALID, "plan_gemm: kind must be 0 (int8) or 1 (bf16)");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(AIEHLC_ERR_INVALID, "plan_gemm: M, N, K must be positive");
+  if (!ctx) {
+    // no device needed to plan: a B200 with default settings
+    aiehlc_ctx defaults;
+    defaults.sm_count = 148;
+    return plan_gemm(&defaults, kind, M, N, K, plan);
+  }
+  return plan_gemm(ctx, kind, M, N, K, plan);
+}
+
+int aiehlc_set_group_m(aiehlc_ctx* ctx, int group_m) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (group_m < 0) return fail(AIEHLC_ERR_INVALID, "group_m must be >= 0");
+  ctx->group_m = group_m;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_pdl(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   ctx->pdl = on ? 1 : 0;

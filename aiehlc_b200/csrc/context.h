@@ -54,6 +54,7 @@ struct aiehlc_ctx {
   aiehlc::EncodeTiledFn encode = nullptr;
   int force_tile_n = 0;
   int pair_mode = -1;           // -1: choose per shape, 0: single-CTA tiles only, 1: CTA pairs wherever M > 128
+  int group_m = 0;              // row-blocks per rasterisation group (0 = default for the kernel family)
   int pdl = 1;                  // launch the tensor-core kernels with programmatic stream serialization
   int debug_mode = 0;           // see GemmParams::debug
   long long* trace = nullptr;   // see GemmParams::trace (device pointer owned by the caller)
@@ -78,8 +79,10 @@ struct GemmCall {
   long long lda, ldb, ldc;      // elements
   const int32_t* acc_in; long long ld_acc;
   const uint8_t* shift_vec; int shift;
+  int group_m;                  // filled in from the plan
 };
 int launch_gemm(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st);
+int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* out);
 
 // SIMT helpers (simt_kernels.cu)
 int launch_mm_i32(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K, cudaStream_t st);

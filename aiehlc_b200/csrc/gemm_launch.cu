@@ -37,30 +37,68 @@ int encode_kmajor_map(aiehlc_ctx* ctx, CUtensorMap* map, int kind, const void* b
 // feed, hence the efficiency factors (measured on int8 4096^3: N = 256 / 128 / 64 tiles take
 // 56.8 / 82.0 / 143.9 us).  A CTA pair does the work of two single-CTA tiles with two thirds of
 // the operand traffic per SM (measured on int8 8192^3: 373 us against 391 us).
-struct TileChoice { int bn; bool pair; };
-TileChoice choose_tile(int M, int N, int sms, int force_bn, int pair_mode) {
+}  // namespace
+
+// The planner: B200 counterpart of the compiler's matmul tiling (tilinglinalg::creatematmul,
+// src/mlir/mlirfront/tilinglinalg/tilinglinalg.cpp:38-146: grid of tiles + per-tile block) and of
+// its data-pattern analysis (tilingpass.cpp:98-150: which operand is broadcast along which grid
+// dimension).  launch_gemm() executes exactly the plan this function returns.
+int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* out) {
   const int cand[3] = {256, 128, 64};
   const double eff[3] = {1.0, 0.60, 0.35};
-  TileChoice best{256, false};
+  const int sms = ctx->sm_count;
+  const int esize = kind == KIND_I8 ? 1 : 2;
+  aiehlc_gemm_plan best{};
   double best_cost = -1;
   for (int pr = 0; pr < 2; ++pr) {
-    if (pr == 1 && pair_mode == 0) continue;      // pairs switched off
-    if (pr == 0 && pair_mode == 1 && M > kBlockM) continue;  // pairs forced where they apply
+    if (pr == 1 && ctx->pair_mode == 0) continue;                  // pairs switched off
+    // pairs forced where they apply (more than one row-block, and not the 64-wide tile they lack)
+    if (pr == 0 && ctx->pair_mode == 1 && M > kBlockM && ctx->force_tile_n != 64) continue;
     for (int i = 0; i < 3; ++i) {
       const int bn = cand[i];
-      if (force_bn && bn != force_bn) continue;
+      if (ctx->force_tile_n && bn != ctx->force_tile_n) continue;
       if (pr == 1 && bn == 64) continue;
-      const long long mblocks = pr ? (M + kPairM - 1) / kPairM : (M + kBlockM - 1) / kBlockM;
-      const long long tiles = mblocks * ((N + bn - 1) / bn);
-      const long long slots = pr ? sms / 2 : sms;
-      const long long waves = (tiles + slots - 1) / slots;
+      const int tm = pr ? kPairM : kBlockM;
+      aiehlc_gemm_plan pl{};
+      pl.tile_m = tm;
+      pl.tile_n = bn;
+      pl.tile_k_bytes = kBlockKBytes;
+      pl.cta_pair = pr;
+      pl.grid_m = (M + tm - 1) / tm;
+      pl.grid_n = (N + bn - 1) / bn;
+      pl.tiles = static_cast<long long>(pl.grid_m) * pl.grid_n;
+      pl.slots = pr ? sms / 2 : sms;
+      pl.waves = static_cast<int>((pl.tiles + pl.slots - 1) / pl.slots);
+      pl.wave_efficiency = static_cast<double>(pl.tiles) / (static_cast<double>(pl.waves) * pl.slots);
       // rows of the last row-block that fall outside M are computed all the same
-      const double cost = static_cast<double>(waves) * bn / eff[i] * (pr ? 0.97 : 1.0);
-      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = TileChoice{bn, pr == 1}; }
+      pl.cost_units = static_cast<double>(pl.waves) * bn / eff[i] * (pr ? 0.97 : 1.0);
+      if (best_cost < 0 || pl.cost_units < best_cost) { best_cost = pl.cost_units; best = pl; }
     }
   }
-  return best;
+  if (best_cost < 0) return fail(AIEHLC_ERR_INVALID, "plan_gemm: no tile shape satisfies the forced settings");
+  const int stage_bytes = best.cta_pair ? kBlockM * kBlockKBytes + best.tile_n / 2 * kBlockKBytes
+                                        : kBlockM * kBlockKBytes + best.tile_n * kBlockKBytes;
+  int stages = (227 * 1024 - 2048) / stage_bytes;
+  if (stages > 8) stages = 8;
+  best.stages = stages;
+  best.smem_bytes = stages * stage_bytes + 512 + 1024;
+  best.tmem_columns = 2 * best.tile_n < 32 ? 32 : 2 * best.tile_n;
+  best.k_blocks = static_cast<int>((static_cast<long long>(K) * esize + kBlockKBytes - 1) / kBlockKBytes);
+  int g = ctx->group_m > 0 ? ctx->group_m : (best.cta_pair ? 8 : 16);
+  if (g > best.grid_m) g = best.grid_m;
+  best.group_m = g;
+  // every tile of a grid row reads the same rows of A, every tile of a grid column the same rows of B
+  best.a_shared_by = best.grid_n;
+  best.b_shared_by = best.grid_m;
+  const long long wave_cols = (best.slots + g - 1) / g;
+  best.wave_footprint_bytes = (static_cast<long long>(g) * best.tile_m +
+                               (wave_cols < best.grid_n ? wave_cols : best.grid_n) * best.tile_n) *
+                              static_cast<long long>(K) * esize;
+  *out = best;
+  return AIEHLC_OK;
 }
+
+namespace {
 
 template <int kKind, int kBN, int kEpi>
 int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
@@ -83,7 +121,7 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.num_m_blocks = (c.M + kBlockM - 1) / kBlockM;
   p.num_n_blocks = (c.N + kBN - 1) / kBN;
   p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
-  p.group_m = 8;
+  p.group_m = c.group_m;
   // 32 consecutive outputs per thread are written with 16-byte stores when every row start is aligned.
   bool vec = (reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0);
   p.vec_ok = vec ? 1 : 0;
@@ -137,7 +175,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.num_m_blocks = (c.M + kPairM - 1) / kPairM;
   p.num_n_blocks = (c.N + kBN - 1) / kBN;
   p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
-  p.group_m = 4;
+  p.group_m = c.group_m;
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0)) ? 1 : 0;
   p.status = ctx->d_status;
   p.debug = ctx->debug_mode;
@@ -227,9 +265,11 @@ int launch_gemm(aiehlc_ctx* ctx, const GemmCall& call, cudaStream_t st) {
     c.B = ctx->pack_b.ptr; c.ldb = ld;
   }
 
-  const TileChoice tc = choose_tile(c.M, c.N, ctx->sm_count, ctx->force_tile_n, ctx->pair_mode);
-  const int bn = tc.bn;
-  const bool pair = tc.pair;
+  aiehlc_gemm_plan plan{};
+  if (int rc = plan_gemm(ctx, c.kind, c.M, c.N, c.K, &plan)) return rc;
+  c.group_m = plan.group_m;
+  const int bn = plan.tile_n;
+  const bool pair = plan.cta_pair != 0;
   if (c.kind == KIND_I8) {
     switch (c.epi) {
       case EPI_I32: return dispatch_bn<KIND_I8, EPI_I32>(ctx, c, bn, pair, st);

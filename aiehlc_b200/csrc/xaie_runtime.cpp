@@ -191,6 +191,10 @@ struct Runtime {
   }
 };
 
+// The device instance that kernel-call expressions (which carry no instance argument) run on:
+// the one initialised last.
+Runtime* g_current_rt = nullptr;
+
 Runtime* rt_of(XAie_DevInst* d) { return d ? static_cast<Runtime*>(d->Priv) : nullptr; }
 
 AieRC need_rt(XAie_DevInst* d, Runtime** out) {
@@ -360,6 +364,7 @@ AieRC XAie_CfgInitialize(XAie_DevInst* DevInst, XAie_Config* ConfigPtr) {
   }
   DevInst->Priv = rt;
   DevInst->IsReady = 1;
+  g_current_rt = rt;
   return XAIE_OK;
 }
 
@@ -384,6 +389,7 @@ AieRC XAie_PmRequestTiles(XAie_DevInst* DevInst, XAie_LocType*, u32) {
 }
 AieRC XAie_PartitionTeardown(XAie_DevInst* DevInst) {
   if (!DevInst) return fail(XAIE_INVALID_ARGS, "null device instance");
+  if (g_current_rt == rt_of(DevInst)) g_current_rt = nullptr;
   free_runtime(rt_of(DevInst));
   DevInst->Priv = nullptr;
   DevInst->IsReady = 0;
@@ -717,6 +723,59 @@ AieRC XAie_DebugInjectStatus(XAie_DevInst* DevInst, u32 Status, u32 Count) {
   if (rc != XAIE_OK) return rc;
   rt->inject_status = Status;
   rt->inject_count = Count;
+  return XAIE_OK;
+}
+
+// ---------------------------------------------------------------------------------- kernel-call form
+// k<Col,Row,colstart,rowstart,M,N,K>(in, out) -- example/nokernelload/aie_nokernelload.cc:130; the
+// compiler declares the template (src/llvm/aiehlc.cc:583-588) but lowers it to nothing.  Here the
+// call is the whole load / move-in / run / wait / move-out sequence on tile (colstart,rowstart):
+// `in` and `out` are addresses inside GMIO buffers (what XAie_MemGetDevAddr returns).
+static XAie_MemInst* find_mem(Runtime* rt, u64 addr, u64* offset) {
+  for (XAie_MemInst* m : rt->mems) {
+    const u64 base = reinterpret_cast<u64>(m->host);
+    if (addr >= base && addr < base + m->bytes) {
+      *offset = addr - base;
+      return m;
+    }
+  }
+  return nullptr;
+}
+
+AieRC XAie_KernelCall(const void* kernel_key, const void* args, u32 args_bytes, int Col, int Row, int colstart,
+                      int rowstart, u64 in_addr, u64 out_addr) {
+  Runtime* rt = g_current_rt;
+  if (!rt) return fail(XAIE_INVALID_DEVICE, "kernel call before XAie_CfgInitialize");
+  XCUDA(cudaSetDevice(rt->device));
+  if (Col < 1 || Row < 1) return fail(XAIE_INVALID_ARGS, "kernel call: Col and Row must be at least 1");
+  const XAie_LocType loc = XAie_TileLoc(static_cast<u8>(colstart), static_cast<u8>(rowstart));
+  if (colstart < 0 || rowstart < 0 || !rt->valid_loc(loc) || rt->is_shim(loc))
+    return fail(XAIE_INVALID_TILE, "kernel call: (colstart,rowstart) is not a tile of the array");
+  AieRC rc = XAie_LoadElfMem(rt->dev, loc, static_cast<const unsigned char*>(kernel_key));
+  if (rc != XAIE_OK) return rc;
+  if (args && args_bytes) {
+    rc = XAie_KernelSetArgs(rt->dev, loc, args, args_bytes);
+    if (rc != XAIE_OK) return rc;
+  }
+  Tile& t = rt->tile(loc);
+  u64 off = 0;
+  XAie_MemInst* min = find_mem(rt, in_addr, &off);
+  if (!min) return fail(XAIE_INVALID_ADDRESS, "kernel call: input address is not inside a GMIO buffer");
+  rc = h2t(rt, loc, t.kernel.in_addr, static_cast<const uint8_t*>(min->host) + off, min->bytes - off);
+  if (rc != XAIE_OK) return rc;
+  XAie_MemInst* mout = find_mem(rt, out_addr, &off);
+  if (!mout) return fail(XAIE_INVALID_ADDRESS, "kernel call: output address is not inside a GMIO buffer");
+  g_err.clear();
+  rc = launch_tile(rt, t, 1);
+  if (rc != XAIE_OK) return rc;
+  Region* r = rt->find_region(t, t.kernel.out_addr, 1);
+  if (!r) return fail(XAIE_INVALID_ADDRESS, "kernel call: kernel produced no output window");
+  u64 n = r->cap;
+  if (n > mout->bytes - off) n = mout->bytes - off;
+  rc = t2h(rt, loc, t.kernel.out_addr, static_cast<uint8_t*>(mout->host) + off, n);  // waits for the stream
+  if (rc != XAIE_OK) return rc;
+  int status = 0;
+  if (aiehlc_sync(rt->ctx, rt->stream, &status) != AIEHLC_OK) return fail(XAIE_ERR_DEVICE, aiehlc_last_error());
   return XAIE_OK;
 }
 

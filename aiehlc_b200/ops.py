@@ -21,6 +21,15 @@ def _np_ptr(a: np.ndarray | None) -> C.c_void_p:
     return C.c_void_p(None) if a is None else C.c_void_p(a.ctypes.data)
 
 
+def plan_gemm(M: int, N: int, K: int, kind: str = "int8", ctx: "Context | None" = None) -> dict:
+    """The tiling the GEMM entry points use for this problem (aiehlc_plan_gemm); needs no GPU when
+    ctx is None (planned for a 148-SM B200 with default knobs)."""
+    plan = _capi.GemmPlan()
+    h = ctx._h if ctx is not None else C.c_void_p(None)
+    _capi.check(_capi.load().aiehlc_plan_gemm(h, {"int8": 0, "bf16": 1}[kind], int(M), int(N), int(K), C.byref(plan)))
+    return plan.as_dict()
+
+
 class Context:
     """Owns an `aiehlc_ctx` (device bring-up; stands in for the XAie_CfgInitialize /
     XAie_PartitionInitialize sequence of example/perf/aieml_perf.cc:265-313)."""
@@ -57,6 +66,9 @@ class Context:
 
     def set_cta_pair(self, mode: int) -> None:
         _capi.check(self._lib.aiehlc_set_cta_pair(self._h, int(mode)))
+
+    def set_group_m(self, group_m: int) -> None:
+        _capi.check(self._lib.aiehlc_set_group_m(self._h, int(group_m)))
 
     def set_pdl(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_pdl(self._h, 1 if on else 0))

@@ -114,6 +114,30 @@ int aiehlc_conv2d_i8_srs_host(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w,
                               int h, int wd, int cin, int cout, int kh, int kw, int pad,
                               const uint8_t* shift_vec);
 
+/* ---- tiling plan --------------------------------------------------------------------------
+ * What the GEMM entry points will do for a problem, without running it: tile shape, tile grid,
+ * waves over the persistent CTAs (or CTA pairs), pipeline depth, and how operands are shared.
+ * Counterpart of the compiler's matmul tiling and broadcast analysis
+ * (src/mlir/mlirfront/tilinglinalg/tilinglinalg.cpp:38-146, tilingpass.cpp:98-150), which prints the
+ * tile grid and which operand must be broadcast along which grid dimension. */
+typedef struct {
+  int tile_m, tile_n, tile_k_bytes;  /* output tile of one CTA (or CTA pair); K bytes per pipeline stage */
+  int cta_pair;                      /* 1: two CTAs (tcgen05 cta_group::2) per tile */
+  int grid_m, grid_n;                /* tile grid */
+  long long tiles;
+  int slots;                         /* tiles in flight: persistent CTAs or CTA pairs */
+  int waves;                         /* ceil(tiles / slots) */
+  double wave_efficiency;            /* tiles / (waves * slots) */
+  int group_m;                       /* tile row-blocks walked before the next tile column */
+  int stages, smem_bytes, tmem_columns, k_blocks;
+  int a_shared_by;                   /* tiles reading the same rows of A (A is shared along the N grid dimension) */
+  int b_shared_by;                   /* tiles reading the same rows of B (B is shared along the M grid dimension) */
+  long long wave_footprint_bytes;    /* operand bytes the tiles of one wave touch (L2 working set) */
+  double cost_units;                 /* the quantity the choice minimises: waves x tile_n / efficiency factor */
+} aiehlc_gemm_plan;
+/* kind: 0 = int8, 1 = bf16.  ctx may be NULL: the plan is then made for a 148-SM B200 with default knobs. */
+int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* plan);
+
 /* ---- the same convolution for callers that must not allocate -----------------------------
  * (No counterpart in the reference: aiehlc has neither a convolution nor a device allocator.)
  * Meant for callers that cannot reach the device allocator when they call: a frozen memory pool, a
@@ -141,6 +165,10 @@ int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n);
  * fetching half of the B tile) wherever M > 128, 0 = one CTA per 128-row tile, -1 = choose per
  * shape (the default). */
 int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode);
+/* Tuning knob: number of tile row-blocks the persistent scheduler walks before it moves to the next
+ * tile column (the L2 footprint of one wave is group_m row-blocks of A plus slots/group_m column-blocks
+ * of B).  0 = default: 8 for CTA-pair tiles, 16 for single-CTA tiles (about square wave footprints). */
+int aiehlc_set_group_m(aiehlc_ctx* ctx, int group_m);
 /* Tuning knob: 1 (default) = the tensor-core kernels are launched with programmatic stream
  * serialization, so their set-up (barriers, TMEM allocation) overlaps the tail of the kernel before
  * them in the stream; they still wait for that kernel to complete before touching global memory.

@@ -97,8 +97,59 @@ u64 aiehlc_conv_offset_shift(const XAie_ConvArgs* a);
 AieRC XAie_KernelBind(const void* key, const char* name, const void* library_kernel, const void* args,
                       u32 args_bytes, u32 in_addr, u32 out_addr, u32 acc_addr);
 
+/* The kernel-call form k<Col,Row,colstart,rowstart,M,N,K>(in, out) of
+ * example/nokernelload/aie_nokernelload.cc:130 as one blocking call: loads `kernel_key` on tile
+ * (colstart,rowstart) of the device instance initialised last, sets its arguments, moves the GMIO
+ * data at host address `in` to the kernel's input window, runs it, and moves the output window back
+ * to host address `out` (both addresses must lie inside buffers from XAie_MemAllocate).  Col x Row
+ * is the tile grid the caller asked for; the CUDA kernels choose their own grid, so it is validated
+ * (>= 1) and otherwise unused. */
+AieRC XAie_KernelCall(const void* kernel_key, const void* args, u32 args_bytes, int Col, int Row, int colstart,
+                      int rowstart, u64 in, u64 out);
+
 #ifdef __cplusplus
 }  /* extern "C" */
+#endif
+
+#ifdef __cplusplus
+/* C++ declaration of a kernel in the call form.  aiehlc injects
+ *     template <int Col, int Row, int colstart, int rowstart, int M, int N, int K, typename... Args>
+ *     inline void NAME(Args&&... args) { return; }
+ * in front of the user's source (src/llvm/aiehlc.cc:583-588); these macros declare the same template
+ * with a body that runs the kernel, so `NAME<1,1,4,4,16,16,16>(phy, phy_out);` compiles unchanged.
+ * AieRC of the last call: XAie_KernelCallStatus(). */
+inline AieRC& XAie_KernelCallStatus() {
+  static thread_local AieRC rc = XAIE_OK;
+  return rc;
+}
+#define AIEHLC_KERNEL_CALL_MM_I32(NAME)                                                               \
+  template <int Col, int Row, int colstart, int rowstart, int M, int N, int K, typename... Args>      \
+  inline void NAME(Args&&... args) {                                                                  \
+    static_assert(sizeof...(Args) == 2, "kernel call takes (in, out)");                               \
+    const u64 io[2] = {(u64)(args)...};                                                               \
+    const XAie_MmArgs a = {M, N, K};                                                                  \
+    XAie_KernelCallStatus() = XAie_KernelCall((const void*)aiehlc_k_mm_i32, &a, sizeof a, Col, Row,   \
+                                              colstart, rowstart, io[0], io[1]);                      \
+  }
+/* int8 GEMM + srs (shift, split-K fixed at declaration), input window A | B, output window C int8 */
+#define AIEHLC_KERNEL_CALL_GEMM_I8_SRS(NAME, SHIFT, SPLITK)                                           \
+  template <int Col, int Row, int colstart, int rowstart, int M, int N, int K, typename... Args>      \
+  inline void NAME(Args&&... args) {                                                                  \
+    static_assert(sizeof...(Args) == 2, "kernel call takes (in, out)");                               \
+    const u64 io[2] = {(u64)(args)...};                                                               \
+    const XAie_GemmArgs a = {M, N, K, (SHIFT), 0, (SPLITK), 0, 0};                                    \
+    XAie_KernelCallStatus() = XAie_KernelCall((const void*)aiehlc_k_gemm_i8_srs, &a, sizeof a, Col,   \
+                                              Row, colstart, rowstart, io[0], io[1]);                 \
+  }
+#define AIEHLC_KERNEL_CALL_GEMM_I8_I32(NAME)                                                          \
+  template <int Col, int Row, int colstart, int rowstart, int M, int N, int K, typename... Args>      \
+  inline void NAME(Args&&... args) {                                                                  \
+    static_assert(sizeof...(Args) == 2, "kernel call takes (in, out)");                               \
+    const u64 io[2] = {(u64)(args)...};                                                               \
+    const XAie_GemmArgs a = {M, N, K, 0, 0, 1, 0, 0};                                                 \
+    XAie_KernelCallStatus() = XAie_KernelCall((const void*)aiehlc_k_gemm_i8_i32, &a, sizeof a, Col,   \
+                                              Row, colstart, rowstart, io[0], io[1]);                 \
+  }
 #endif
 
 /* Declaration macros: define a symbol with the reference kernel's name and register it before

@@ -43,7 +43,7 @@ def test_every_declared_xaie_symbol_is_exported():
         assert hasattr(lib, n), f"{n} declared in xaiengine.h but not exported"
     for n in _declared_functions(ROOT / "include" / "aiehlc_kernels.h", "aiehlc_"):
         assert hasattr(lib, n), f"{n} declared in aiehlc_kernels.h but not exported"
-    for n in ("XAie_KernelRegister", "XAie_KernelBind"):
+    for n in ("XAie_KernelRegister", "XAie_KernelBind", "XAie_KernelCall"):
         assert hasattr(lib, n)
 
 

@@ -51,6 +51,24 @@ def test_k_slices():
         shard.row_shard(8, 2, 2)
 
 
+def test_gemm_planner_needs_no_gpu():
+    """The tiling plan (counterpart of the compiler's creatematmul + broadcast analysis) is host logic."""
+    from aiehlc_b200.ops import plan_gemm
+    p = plan_gemm(4096, 4096, 4096)                     # the benchmark GEMM: 256 pair tiles on 74 CTA pairs
+    assert (p["tile_m"], p["tile_n"], p["cta_pair"]) == (256, 256, 1)
+    assert (p["grid_m"], p["grid_n"], p["tiles"], p["slots"], p["waves"]) == (16, 16, 256, 74, 4)
+    assert abs(p["wave_efficiency"] - 256 / 296) < 1e-9
+    assert p["k_blocks"] == 32 and p["stages"] == 7 and p["tmem_columns"] == 512 and p["smem_bytes"] <= 227 * 1024
+    assert (p["a_shared_by"], p["b_shared_by"]) == (16, 16)   # A rows serve a grid row, B rows a grid column
+    p = plan_gemm(64, 64, 64)                           # one tile: a single CTA, the narrowest tile
+    assert (p["tile_m"], p["tile_n"], p["cta_pair"], p["tiles"], p["waves"]) == (128, 64, 0, 1, 1)
+    p = plan_gemm(8192, 8192, 8192, kind="bf16")
+    assert p["k_blocks"] == 128 and p["tiles"] == 1024 and p["waves"] == 14
+    from aiehlc_b200 import _capi
+    with pytest.raises(_capi.AiehlcError):
+        plan_gemm(0, 4, 4)
+
+
 _WORKER = textwrap.dedent("""
     import os, sys
     import numpy as np, torch, torch.distributed as dist
@@ -71,12 +89,9 @@ _WORKER = textwrap.dedent("""
     # split-K: rank-local partial over its K slices, then one reduce-scatter of int32 partials
     k0, nk = shard.k_range(K, splitk, world, rank)
     partial = torch.from_numpy(O.gemm_i8_i32(A[:, k0:k0 + nk], B[:, k0:k0 + nk]))
-    out = torch.empty((M // world, N), dtype=torch.int32)
-    chunks = list(partial.chunk(world, dim=0))
-    dist.reduce_scatter(out, chunks, op=dist.ReduceOp.SUM) if dist.get_backend() != "gloo" else None
-    if dist.get_backend() == "gloo":   # gloo has no reduce_scatter: all_reduce then keep the own row block
-        dist.all_reduce(partial, op=dist.ReduceOp.SUM)
-        out = partial[rank * (M // world):(rank + 1) * (M // world)]
+    # gloo has no reduce_scatter: all_reduce, then keep the own row block (same sums, same owner)
+    dist.all_reduce(partial, op=dist.ReduceOp.SUM)
+    out = partial[rank * (M // world):(rank + 1) * (M // world)]
     assert np.array_equal(out.numpy(), full[rank * (M // world):(rank + 1) * (M // world)])
     dist.barrier()
     dist.destroy_process_group()

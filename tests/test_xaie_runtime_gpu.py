@@ -44,6 +44,10 @@ def test_cpp_examples():
         res = subprocess.run([str(exes["cascade_gemm"]), *argv], capture_output=True, text=True, timeout=300)
         assert res.returncode == 0 and "CPU result matches device output." in res.stdout, res.stdout + res.stderr
         assert "kernel launches: 4" in res.stdout
+    # the kernel-call form k<Col,Row,colstart,rowstart,M,N,K>(in, out) of aie_nokernelload.cc:130
+    res = subprocess.run([str(exes["kernel_call"])], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "CPU result matches device output." in res.stdout, res.stdout + res.stderr
+    assert "perf: C[0]=36312 C[255]=2006232, 0 mismatches" in res.stdout
 
 
 # ------------------------------------------------------------------ the same surface through ctypes
