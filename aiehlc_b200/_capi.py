@@ -42,6 +42,7 @@ SIGNATURES = {
     "aiehlc_set_debug": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_pdl": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_group_m": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_set_split_tail": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_trace": (C.c_int, [_vp, _vp]),
     "aiehlc_launch_count": (C.c_longlong, [_vp]),
 }
@@ -54,7 +55,8 @@ class GemmPlan(C.Structure):
                 ("grid_m", C.c_int), ("grid_n", C.c_int), ("tiles", C.c_longlong), ("slots", C.c_int),
                 ("waves", C.c_int), ("wave_efficiency", C.c_double), ("group_m", C.c_int), ("stages", C.c_int),
                 ("smem_bytes", C.c_int), ("tmem_columns", C.c_int), ("k_blocks", C.c_int), ("a_shared_by", C.c_int),
-                ("b_shared_by", C.c_int), ("wave_footprint_bytes", C.c_longlong), ("cost_units", C.c_double)]
+                ("b_shared_by", C.c_int), ("wave_footprint_bytes", C.c_longlong), ("cost_units", C.c_double),
+                ("split_tail_tiles", C.c_int), ("split_tail_parts", C.c_int)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -113,6 +113,7 @@ int aiehlc_destroy(aiehlc_ctx* ctx) {
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   ctx->buf_a.release(); ctx->buf_b.release(); ctx->buf_c.release(); ctx->buf_aux.release();
   ctx->pack_a.release(); ctx->pack_b.release();
+  ctx->sk_scratch.release(); ctx->sk_flags.release();
   delete ctx;
   return AIEHLC_OK;
 }
@@ -146,6 +147,12 @@ int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm
     return plan_gemm(&defaults, kind, M, N, K, plan);
   }
   return plan_gemm(ctx, kind, M, N, K, plan);
+}
+
+int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->split_tail = on ? 1 : 0;
+  return AIEHLC_OK;
 }
 
 int aiehlc_set_group_m(aiehlc_ctx* ctx, int group_m) {
@@ -183,6 +190,11 @@ int aiehlc_sync(aiehlc_ctx* ctx, void* stream, int* status) {
   AIEHLC_CUDA(cudaStreamSynchronize(st));
   const int s = *ctx->h_status;
   if (status) *status = s;
+  if (s != 0 && ctx->sk_flags.ptr) {
+    // a launch gave up half-way: its tail-tile deposit counters may be left non-zero
+    cudaMemsetAsync(ctx->sk_flags.ptr, 0, ctx->sk_flags.bytes, st);
+    cudaStreamSynchronize(st);
+  }
   if (s != 0) return fail(AIEHLC_ERR_DEVICE, "kernel status word = " + std::to_string(s) + " (a bounded wait ran out)");
   return AIEHLC_OK;
 }

@@ -54,6 +54,7 @@ struct aiehlc_ctx {
   aiehlc::EncodeTiledFn encode = nullptr;
   int force_tile_n = 0;
   int pair_mode = -1;           // -1: choose per shape, 0: single-CTA tiles only, 1: CTA pairs wherever M > 128
+  int split_tail = 0;           // cut the tiles of a thin last wave along K across idle CTA pairs (off: no measured gain yet)
   int group_m = 0;              // row-blocks per rasterisation group (0 = default for the kernel family)
   int pdl = 1;                  // launch the tensor-core kernels with programmatic stream serialization
   int debug_mode = 0;           // see GemmParams::debug
@@ -62,6 +63,7 @@ struct aiehlc_ctx {
   std::unordered_map<const void*, aiehlc::KernelSetup> kernel_setup;
   // staging for *_host entry points and for operands that TMA cannot address directly
   aiehlc::DevBuf buf_a, buf_b, buf_c, buf_aux, pack_a, pack_b;
+  aiehlc::DevBuf sk_scratch, sk_flags;  // partial sums and deposit counters of split tail tiles
 };
 
 namespace aiehlc {
@@ -83,6 +85,8 @@ struct GemmCall {
 };
 int launch_gemm(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st);
 int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* out);
+// Tail balancing: tiles [first, tiles) are cut into `parts` K ranges (parts == 1: no cut).
+void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int* parts);
 
 // SIMT helpers (simt_kernels.cu)
 int launch_mm_i32(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K, cudaStream_t st);

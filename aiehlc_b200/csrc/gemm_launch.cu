@@ -39,6 +39,23 @@ int encode_kmajor_map(aiehlc_ctx* ctx, CUtensorMap* map, int kind, const void* b
 // the operand traffic per SM (measured on int8 8192^3: 373 us against 391 us).
 }  // namespace
 
+// When the last wave of a persistent launch is at most half full, its tiles are cut along K into as
+// many ranges as there are idle slots per tile (at most 4, at least 8 K-blocks each).
+void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int* parts) {
+  *first = tiles;
+  *parts = 1;
+  if (!enabled || slots <= 0) return;
+  const int rem = tiles % slots;
+  if (rem == 0 || rem * 2 > slots) return;
+  int s = slots / rem;
+  if (s > 4) s = 4;
+  while (s > 1 && k_blocks / s < 8) --s;
+  if (s > 1) {
+    *first = tiles - rem;
+    *parts = s;
+  }
+}
+
 // The planner: B200 counterpart of the compiler's matmul tiling (tilinglinalg::creatematmul,
 // src/mlir/mlirfront/tilinglinalg/tilinglinalg.cpp:38-146: grid of tiles + per-tile block) and of
 // its data-pattern analysis (tilingpass.cpp:98-150: which operand is broadcast along which grid
@@ -94,6 +111,10 @@ int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_
   best.wave_footprint_bytes = (static_cast<long long>(g) * best.tile_m +
                                (wave_cols < best.grid_n ? wave_cols : best.grid_n) * best.tile_n) *
                               static_cast<long long>(K) * esize;
+  int first = 0, parts = 1;
+  split_tail(static_cast<int>(best.tiles), best.slots, best.k_blocks, best.cta_pair ? ctx->split_tail : 0, &first, &parts);
+  best.split_tail_tiles = parts > 1 ? static_cast<int>(best.tiles) - first : 0;
+  best.split_tail_parts = parts;
   *out = best;
   return AIEHLC_OK;
 }
@@ -217,7 +238,28 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
     cfg.numAttrs = na;
   }
   max_pairs = ks.max_clusters;
-  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  int pairs = tiles < max_pairs ? tiles : max_pairs;
+  // Tail balancing (int32 accumulation only: sums of partial sums are exact; fp32 would change rounding)
+  p.sk_first_tile = tiles;
+  p.sk_parts = 1;
+  if (kKind == KIND_I8) {
+    split_tail(tiles, tiles < max_pairs ? max_pairs : pairs, p.num_k_blocks, ctx->split_tail, &p.sk_first_tile, &p.sk_parts);
+    if (p.sk_parts > 1) {
+      const int tail = tiles - p.sk_first_tile;
+      const size_t cta_ints = static_cast<size_t>(kBN / 32) * kSkChunkInts;
+      const size_t scratch_bytes = static_cast<size_t>(tail) * p.sk_parts * 2 * cta_ints * sizeof(int32_t);
+      const size_t flag_bytes = static_cast<size_t>(tail) * 2 * 4 * sizeof(int);
+      if (ctx->sk_scratch.reserve(scratch_bytes)) return AIEHLC_ERR_NOMEM;
+      if (flag_bytes > ctx->sk_flags.bytes) {
+        if (ctx->sk_flags.reserve(flag_bytes)) return AIEHLC_ERR_NOMEM;
+        AIEHLC_CUDA(cudaMemset(ctx->sk_flags.ptr, 0, ctx->sk_flags.bytes));  // counters start at zero
+      }
+      p.sk_scratch = static_cast<int32_t*>(ctx->sk_scratch.ptr);
+      p.sk_flags = static_cast<int*>(ctx->sk_flags.ptr);
+      const int units = p.sk_first_tile + tail * p.sk_parts;
+      pairs = units < max_pairs ? units : max_pairs;
+    }
+  }
   cfg.gridDim = dim3(2 * pairs);
   AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
   ctx->launches++;

@@ -51,6 +51,13 @@ struct GemmParams {
   int group_m;             // rasterisation: tiles walk group_m row-blocks before the next column
   int vec_ok;              // C (and acc_in) rows are 16-byte aligned: vector stores allowed
   int* status;             // device status word (0 = ok)
+  // Tail balancing of the pair kernel: tiles >= sk_first_tile are cut into sk_parts K ranges that
+  // run on different CTA pairs.  Each range owns a share of the tile's column chunks: it deposits
+  // the int32 partial sums of the other chunks in sk_scratch, adds what the other ranges deposited
+  // to its own chunks and runs the output stage on them.  sk_parts == 1: every tile is computed whole.
+  int sk_first_tile, sk_parts;
+  int32_t* sk_scratch;     // [tail tile][depositing range][CTA rank][32-column chunk] partial sums
+  int* sk_flags;           // [tail tile][CTA rank][owning range (4 slots)] deposits so far; zero between launches
   long long* trace;        // measurement aid: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
   int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling)
 };

@@ -34,6 +34,61 @@ struct PairSmem {
   static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;
 };
 
+// One unit of work of a CTA pair: a whole tile, or one K range of a tail tile.
+struct WorkUnit {
+  int tile, kb0, kb1, part, parts;
+};
+// Unit number `u` of the launch (pair p runs units p, p + pairs, p + 2 pairs, ...).
+__device__ __forceinline__ bool work_unit(int u, const GemmParams& p, int num_tiles, WorkUnit& w) {
+  if (u < p.sk_first_tile) {
+    w = WorkUnit{u, 0, p.num_k_blocks, 0, 1};
+    return true;
+  }
+  const int v = u - p.sk_first_tile;
+  if (p.sk_parts <= 1 || v >= (num_tiles - p.sk_first_tile) * p.sk_parts) {
+    if (p.sk_parts > 1 || u >= num_tiles) return false;
+    w = WorkUnit{u, 0, p.num_k_blocks, 0, 1};
+    return true;
+  }
+  const int part = v % p.sk_parts;
+  w.tile = p.sk_first_tile + v / p.sk_parts;
+  w.part = part;
+  w.parts = p.sk_parts;
+  w.kb0 = static_cast<int>(static_cast<long long>(part) * p.num_k_blocks / p.sk_parts);
+  w.kb1 = static_cast<int>(static_cast<long long>(part + 1) * p.num_k_blocks / p.sk_parts);
+  return true;
+}
+
+constexpr int kSkChunkInts = kBlockM * 32;  // one 32-column chunk of a CTA's 128 accumulator rows
+
+// The K ranges of a tail tile share the output stage: range q owns the 32-column chunks c with
+// (c * parts) / chunks == q.  Every range deposits the chunks it does not own as raw 32-bit words,
+// then adds the other ranges' deposits to the chunks it owns and runs the output stage on them.
+// Layout of a deposited chunk: [warp quadrant][j = 0..7][lane][4 words], so that every store or
+// load instruction of a warp moves 512 contiguous bytes (the layout never leaves this file).
+__device__ __forceinline__ void deposit_chunk(const uint32_t (&r)[32], int32_t* chunk, int quad, int lane) {
+  int4* dst = reinterpret_cast<int4*>(chunk + quad * 1024) + lane;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) dst[j * 32] = make_int4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+}
+// Loads only: the values are consumed an iteration later, so the round trip to L2 overlaps other work.
+__device__ __forceinline__ void load_deposited_chunk(uint32_t (&d)[32], const int32_t* chunk, int quad, int lane) {
+  const int4* src = reinterpret_cast<const int4*>(chunk + quad * 1024) + lane;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int4 v = src[j * 32];
+    d[4 * j] = v.x; d[4 * j + 1] = v.y; d[4 * j + 2] = v.z; d[4 * j + 3] = v.w;
+  }
+}
+__device__ __forceinline__ void add_deposited_chunk(uint32_t (&r)[32], const int32_t* chunk, int quad, int lane) {
+  const int4* src = reinterpret_cast<const int4*>(chunk + quad * 1024) + lane;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int4 v = src[j * 32];
+    r[4 * j] += v.x; r[4 * j + 1] += v.y; r[4 * j + 2] += v.z; r[4 * j + 3] += v.w;
+  }
+}
+
 template <int kKind, int kBN, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -56,6 +111,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;                // used in the leader CTA
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  int* sk_warps_done = reinterpret_cast<int*>(tmem_base_slot + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -76,6 +132,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(smem_u32(&tmem_empty_bar[a]), 8);  // 4 epilogue warps in each of the two CTAs
     }
     *abort_flag = 0;
+    *sk_warps_done = 0;
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -105,10 +162,11 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+      WorkUnit w;
+      for (int u = pair_id; ok && work_unit(u, p, num_tiles, w); u += num_pairs) {
         int mb, nb;
-        tile_coords(t, p, mb, nb);
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        tile_coords(w.tile, p, mb, nb);
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
           if (!ok) break;
           const uint32_t fb_local = smem_u32(&full_bar[stage]);
@@ -139,7 +197,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+      WorkUnit w;
+      for (int u = pair_id; ok && work_unit(u, p, num_tiles, w); u += num_pairs, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status,
@@ -148,7 +207,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tc_fence_after();
         if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
           if (!ok) break;
           tc_fence_after();
@@ -159,7 +218,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (p.debug != 2) {
 #pragma unroll
             for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
-              umma_ss<kKind, 2>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_ss<kKind, 2>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair_mask(smem_u32(&empty_bar[stage]), 3);  // frees the stage in both CTAs
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -173,9 +232,10 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int quad = warp & 3;
     int it = 0;
     bool ok = true;
-    for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+    WorkUnit w;
+    for (int u = pair_id; ok && work_unit(u, p, num_tiles, w); u += num_pairs, ++it) {
       int mb, nb;
-      tile_coords(t, p, mb, nb);
+      tile_coords(w.tile, p, mb, nb);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const bool tracer = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0;
@@ -185,10 +245,86 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (!ok) break;
       tc_fence_after();
       if (tracer) p.trace[it * 8 + 3] = clock64();
-      const int row = mb * kPairM + static_cast<int>(rank) * kBlockM + quad * 32 + lane;
+      const int lane_row = quad * 32 + lane;
+      const int row = mb * kPairM + static_cast<int>(rank) * kBlockM + lane_row;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
-      drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN);
+      if (w.parts == 1) {
+        drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN);
+      } else {
+        // tail tile cut along K; scratch is [tail tile][depositing range][CTA rank][chunk]
+        constexpr int kChunks = kBN / 32;
+        constexpr long long kCtaInts = static_cast<long long>(kChunks) * kSkChunkInts;
+        const long long part_stride = 2 * kCtaInts;
+        const int tail = w.tile - p.sk_first_tile;
+        int32_t* tile_base = p.sk_scratch + static_cast<long long>(tail) * w.parts * part_stride + rank * kCtaInts;
+        int* flags = p.sk_flags + (tail * 2 + static_cast<int>(rank)) * 4;  // one counter per owning range
+        // 1. hand the chunks owned by other ranges over
+#pragma unroll 1
+        for (int c = 0; c < kChunks; ++c) {
+          if ((c * w.parts) / kChunks == w.part) continue;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          deposit_chunk(r, tile_base + w.part * part_stride + c * kSkChunkInts, quad, lane);
+        }
+        __syncwarp();
+        if (lane == 0)
+          for (int q = 0; q < w.parts; ++q)
+            if (q != w.part) red_release_gpu_add(flags + q, 1);  // one arrival per epilogue warp
+        if (tracer && it >= 2) p.trace[it * 8 + 5] = clock64();
+        // 2. wait (bounded) for the 4 warps of every other range of this tile and CTA rank
+        const int want = 4 * (w.parts - 1);
+        if (lane == 0) {
+          const long long t0 = clock64();
+          while (ld_acquire_gpu(flags + w.part) < want) {
+            if (*abort_flag) { ok = false; break; }
+            if (clock64() - t0 > kWaitLimitCycles) {
+              *abort_flag = 1;
+              atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
+              ok = false;
+              break;
+            }
+          }
+        }
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (tracer && it >= 2) p.trace[it * 8 + 6] = clock64();
+        if (ok) {
+          // 3. own chunks: accumulator + the other ranges' deposits, then the output stage.  The
+          //    deposits of the next chunk are requested before the current one is processed: they come
+          //    from L2 and one round trip per chunk would otherwise be the critical path.
+          const int c_begin = (w.part * kChunks + w.parts - 1) / w.parts;
+          const int c_end = ((w.part + 1) * kChunks + w.parts - 1) / w.parts;
+          // first other range: prefetched one chunk ahead; further ranges (parts > 2): added in place
+          const int q0 = w.part == 0 ? 1 : 0;
+          const int32_t* src0 = tile_base + q0 * part_stride;
+          uint32_t dep[32], dep_next[32];
+          if (c_begin < c_end) load_deposited_chunk(dep, src0 + c_begin * kSkChunkInts, quad, lane);
+#pragma unroll 1
+          for (int c = c_begin; c < c_end; ++c) {
+            __syncwarp();
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c * 32, r);
+            if (c + 1 < c_end) load_deposited_chunk(dep_next, src0 + (c + 1) * kSkChunkInts, quad, lane);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] += dep[j];
+            for (int q = 0; q < w.parts; ++q)
+              if (q != w.part && q != q0) add_deposited_chunk(r, tile_base + q * part_stride + c * kSkChunkInts, quad, lane);
+            if (row_ok && nb * kBN + c * 32 < p.N) store_chunk<kEpi>(p, r, row, nb * kBN + c * 32);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) dep[j] = dep_next[j];
+          }
+          // 4. the last of the four warps to finish puts this range's counter back to zero for the next
+          //    launch (by then every warp is past its wait).  No blocking barrier: a warp that gave up on
+          //    its wait must not be able to strand the others.
+          __syncwarp();
+          if (lane == 0 && atomicAdd(sk_warps_done, 1) == 3) {
+            *sk_warps_done = 0;
+            flags[w.part] = 0;
+          }
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (tracer) p.trace[it * 8 + 4] = clock64();

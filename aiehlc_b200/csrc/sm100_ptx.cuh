@@ -210,6 +210,16 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 
 
+// ------------------------------------------------------------------ cross-CTA flags in global memory
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // ---------------------------------------------------------------- CTA pairs (cluster of two)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

@@ -67,6 +67,9 @@ class Context:
     def set_cta_pair(self, mode: int) -> None:
         _capi.check(self._lib.aiehlc_set_cta_pair(self._h, int(mode)))
 
+    def set_split_tail(self, on: bool) -> None:
+        _capi.check(self._lib.aiehlc_set_split_tail(self._h, 1 if on else 0))
+
     def set_group_m(self, group_m: int) -> None:
         _capi.check(self._lib.aiehlc_set_group_m(self._h, int(group_m)))
 

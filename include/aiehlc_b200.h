@@ -134,6 +134,8 @@ typedef struct {
   int b_shared_by;                   /* tiles reading the same rows of B (B is shared along the M grid dimension) */
   long long wave_footprint_bytes;    /* operand bytes the tiles of one wave touch (L2 working set) */
   double cost_units;                 /* the quantity the choice minimises: waves x tile_n / efficiency factor */
+  int split_tail_tiles;              /* tiles of a thin last wave that are cut along K (int8 pair kernel), else 0 */
+  int split_tail_parts;              /* K ranges per such tile (1 = none) */
 } aiehlc_gemm_plan;
 /* kind: 0 = int8, 1 = bf16.  ctx may be NULL: the plan is then made for a 148-SM B200 with default knobs. */
 int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* plan);
@@ -165,6 +167,12 @@ int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n);
  * fetching half of the B tile) wherever M > 128, 0 = one CTA per 128-row tile, -1 = choose per
  * shape (the default). */
 int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode);
+/* Tuning knob: 1 = when the last wave of an int8 CTA-pair launch is at most half full, its tiles are
+ * cut along K across the idle pairs; the K ranges of a tile exchange int32 partial sums through a
+ * context workspace and each runs the output stage on its share of the columns (integer sums:
+ * bit-identical results).  0 (default) = every tile computed whole: on the 4096^3 benchmark the
+ * exchange costs about what the shorter main loop saves. */
+int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on);
 /* Tuning knob: number of tile row-blocks the persistent scheduler walks before it moves to the next
  * tile column (the L2 footprint of one wave is group_m row-blocks of A plus slots/group_m column-blocks
  * of B).  0 = default: 8 for CTA-pair tiles, 16 for single-CTA tiles (about square wave footprints). */

@@ -132,6 +132,36 @@ def test_split_k_in_one_launch_and_as_cascade(ctx, splitk):
     assert np.array_equal(ctx.gemm_i8_srs_cascade(dA, dB, splitk, shift=8).cpu().numpy(), unsplit)
 
 
+@pytest.mark.parametrize("shape", [(1024, 1024, 4096), (512, 768, 2048), (1000, 900, 4112), (2304, 256, 4096),
+                                   (256, 256, 8192)])
+def test_split_tail_tiles_are_bit_identical(ctx, shape):
+    """A thin last wave is cut along K across idle CTA pairs (partial sums meet in a workspace):
+    same bits as the oracle and as the uncut schedule, launch after launch (the deposit counters
+    return to zero), for the int32 and the srs output stages."""
+    from aiehlc_b200.ops import plan_gemm
+    M, N, K = shape
+    ctx.set_cta_pair(1)
+    ctx.set_split_tail(True)
+    try:
+        plan = plan_gemm(M, N, K, ctx=ctx)
+        assert plan["split_tail_parts"] > 1, plan
+        A = synth.int8_uniform(6, (M, K))
+        B = synth.int8_uniform(1006, (N, K))
+        dA, dB = _dev(A), _dev(B)
+        exp32 = O.gemm_i8_i32(A, B)
+        exp8 = O.gemm_i8_srs(A, B, shift=9)
+        for _ in range(3):
+            assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), exp32)
+            assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift=9).cpu().numpy(), exp8)
+        ctx.set_split_tail(False)
+        assert plan_gemm(M, N, K, ctx=ctx)["split_tail_parts"] == 1
+        assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), exp32)
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_split_tail(False)
+        ctx.set_cta_pair(-1)
+
+
 def test_accumulate_and_flush(ctx):
     M, N, K = 200, 136, 512
     A = synth.int8_uniform(2, (M, K))
