@@ -106,6 +106,14 @@ struct XAie_RoutingInstance {
   std::vector<std::pair<u16, u16>> edges;
 };
 
+struct XAie_Graph {
+  Runtime* rt = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  cudaEvent_t done = nullptr;
+  bool launched = false;
+};
+
 namespace {
 
 inline u16 loc_key(XAie_LocType l) { return static_cast<u16>((l.Col << 8) | l.Row); }
@@ -120,6 +128,7 @@ struct Runtime {
   std::vector<XAie_RoutingInstance*> routes;
   u64 launches = 0;
   u32 inject_status = 0, inject_count = 0;
+  bool capturing = false;   // between XAie_GraphBeginCapture and XAie_GraphEndCapture
 
   bool is_shim(XAie_LocType l) const { return l.Row == dev->Cfg.ShimRowNum; }
   bool valid_loc(XAie_LocType l) const {
@@ -167,6 +176,7 @@ struct Runtime {
     const size_t need = static_cast<size_t>(addr - start) + bytes;
     if (Region* r = find_window(t, start)) {
       if (need > r->cap) {
+        if (capturing) return fail(XAIE_ERR, "a tile window would have to grow while a graph is being recorded; run the sequence once before recording it");
         void* p = nullptr;
         cudaError_t e = cudaMalloc(&p, need);
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(tile window)");
@@ -239,7 +249,7 @@ AieRC t2h(Runtime* rt, XAie_LocType src, u64 tile_addr, void* dst, size_t bytes)
   if (n)
     XCUDA(cudaMemcpyAsync(dst, static_cast<uint8_t*>(r->dptr) + (tile_addr - r->addr), n,
                           cudaMemcpyDeviceToHost, rt->stream));
-  XCUDA(cudaStreamSynchronize(rt->stream));
+  if (!rt->capturing) XCUDA(cudaStreamSynchronize(rt->stream));  // a recorded copy lands when the graph runs
   if (bytes > n) memset(static_cast<uint8_t*>(dst) + n, 0, bytes - n);
   return XAIE_OK;
 }
@@ -295,8 +305,10 @@ AieRC launch_tile(Runtime* rt, Tile& t, u32 count) {
     }
     rt->launches++;
   }
-  if (!t.done) XCUDA(cudaEventCreateWithFlags(&t.done, cudaEventDisableTiming));
-  XCUDA(cudaEventRecord(t.done, rt->stream));
+  if (!rt->capturing) {
+    if (!t.done) XCUDA(cudaEventCreateWithFlags(&t.done, cudaEventDisableTiming));
+    XCUDA(cudaEventRecord(t.done, rt->stream));
+  }
   t.launched = true;
   t.armed = false;
   return XAIE_OK;
@@ -446,6 +458,7 @@ static AieRC poll_done(Runtime* rt, Tile& t) {
   }
   if (!t.loaded) return fail(XAIE_INVALID_TILE, "no kernel loaded on this tile");
   if (!t.launched) return fail(XAIE_CORE_STATUS_TIMEOUT, "tile has not been run");
+  if (rt->capturing) return XAIE_OK;  // recording: ordering is the graph's, completion is XAie_GraphWait's
   cudaError_t e = cudaEventQuery(t.done);
   if (e == cudaErrorNotReady) return XAIE_CORE_STATUS_TIMEOUT;
   if (e != cudaSuccess) return cuda_fail(e, "cudaEventQuery");
@@ -583,7 +596,7 @@ AieRC XAie_MemSyncForDev(XAie_MemInst* m) {
 AieRC XAie_MemSyncForCPU(XAie_MemInst* m) {
   if (!m) return fail(XAIE_INVALID_ARGS, "null buffer");
   XCUDA(cudaSetDevice(m->rt->device));
-  XCUDA(cudaStreamSynchronize(m->rt->stream));
+  if (!m->rt->capturing) XCUDA(cudaStreamSynchronize(m->rt->stream));
   return XAIE_OK;
 }
 
@@ -608,7 +621,7 @@ AieRC XAie_Route(XAie_RoutingInstance* ri, void*, XAie_LocType s, XAie_LocType d
 AieRC XAie_RouteDmaWait(XAie_RoutingInstance* ri, XAie_LocType, XAie_LocType, u8) {
   if (!ri) return fail(XAIE_INVALID_ARGS, "null routing instance");
   XCUDA(cudaSetDevice(ri->rt->device));
-  XCUDA(cudaStreamSynchronize(ri->rt->stream));
+  if (!ri->rt->capturing) XCUDA(cudaStreamSynchronize(ri->rt->stream));
   return XAIE_OK;
 }
 
@@ -708,7 +721,7 @@ AieRC XAie_DataMemBlockWrite(XAie_DevInst* DevInst, XAie_LocType Loc, u64 Addr, 
   if (!Src) return fail(XAIE_INVALID_ARGS, "null source");
   rc = h2t(rt, Loc, Addr, Src, Size);
   if (rc != XAIE_OK) return rc;
-  XCUDA(cudaStreamSynchronize(rt->stream));  // Src may be pageable and short-lived
+  if (!rt->capturing) XCUDA(cudaStreamSynchronize(rt->stream));  // Src may be pageable and short-lived
   return XAIE_OK;
 }
 
@@ -723,6 +736,96 @@ AieRC XAie_DebugInjectStatus(XAie_DevInst* DevInst, u32 Status, u32 Count) {
   if (rc != XAIE_OK) return rc;
   rt->inject_status = Status;
   rt->inject_count = Count;
+  return XAIE_OK;
+}
+
+// ---------------------------------------------------------------------------------- recorded chains
+// The reference drives a chain of kernels with a host round trip per stage (run, poll, move, run,
+// ...: example/multi/multi_tile.cpp:105-145, seq_full_col.cpp:132-153).  The same call sequence can
+// be recorded once into a CUDA graph and replayed with one launch: intermediates stay on the device,
+// the host re-enters only to wait for the whole chain.
+AieRC XAie_GraphBeginCapture(XAie_DevInst* DevInst) {
+  Runtime* rt;
+  AieRC rc = need_rt(DevInst, &rt);
+  if (rc != XAIE_OK) return rc;
+  if (rt->capturing) return fail(XAIE_ERR, "a graph is already being recorded on this device instance");
+  XCUDA(cudaStreamSynchronize(rt->stream));
+  aiehlc_set_pdl(rt->ctx, 0);  // plain kernel nodes inside the graph
+  cudaError_t e = cudaStreamBeginCapture(rt->stream, cudaStreamCaptureModeRelaxed);
+  if (e != cudaSuccess) {
+    aiehlc_set_pdl(rt->ctx, 1);
+    return cuda_fail(e, "cudaStreamBeginCapture");
+  }
+  rt->capturing = true;
+  return XAIE_OK;
+}
+
+AieRC XAie_GraphEndCapture(XAie_DevInst* DevInst, XAie_Graph** Out) {
+  Runtime* rt;
+  AieRC rc = need_rt(DevInst, &rt);
+  if (rc != XAIE_OK) return rc;
+  if (!Out) return fail(XAIE_INVALID_ARGS, "null graph pointer");
+  *Out = nullptr;
+  if (!rt->capturing) return fail(XAIE_ERR, "no graph is being recorded");
+  rt->capturing = false;
+  aiehlc_set_pdl(rt->ctx, 1);
+  cudaGraph_t g = nullptr;
+  cudaError_t e = cudaStreamEndCapture(rt->stream, &g);
+  if (e != cudaSuccess || !g) return cuda_fail(e, "cudaStreamEndCapture");
+  XAie_Graph* gr = new XAie_Graph();
+  gr->rt = rt;
+  gr->graph = g;
+  e = cudaGraphInstantiate(&gr->exec, g, 0);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&gr->done, cudaEventDisableTiming);
+  if (e != cudaSuccess) {
+    cuda_fail(e, "cudaGraphInstantiate");
+    if (gr->exec) cudaGraphExecDestroy(gr->exec);
+    cudaGraphDestroy(g);
+    delete gr;
+    return XAIE_ERR_DEVICE;
+  }
+  *Out = gr;
+  return XAIE_OK;
+}
+
+AieRC XAie_GraphLaunch(XAie_Graph* Graph) {
+  if (!Graph) return fail(XAIE_INVALID_ARGS, "null graph");
+  Runtime* rt = Graph->rt;
+  XCUDA(cudaSetDevice(rt->device));
+  if (rt->capturing) return fail(XAIE_ERR, "cannot launch a graph while another one is being recorded");
+  XCUDA(cudaGraphLaunch(Graph->exec, rt->stream));
+  XCUDA(cudaEventRecord(Graph->done, rt->stream));
+  Graph->launched = true;
+  return XAIE_OK;
+}
+
+AieRC XAie_GraphWait(XAie_Graph* Graph, u32 TimeOut) {
+  if (!Graph) return fail(XAIE_INVALID_ARGS, "null graph");
+  if (!Graph->launched) return fail(XAIE_CORE_STATUS_TIMEOUT, "graph has not been launched");
+  Runtime* rt = Graph->rt;
+  XCUDA(cudaSetDevice(rt->device));
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::microseconds(TimeOut);
+  for (;;) {
+    cudaError_t e = cudaEventQuery(Graph->done);
+    if (e == cudaSuccess) break;
+    if (e != cudaErrorNotReady) return cuda_fail(e, "cudaEventQuery");
+    if (TimeOut == 0 || std::chrono::steady_clock::now() >= deadline) return XAIE_CORE_STATUS_TIMEOUT;
+    std::this_thread::yield();
+  }
+  int status = 0;
+  if (aiehlc_sync(rt->ctx, rt->stream, &status) != AIEHLC_OK)
+    return fail(XAIE_ERR_DEVICE, status ? "kernel status word = " + std::to_string(status) : std::string(aiehlc_last_error()));
+  return XAIE_OK;
+}
+
+AieRC XAie_GraphDestroy(XAie_Graph* Graph) {
+  if (!Graph) return XAIE_OK;
+  cudaSetDevice(Graph->rt->device);
+  cudaStreamSynchronize(Graph->rt->stream);
+  if (Graph->exec) cudaGraphExecDestroy(Graph->exec);
+  if (Graph->graph) cudaGraphDestroy(Graph->graph);
+  if (Graph->done) cudaEventDestroy(Graph->done);
+  delete Graph;
   return XAIE_OK;
 }
 

@@ -185,6 +185,22 @@ AieRC XAie_Run(XAie_RoutingInstance* RoutingInstance, u32 Count);
 AieRC XAie_DataMemBlockRead(XAie_DevInst* DevInst, XAie_LocType Loc, u64 Addr, void* Dst, u32 Size);
 AieRC XAie_DataMemBlockWrite(XAie_DevInst* DevInst, XAie_LocType Loc, u64 Addr, const void* Src, u32 Size);
 
+/* ---- recorded chains (no counterpart in aie-rt) ----------------------------------------------
+ * The examples drive a kernel chain with a host round trip per stage (run, poll, move tile->tile,
+ * run, ...: example/multi/multi_tile.cpp:105-145).  Between BeginCapture and EndCapture the same
+ * calls (XAie_MoveData*, XAie_Run; XAie_CoreWaitForDone returns XAIE_OK at once) are recorded into a
+ * CUDA graph instead of being executed.  XAie_GraphLaunch replays the whole chain with one launch and
+ * returns immediately; XAie_GraphWait polls for its completion like XAie_CoreWaitForDone (TimeOut in
+ * microseconds, 0 = poll once).  GMIO buffers are read and written when the graph runs, so new input
+ * is: fill the buffer, launch, wait, read the output buffer.  Run the sequence once normally before
+ * recording it (tile windows must already have their size), and record again if a window grows. */
+typedef struct XAie_Graph XAie_Graph;
+AieRC XAie_GraphBeginCapture(XAie_DevInst* DevInst);
+AieRC XAie_GraphEndCapture(XAie_DevInst* DevInst, XAie_Graph** Graph);
+AieRC XAie_GraphLaunch(XAie_Graph* Graph);
+AieRC XAie_GraphWait(XAie_Graph* Graph, u32 TimeOut);
+AieRC XAie_GraphDestroy(XAie_Graph* Graph);
+
 /* ---- additions for parameterised kernels (no counterpart in aie-rt) ------------------------- */
 /* Per-tile kernel arguments (a struct from aiehlc_kernels.h); copied. */
 AieRC XAie_KernelSetArgs(XAie_DevInst* DevInst, XAie_LocType Loc, const void* Args, u32 Bytes);

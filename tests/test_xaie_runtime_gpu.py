@@ -108,6 +108,12 @@ def xaie():
         "XAie_LastError": (C.c_char_p, []),
         "XAie_LaunchCount": (u64, [C.POINTER(DevInst)]),
         "aiehlc_window_offset_b": (u64, [vp, u32]),
+        "XAie_MoveData": (C.c_int, [vp, Loc, vp, u32, vp, Loc]),
+        "XAie_GraphBeginCapture": (C.c_int, [C.POINTER(DevInst)]),
+        "XAie_GraphEndCapture": (C.c_int, [C.POINTER(DevInst), C.POINTER(vp)]),
+        "XAie_GraphLaunch": (C.c_int, [vp]),
+        "XAie_GraphWait": (C.c_int, [vp, u32]),
+        "XAie_GraphDestroy": (C.c_int, [vp]),
     }
     for n, (r, a) in sig.items():
         getattr(lib, n).restype = r
@@ -199,3 +205,62 @@ def test_failure_paths_return_codes(xaie):
     st = C.c_uint32(9)
     assert lib.XAie_CoreGetStatus(C.byref(dev), Loc(4, 4), C.byref(st)) == XAIE_OK and st.value == 1
     assert lib.XAie_CoreGetStatus(C.byref(dev), Loc(1, 4), C.byref(st)) == XAIE_OK and st.value == 0
+
+
+def test_recorded_chain_replays_with_new_inputs(xaie):
+    """A two-stage cascade (K slice 0 -> int32 partials -> tile-to-tile move -> K slice 1 + srs) recorded
+    once as a graph and replayed: every replay reads the GMIO buffers afresh and matches the oracle."""
+    lib, dev = xaie
+    M, N, K = 192, 160, 512
+    ks = K // 2
+    t0, t1, shim = Loc(3, 4), Loc(4, 4), Loc(0, 2)
+    assert lib.XAie_LoadElfMem(C.byref(dev), t0, _kernel(lib, "aiehlc_k_gemm_i8_i32")) == XAIE_OK
+    assert lib.XAie_LoadElfMem(C.byref(dev), t1, _kernel(lib, "aiehlc_k_gemm_i8_srs")) == XAIE_OK
+    a0 = GemmArgs(M, N, ks, 0, 0, 1, 0, 0)
+    a1 = GemmArgs(M, N, ks, 8, 0, 1, 0, 1)            # use_acc: add the partials handed down by stage 0
+    lib.XAie_KernelSetArgs(C.byref(dev), t0, C.byref(a0), C.sizeof(a0))
+    lib.XAie_KernelSetArgs(C.byref(dev), t1, C.byref(a1), C.sizeof(a1))
+    ri = lib.XAie_InitRoutingHandler(C.byref(dev))
+    for s_, d_ in ((shim, t0), (shim, t1), (t0, t1), (t1, shim)):
+        assert lib.XAie_Route(ri, None, s_, d_) == XAIE_OK
+    off_b = lib.aiehlc_window_offset_b(C.byref(a0), 1)
+    win = off_b + N * ks
+    mems = [lib.XAie_MemAllocate(C.byref(dev), win, 0) for _ in range(2)]
+    mem_out = lib.XAie_MemAllocate(C.byref(dev), M * N, 0)
+    bufs = [_host_array(lib, m, win, np.int8) for m in mems]
+    out = _host_array(lib, mem_out, M * N, np.int8)
+
+    def fill(seed):
+        A = synth.int8_uniform(seed, (M, K))
+        B = synth.int8_uniform(seed + 1000, (N, K))
+        for s_ in range(2):
+            bufs[s_][:M * ks] = A[:, s_ * ks:(s_ + 1) * ks].ravel()
+            bufs[s_][off_b:off_b + N * ks] = B[:, s_ * ks:(s_ + 1) * ks].ravel()
+        return O.gemm_i8_srs(A, B, shift=8, splitk=2)
+
+    def chain():
+        assert lib.XAie_MoveDataExternal2Aie(ri, shim, mems[0], win, 0x1000, t0) == XAIE_OK
+        assert lib.XAie_Run(ri, 1) == XAIE_OK, lib.XAie_LastError()
+        assert lib.XAie_MoveData(ri, t0, C.c_void_p(0x6000), M * N * 4, C.c_void_p(0x3000), t1) == XAIE_OK
+        assert lib.XAie_MoveDataExternal2Aie(ri, shim, mems[1], win, 0x1000, t1) == XAIE_OK
+        assert lib.XAie_Run(ri, 1) == XAIE_OK, lib.XAie_LastError()
+        assert lib.XAie_MoveDataAie2External(ri, t1, 0x6000, M * N, mem_out, shim) == XAIE_OK
+
+    exp = fill(11)
+    chain()                                               # plain run: sizes every tile window
+    assert lib.XAie_CoreWaitForDone(C.byref(dev), t1, 5_000_000) == XAIE_OK
+    assert np.array_equal(out.reshape(M, N), exp)
+    launches_before = lib.XAie_LaunchCount(C.byref(dev))
+
+    assert lib.XAie_GraphBeginCapture(C.byref(dev)) == XAIE_OK, lib.XAie_LastError()
+    chain()                                               # recorded, not executed
+    graph = C.c_void_p()
+    assert lib.XAie_GraphEndCapture(C.byref(dev), C.byref(graph)) == XAIE_OK, lib.XAie_LastError()
+    for seed in (21, 22, 23):
+        exp = fill(seed)
+        out[:] = 0x55
+        assert lib.XAie_GraphLaunch(graph) == XAIE_OK, lib.XAie_LastError()
+        assert lib.XAie_GraphWait(graph, 5_000_000) == XAIE_OK, lib.XAie_LastError()
+        assert np.array_equal(out.reshape(M, N), exp)
+    assert lib.XAie_LaunchCount(C.byref(dev)) == launches_before + 2     # recording issued the two launches once
+    assert lib.XAie_GraphDestroy(graph) == XAIE_OK
