@@ -36,6 +36,8 @@ SIGNATURES = {
     "aiehlc_gemm_bf16_host": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int]),
     "aiehlc_conv2d_i8_srs_dev": (C.c_int, [_vp, _vp, _vp, _vp] + [C.c_int] * 8 + [_vp, _vp]),
     "aiehlc_conv2d_i8_srs_host": (C.c_int, [_vp, _vp, _vp, _vp] + [C.c_int] * 8 + [_vp]),
+    "aiehlc_conv2d_pack_weights_dev": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
+    "aiehlc_conv2d_i8_srs_packed_dev": (C.c_int, [_vp, _vp, _vp, _vp] + [C.c_int] * 8 + [_vp, _vp]),
     "aiehlc_conv2d_i8_srs_static_dev": (C.c_int, [_vp, _vp, _vp, _vp] + [C.c_int] * 8 + [_vp, _vp]),
     "aiehlc_set_tile_n": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_cta_pair": (C.c_int, [_vp, C.c_int]),

@@ -300,6 +300,33 @@ int aiehlc_conv2d_i8_srs_dev(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, 
   return launch_conv2d(ctx, x, w, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec, pick_stream(ctx, stream));
 }
 
+int aiehlc_conv2d_pack_weights_dev(aiehlc_ctx* ctx, const int8_t* w, int8_t* packed, int kh, int kw, int cin,
+                                   int cout, void* stream) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (kh <= 0 || kw <= 0 || cin <= 0 || cout <= 0) return fail(AIEHLC_ERR_INVALID, "conv2d pack: bad size");
+  if (!w || !packed) return fail(AIEHLC_ERR_INVALID, "conv2d pack: null pointer");
+  if (reinterpret_cast<uintptr_t>(packed) % 16 != 0) return fail(AIEHLC_ERR_INVALID, "conv2d pack: destination must be 16-byte aligned");
+  return launch_conv_pack_weights(ctx, w, packed, kh * kw, cin, cout, pick_stream(ctx, stream));
+}
+
+int aiehlc_conv2d_i8_srs_packed_dev(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, int8_t* y, int n, int h,
+                                    int wd, int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec,
+                                    void* stream) {
+  int rc = check_ctx(ctx);
+  if (rc) return rc;
+  if (n < 0 || h < 0 || wd < 0 || cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0 || pad < 0)
+    return fail(AIEHLC_ERR_INVALID, "conv2d: bad size");
+  if (kh != 2 * pad + 1 || kw != 2 * pad + 1)
+    return fail(AIEHLC_ERR_UNSUPPORTED, "conv2d: only stride 1 with kh = kw = 2*pad+1 (same-size output)");
+  if (n == 0 || h == 0 || wd == 0) return AIEHLC_OK;
+  if (!x || !packed || !y || !shift_vec) return fail(AIEHLC_ERR_INVALID, "conv2d: null pointer");
+  if (!conv_tensor_path(x, cin, cout) || reinterpret_cast<uintptr_t>(packed) % 16 != 0)
+    return fail(AIEHLC_ERR_UNSUPPORTED, "conv2d (packed weights): needs cin in {32, 64, k*128}, cout a multiple of 16 and "
+                                        "16-byte aligned x and weights; use aiehlc_conv2d_i8_srs_dev for other shapes");
+  return launch_conv2d_packed(ctx, x, packed, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec, pick_stream(ctx, stream));
+}
+
 // ------------------------------------------------------------------ host-pointer entry points
 // H2D copy of the operands, the same kernels, D2H copy of the result, one synchronisation.
 static int finish_host(aiehlc_ctx* ctx) {

@@ -225,10 +225,29 @@ __global__ void conv2d_i8_direct_kernel(const int8_t* __restrict__ x, const int8
   }
 }
 
+// Shapes the tensor-core tiling covers (the others take the direct CUDA-core kernel).
+bool conv_tensor_path(const int8_t* x, int cin, int cout) {
+  return (cin % 32 == 0) && (cin == 32 || cin == 64 || cin % 128 == 0) && (cout % 16 == 0) &&
+         (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+}
+
+int launch_conv_pack_weights(aiehlc_ctx* ctx, const int8_t* w, int8_t* packed, int taps, int cin, int cout,
+                             cudaStream_t st) {
+  const long long wbytes = static_cast<long long>(taps) * cin * cout;
+  long long g = (wbytes + 255) / 256;
+  if (g > ctx->sm_count * 8LL) g = ctx->sm_count * 8LL;
+  conv_weight_prepack_kernel<<<static_cast<int>(g), 256, 0, st>>>(w, packed, taps, cin, cout);
+  AIEHLC_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return AIEHLC_OK;
+}
+
+int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, int8_t* y, int n, int h, int wd,
+                         int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st);
+
 int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
                   int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
-  const bool tensor_ok = (cin % 32 == 0) && (cin == 32 || cin == 64 || cin % 128 == 0) &&
-                         (cout % 16 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+  const bool tensor_ok = conv_tensor_path(x, cin, cout);
   if (!tensor_ok) {
     const long long total = static_cast<long long>(n) * h * wd * cout;
     long long g = (total + 255) / 256;
@@ -243,15 +262,15 @@ int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, 
   const int taps = kh * kw;
   const size_t wbytes = static_cast<size_t>(taps) * cin * cout;
   if (ctx->pack_b.reserve(wbytes)) return AIEHLC_ERR_NOMEM;
-  {
-    long long g = (static_cast<long long>(wbytes) + 255) / 256;
-    if (g > ctx->sm_count * 8LL) g = ctx->sm_count * 8LL;
-    conv_weight_prepack_kernel<<<static_cast<int>(g), 256, 0, st>>>(
-        w, static_cast<int8_t*>(ctx->pack_b.ptr), taps, cin, cout);
-    AIEHLC_CUDA(cudaGetLastError());
-    ctx->launches++;
-  }
+  if (int rc = launch_conv_pack_weights(ctx, w, static_cast<int8_t*>(ctx->pack_b.ptr), taps, cin, cout, st)) return rc;
+  return launch_conv2d_packed(ctx, x, static_cast<const int8_t*>(ctx->pack_b.ptr), y, n, h, wd, cin, cout, kh, kw, pad,
+                              shift_vec, st);
+}
 
+// The implicit-GEMM kernel on weights that are already [tap][cout][cin].
+int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, int8_t* y, int n, int h, int wd,
+                         int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
+  const int taps = kh * kw;
   ConvParams p{};
   p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
   p.wt = wd <= kBlockM ? wd : kBlockM;
@@ -306,7 +325,7 @@ int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, 
     const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(taps) * cout};
     const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(cin)};
     const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.cout_tile)};
-    r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, ctx->pack_b.ptr, wdims, wstrides, wbox, estr,
+    r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(packed), wdims, wstrides, wbox, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");

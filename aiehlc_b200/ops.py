@@ -245,6 +245,29 @@ class Context:
             self._dev(shift_vec, torch.uint8, "shift_vec"), self._stream()))
         return out
 
+    def conv2d_pack_weights(self, w):
+        """HWIO int8 weights -> the [tap][cout][cin] copy the packed entry point reads."""
+        import torch
+        kh, kw, cin, cout = w.shape
+        packed = torch.empty((kh * kw, cout, cin), dtype=torch.int8, device=w.device)
+        _capi.check(self._lib.aiehlc_conv2d_pack_weights_dev(self._h, self._dev(w, torch.int8, "w"),
+                                                             self._dev(packed, torch.int8, "packed"), kh, kw, cin, cout,
+                                                             self._stream()))
+        return packed
+
+    def conv2d_i8_srs_packed(self, x, packed, kernel_hw, shift_vec, pad: int = 1, out=None):
+        import torch
+        n, h, wd, cin = x.shape
+        kh, kw = kernel_hw
+        cout = packed.shape[1]
+        if out is None:
+            out = torch.empty((n, h, wd, cout), dtype=torch.int8, device=x.device)
+        _capi.check(self._lib.aiehlc_conv2d_i8_srs_packed_dev(
+            self._h, self._dev(x, torch.int8, "x"), self._dev(packed, torch.int8, "packed"),
+            self._dev(out, torch.int8, "y"), n, h, wd, cin, cout, kh, kw, int(pad),
+            self._dev(shift_vec, torch.uint8, "shift_vec"), self._stream()))
+        return out
+
     # ------------------------------------------------------------ host arrays
     @staticmethod
     def _host(a, dtype, name):

@@ -114,6 +114,16 @@ int aiehlc_conv2d_i8_srs_host(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w,
                               int h, int wd, int cin, int cout, int kh, int kw, int pad,
                               const uint8_t* shift_vec);
 
+/* Weights that do not change between calls (inference) can be re-laid once: pack_weights writes
+ * w[kh][kw][cin][cout] as [kh*kw][cout][cin] (kh*kw*cin*cout bytes, 16-byte aligned) and the _packed
+ * entry point runs the convolution on that copy with a single kernel launch.  Tensor-core shapes only
+ * (cin 32, 64 or a multiple of 128; cout a multiple of 16). */
+int aiehlc_conv2d_pack_weights_dev(aiehlc_ctx* ctx, const int8_t* w, int8_t* packed, int kh, int kw, int cin,
+                                   int cout, void* stream);
+int aiehlc_conv2d_i8_srs_packed_dev(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, int8_t* y, int n,
+                                    int h, int wd, int cin, int cout, int kh, int kw, int pad,
+                                    const uint8_t* shift_vec, void* stream);
+
 /* ---- tiling plan --------------------------------------------------------------------------
  * What the GEMM entry points will do for a problem, without running it: tile shape, tile grid,
  * waves over the persistent CTAs (or CTA pairs), pipeline depth, and how operands are shared.

@@ -44,6 +44,24 @@ def test_conv2d_per_channel_shifts_5x5_and_host_entry(ctx):
     assert np.array_equal(ctx.conv2d_i8_srs_host(x1, w1, sv, pad=0), O.conv2d_i8_srs(x1, w1, sv, pad=0))
 
 
+def test_conv2d_with_prepacked_weights(ctx):
+    """Weights re-laid once, then one launch per convolution: same bits as the two-launch entry point."""
+    x1 = synth.int8_uniform(4, (1, 56, 56, 64))
+    x2 = synth.int8_uniform(5, (1, 56, 56, 64))
+    wt = synth.int8_uniform(1004, (3, 3, 64, 64))
+    sv = np.full(64, 6, np.uint8)
+    packed = ctx.conv2d_pack_weights(_dev(wt))
+    assert np.array_equal(packed.cpu().numpy(), np.ascontiguousarray(wt.reshape(9, 64, 64).transpose(0, 2, 1)))
+    before = ctx.launch_count
+    for x in (x1, x2):
+        got = ctx.conv2d_i8_srs_packed(_dev(x), packed, (3, 3), _dev(sv), pad=1).cpu().numpy()
+        assert np.array_equal(got, O.conv2d_i8_srs(x, wt, sv, pad=1))
+    assert ctx.launch_count == before + 2 and ctx.sync() == 0
+    from aiehlc_b200 import _capi
+    with pytest.raises(_capi.AiehlcError):                     # direct-kernel shapes have no packed form
+        ctx.conv2d_i8_srs_packed(_dev(synth.int8_uniform(4, (1, 4, 4, 24))), packed, (3, 3), _dev(sv), pad=1)
+
+
 def _bf16_err(got_bits, ref32):
     got = synth.bf16_bits_to_f32(got_bits).astype(np.float64)
     return float(np.max(np.abs(got - ref32) / np.maximum(np.abs(ref32), 1.0)))
