@@ -149,6 +149,13 @@ int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm
   return plan_gemm(ctx, kind, M, N, K, plan);
 }
 
+int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (on < 0 || on > 2) return fail(AIEHLC_ERR_INVALID, "tma_store must be 0, 1 or 2");
+  ctx->tma_store = on;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   ctx->split_tail = on ? 1 : 0;

@@ -39,6 +39,26 @@ int encode_kmajor_map(aiehlc_ctx* ctx, CUtensorMap* map, int kind, const void* b
 // the operand traffic per SM (measured on int8 8192^3: 373 us against 391 us).
 }  // namespace
 
+// C as a tiled tensor for the epilogue's tile stores: box of 32 rows x one staged row (128 bytes,
+// or the tile width where that is less), swizzle mode matching the staged row width.
+int encode_c_map(aiehlc_ctx* ctx, CUtensorMap* map, int epi, int bn, void* base, long long rows, long long cols,
+                 long long ld) {
+  const int esize = epi == EPI_I8_SRS ? 1 : (epi == EPI_BF16 ? 2 : 4);
+  const int group_bytes = bn * esize < 128 ? bn * esize : 128;
+  const CUtensorMapDataType dt = epi == EPI_I8_SRS ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : epi == EPI_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_INT32;
+  const CUtensorMapSwizzle sw = group_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : group_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * esize};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(group_bytes / esize), 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = ctx->encode(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                 CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for the output tensor");
+  return AIEHLC_OK;
+}
+
 // When the last wave of a persistent launch is at most half full, its tiles are cut along K into as
 // many ranges as there are idle slots per tile (at most 4, at least 8 K-blocks each).
 void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int* parts) {
@@ -95,10 +115,10 @@ int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_
   if (best_cost < 0) return fail(AIEHLC_ERR_INVALID, "plan_gemm: no tile shape satisfies the forced settings");
   const int stage_bytes = best.cta_pair ? kBlockM * kBlockKBytes + best.tile_n / 2 * kBlockKBytes
                                         : kBlockM * kBlockKBytes + best.tile_n * kBlockKBytes;
-  int stages = (227 * 1024 - 2048) / stage_bytes;
+  int stages = (227 * 1024 - 2048 - kStoreStagingBytes) / stage_bytes;
   if (stages > 8) stages = 8;
   best.stages = stages;
-  best.smem_bytes = stages * stage_bytes + 512 + 1024;
+  best.smem_bytes = stages * stage_bytes + kStoreStagingBytes + 512 + 1024;
   best.tmem_columns = 2 * best.tile_n < 32 ? 32 : 2 * best.tile_n;
   best.k_blocks = static_cast<int>((static_cast<long long>(K) * esize + kBlockKBytes - 1) / kBlockKBytes);
   int g = ctx->group_m > 0 ? ctx->group_m : (best.cta_pair ? 8 : 16);
@@ -146,6 +166,11 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   // 32 consecutive outputs per thread are written with 16-byte stores when every row start is aligned.
   bool vec = (reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0);
   p.vec_ok = vec ? 1 : 0;
+  // int8 results are 32 contiguous bytes per thread and chunk (whole sectors) and that epilogue is
+  // bound by its integer arithmetic: per-thread stores are faster there unless tile stores are forced (2)
+  p.tma_store = (vec && (ctx->tma_store == 2 || (ctx->tma_store == 1 && kEpi != EPI_I8_SRS))) ? 1 : 0;
+  CUtensorMap mc = ma;  // unused unless tma_store
+  if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
   p.status = ctx->d_status;
   p.debug = ctx->debug_mode;
   p.trace = ctx->trace;
@@ -168,7 +193,7 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 1 : 0;
-  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
+  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, p));
   ctx->launches++;
   return AIEHLC_OK;
 }
@@ -198,6 +223,9 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
   p.group_m = c.group_m;
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0)) ? 1 : 0;
+  p.tma_store = (p.vec_ok && (ctx->tma_store == 2 || (ctx->tma_store == 1 && kEpi != EPI_I8_SRS))) ? 1 : 0;
+  CUtensorMap mc = ma;  // unused unless tma_store
+  if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
   p.status = ctx->d_status;
   p.debug = ctx->debug_mode;
   p.trace = ctx->trace;
@@ -261,7 +289,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
     }
   }
   cfg.gridDim = dim3(2 * pairs);
-  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
+  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, p));
   ctx->launches++;
   return AIEHLC_OK;
 }

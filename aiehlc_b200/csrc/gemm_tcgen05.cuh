@@ -37,6 +37,9 @@ constexpr int kBlockM = 128;        // rows of C per tile = TMEM lanes
 constexpr int kBlockKBytes = 128;   // one 128B swizzle span of K per stage
 constexpr int kUmmaKBytes = 32;     // K bytes consumed by one tcgen05.mma (32 x i8, 16 x bf16)
 constexpr int kGemmThreads = 192;
+// Results leave the epilogue through shared memory: 2 buffers of 32 rows x 128 B for each of the 4 warps.
+constexpr int kStoreBufBytes = 4096;
+constexpr int kStoreStagingBytes = 4 * 2 * kStoreBufBytes;
 
 struct GemmParams {
   int M, N, K;
@@ -50,6 +53,7 @@ struct GemmParams {
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int group_m;             // rasterisation: tiles walk group_m row-blocks before the next column
   int vec_ok;              // C (and acc_in) rows are 16-byte aligned: vector stores allowed
+  int tma_store;           // results leave through shared memory and TMA tile stores (needs vec_ok)
   int* status;             // device status word (0 = ok)
   // Tail balancing of the pair kernel: tiles >= sk_first_tile are cut into sk_parts K ranges that
   // run on different CTA pairs.  Each range owns a share of the tile's column chunks: it deposits
@@ -103,11 +107,11 @@ struct GemmSmem {
   static constexpr int kABytes = kBlockM * kBlockKBytes;
   static constexpr int kBBytes = kBN * kBlockKBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBudget = 227 * 1024 - 2048;  // keep room for barriers + 1 KB alignment
+  static constexpr int kBudget = 227 * 1024 - 2048 - kStoreStagingBytes;  // barriers, alignment, store staging
   static constexpr int kStagesRaw = kBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kBarBytes = 512;
-  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;
+  static constexpr int kTotal = kStages * kStageBytes + kStoreStagingBytes + kBarBytes + 1024;
 };
 
 __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb, int& nb) {
@@ -120,12 +124,73 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb,
   nb = r / rows;
 }
 
-// Output stage for 32 consecutive accumulator columns of one row (the caller has checked that
-// row < M and col0 < N).
-template <int kEpi>
-__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[32], int row, int col0) {
+// Where an epilogue warp puts its results when they leave through TMA tile stores.
+struct StoreCtx {
+  const void* tmap;     // C as a tiled tensor, box = 32 columns x 32 rows
+  uint8_t* buf[2];      // this warp's two staging buffers (1024-byte aligned)
+  int which;            // buffer the current group of chunks goes to
+  int chunk_in_group;   // 32-column chunks already staged in that buffer
+  int lane;
+  int warp_row0;        // first row of C this warp's 32 TMEM lanes map to
+};
+
+// Stages one 32-column chunk of this warp's 32 rows; once a group of chunks fills a row of
+// kGroupBytes (128 B, or the whole tile width if that is less) one tile store (or add-reduction)
+// writes the group.  Each thread writes its own row in 16-byte pieces whose position is
+// XOR-swizzled with the row number exactly as the tensor map's swizzle mode expects, which also
+// spreads the rows over the shared-memory banks.  The hardware clips rows >= M and columns >= N.
+template <int kGroupBytes, int kPieceBytes, bool kReduceAdd>
+__device__ __forceinline__ void tma_emit(StoreCtx& sc, const uint32_t* words, int col0) {
+  constexpr int kPerGroup = kGroupBytes / kPieceBytes;
+  constexpr int kPieces = kPieceBytes / 16;
+  const int k = sc.chunk_in_group;
+  uint8_t* buf = sc.buf[sc.which];
+  if (k == 0) {
+    if (sc.lane == 0) tma_store_wait_read<1>();  // the store issued from this buffer two groups ago has read it
+    __syncwarp();
+  }
+  const int swz = kGroupBytes == 128 ? (sc.lane & 7) : kGroupBytes == 64 ? ((sc.lane >> 1) & 3) : ((sc.lane >> 2) & 1);
+#pragma unroll
+  for (int j = 0; j < kPieces; ++j)
+    *reinterpret_cast<uint4*>(buf + sc.lane * kGroupBytes + (((k * kPieces + j) ^ swz) << 4)) =
+        make_uint4(words[4 * j], words[4 * j + 1], words[4 * j + 2], words[4 * j + 3]);
+  if (k == kPerGroup - 1) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (sc.lane == 0) {
+      const int group_col0 = col0 - k * 32;
+      if constexpr (kReduceAdd) tma_reduce_add_2d(sc.tmap, smem_u32(buf), group_col0, sc.warp_row0);
+      else tma_store_2d(sc.tmap, smem_u32(buf), group_col0, sc.warp_row0);
+      tma_store_commit();
+    }
+    sc.which ^= 1;
+    sc.chunk_in_group = 0;
+  } else {
+    sc.chunk_in_group = k + 1;
+  }
+}
+
+// Bytes of one staged row: 128, or the tile width in bytes where that is less.
+template <int kEpi, int kBN>
+struct StoreGroup {
+  static constexpr int kElem = kEpi == EPI_I8_SRS ? 1 : (kEpi == EPI_BF16 ? 2 : 4);
+  static constexpr int kBytes = kBN * kElem < 128 ? kBN * kElem : 128;
+  static constexpr int kCols = kBytes / kElem;
+};
+
+// Output stage for 32 consecutive accumulator columns of one row.  Direct stores: the caller has
+// checked row < M and col0 < N.  TMA stores (p.tma_store): called by the whole warp for EVERY chunk
+// of the tile in column order; rows >= M and columns >= N are staged like the others and clipped
+// by the hardware.
+template <int kEpi, int kBN, bool kForceDirect = false>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[32], int row, int col0, bool row_ok,
+                                            StoreCtx& sc) {
   const int ncols = min(32, p.N - col0);
   if constexpr (kEpi == EPI_I32 || kEpi == EPI_I32_ACC) {
+    if (!kForceDirect && p.tma_store) {
+      tma_emit<128, 128, kEpi == EPI_I32_ACC>(sc, r, col0);
+      return;
+    }
     int32_t* dst = static_cast<int32_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
     if (p.vec_ok && ncols == 32) {
 #pragma unroll
@@ -147,7 +212,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
     }
   } else if constexpr (kEpi == EPI_I8_SRS) {
     int8_t* dst = static_cast<int8_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-    if (p.acc_in != nullptr) {
+    if (p.acc_in != nullptr && row_ok) {
       const int32_t* ai = p.acc_in + static_cast<long long>(row) * p.ld_acc + col0;
 #pragma unroll
       for (int j = 0; j < 32; ++j)
@@ -181,6 +246,10 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
 #pragma unroll
       for (int j = 0; j < 32; j += 4) packed[j >> 2] = pack_sat_s8x4(q[j], q[j + 1], q[j + 2], q[j + 3]);
     }
+    if (!kForceDirect && p.tma_store) {
+      tma_emit<StoreGroup<kEpi, kBN>::kBytes, 32, false>(sc, packed, col0);
+      return;
+    }
     if (p.vec_ok && ncols == 32) {
       *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
@@ -196,6 +265,10 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
     for (int j = 0; j < 32; j += 2) {
       const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
       packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    if (!kForceDirect && p.tma_store) {
+      tma_emit<128, 64, false>(sc, packed, col0);
+      return;
     }
     if (p.vec_ok && ncols == 32) {
 #pragma unroll
@@ -216,7 +289,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
 // per step: two TMEM loads are issued back to back, then waited for once.
 template <int kBN, int kEpi>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t taddr, int row, bool row_ok,
-                                                  int n0) {
+                                                  int n0, StoreCtx& sc) {
   static_assert(kBN % 64 == 0, "accumulator is drained 64 columns at a time");
 #pragma unroll 1
   for (int c = 0; c < kBN; c += 64) {
@@ -225,15 +298,15 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
     tmem_ld_32x32b_x32(taddr + c, ra);
     tmem_ld_32x32b_x32(taddr + c + 32, rb);
     tmem_ld_wait();
-    if (row_ok && n0 + c < p.N) store_chunk<kEpi>(p, ra, row, n0 + c);
-    if (row_ok && n0 + c + 32 < p.N) store_chunk<kEpi>(p, rb, row, n0 + c + 32);
+    if (p.tma_store || (row_ok && n0 + c < p.N)) store_chunk<kEpi, kBN>(p, ra, row, n0 + c, row_ok, sc);
+    if (p.tma_store || (row_ok && n0 + c + 32 < p.N)) store_chunk<kEpi, kBN>(p, rb, row, n0 + c + 32, row_ok, sc);
   }
 }
 
 template <int kKind, int kBN, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using S = GemmSmem<kBN>;
   constexpr int kStages = S::kStages;
   constexpr int kBBoxRows = kBN > 128 ? 128 : kBN;     // B arrives in boxes of at most 128 rows
@@ -248,7 +321,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // 128B-swizzled tiles need 1024-byte aligned bases.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* bar_mem = smem + kStages * S::kStageBytes;
+  uint8_t* store_staging = smem + kStages * S::kStageBytes;  // 1024-byte aligned: stages are multiples of 1 KB
+  uint8_t* bar_mem = store_staging + kStoreStagingBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full_bar = empty_bar + kStages;
@@ -372,6 +446,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    StoreCtx sc{&tmap_c, {store_staging + (quad * 2) * kStoreBufBytes, store_staging + (quad * 2 + 1) * kStoreBufBytes},
+                0, 0, lane, 0};
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
@@ -390,13 +466,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int row = mb * kBlockM + quad * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
-      drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN);
+      sc.warp_row0 = row - lane;
+      drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN, sc);
       // Accumulator drained: hand it back to the MMA issuer.
       tc_fence_before();
       __syncwarp();
       if (tracer) p.trace[it * 8 + 4] = clock64();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
+    if (lane == 0) tma_store_wait_all();  // tile stores in flight still read this CTA's shared memory
   }
 
   tc_fence_before();

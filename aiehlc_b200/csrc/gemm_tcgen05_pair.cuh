@@ -27,11 +27,11 @@ struct PairSmem {
   static constexpr int kABytes = kBlockM * kBlockKBytes;           // this CTA's 128 rows of A
   static constexpr int kBBytes = (kBN / 2) * kBlockKBytes;         // this CTA's half of B
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBudget = 227 * 1024 - 2048;
+  static constexpr int kBudget = 227 * 1024 - 2048 - kStoreStagingBytes;
   static constexpr int kStagesRaw = kBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kBarBytes = 512;
-  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;
+  static constexpr int kTotal = kStages * kStageBytes + kStoreStagingBytes + kBarBytes + 1024;
 };
 
 // One unit of work of a CTA pair: a whole tile, or one K range of a tail tile.
@@ -92,7 +92,7 @@ __device__ __forceinline__ void add_deposited_chunk(uint32_t (&r)[32], const int
 template <int kKind, int kBN, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using S = PairSmem<kBN>;
   constexpr int kStages = S::kStages;
   constexpr int kBHalf = kBN / 2;
@@ -104,7 +104,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* bar_mem = smem + kStages * S::kStageBytes;
+  uint8_t* store_staging = smem + kStages * S::kStageBytes;  // 1024-byte aligned: stages are multiples of 1 KB
+  uint8_t* bar_mem = store_staging + kStoreStagingBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);   // used in the leader CTA
   uint64_t* empty_bar = full_bar + kStages;                    // one set per CTA
   uint64_t* tmem_full_bar = empty_bar + kStages;               // one set per CTA
@@ -230,6 +231,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs)
     const int quad = warp & 3;
+    StoreCtx sc{&tmap_c, {store_staging + (quad * 2) * kStoreBufBytes, store_staging + (quad * 2 + 1) * kStoreBufBytes},
+                0, 0, lane, 0};
     int it = 0;
     bool ok = true;
     WorkUnit w;
@@ -249,8 +252,9 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int row = mb * kPairM + static_cast<int>(rank) * kBlockM + lane_row;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
+      sc.warp_row0 = row - lane;
       if (w.parts == 1) {
-        drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN);
+        drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN, sc);
       } else {
         // tail tile cut along K; scratch is [tail tile][depositing range][CTA rank][chunk]
         constexpr int kChunks = kBN / 32;
@@ -311,7 +315,9 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int j = 0; j < 32; ++j) r[j] += dep[j];
             for (int q = 0; q < w.parts; ++q)
               if (q != w.part && q != q0) add_deposited_chunk(r, tile_base + q * part_stride + c * kSkChunkInts, quad, lane);
-            if (row_ok && nb * kBN + c * 32 < p.N) store_chunk<kEpi>(p, r, row, nb * kBN + c * 32);
+            // a K range owns only part of the tile's columns: per-thread stores, not tile stores
+            if (row_ok && nb * kBN + c * 32 < p.N)
+              store_chunk<kEpi, kBN, true>(p, r, row, nb * kBN + c * 32, row_ok, sc);
 #pragma unroll
             for (int j = 0; j < 32; ++j) dep[j] = dep_next[j];
           }
@@ -330,6 +336,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (tracer) p.trace[it * 8 + 4] = clock64();
       if (lane == 0) mbar_arrive_remote(smem_u32(&tmem_empty_bar[acc]), 0);
     }
+    if (lane == 0) tma_store_wait_all();  // tile stores in flight still read this CTA's shared memory
   }
 
   // Neither CTA may retire (or free TMEM) while its partner can still read its shared memory,

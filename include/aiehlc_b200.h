@@ -177,6 +177,12 @@ int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n);
  * fetching half of the B tile) wherever M > 128, 0 = one CTA per 128-row tile, -1 = choose per
  * shape (the default). */
 int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode);
+/* Tuning knob: 1 (default) = the int32 and bf16 GEMM epilogues stage 32 rows x 128 bytes of results in
+ * shared memory and write them with a TMA tile store (whole 128-byte lines, clipped at the edges of C;
+ * `accumulate` uses the add-reduction form); 2 = the int8 srs epilogue does so too (measured slower than
+ * its per-thread 32-byte stores); 0 = every thread stores its own row directly.  Tile stores need C
+ * 16-byte aligned with a 16-byte row pitch; otherwise the direct path is taken whatever the setting. */
+int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on);
 /* Tuning knob: 1 = when the last wave of an int8 CTA-pair launch is at most half full, its tiles are
  * cut along K across the idle pairs; the K ranges of a tile exchange int32 partial sums through a
  * context workspace and each runs the output stage on its share of the columns (integer sums:

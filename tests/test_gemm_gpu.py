@@ -162,6 +162,31 @@ def test_split_tail_tiles_are_bit_identical(ctx, shape):
         ctx.set_cta_pair(-1)
 
 
+@pytest.mark.parametrize("tma_store", [0, 1, 2])
+def test_both_store_paths(ctx, tma_store):
+    """Results leave either through shared memory + TMA tile stores or through per-thread stores."""
+    M, N, K = 520, 336, 272
+    A = synth.int8_uniform(8, (M, K))
+    B = synth.int8_uniform(1008, (N, K))
+    ctx.set_tma_store(tma_store)
+    try:
+        dA, dB = _dev(A), _dev(B)
+        acc = ctx.gemm_i8_i32(dA, dB)
+        assert np.array_equal(acc.cpu().numpy(), O.gemm_i8_i32(A, B))
+        ctx.gemm_i8_i32(dA, dB, out=acc, accumulate=True)                       # add-reduction form of the store
+        assert np.array_equal(acc.cpu().numpy(), 2 * O.gemm_i8_i32(A, B))
+        assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift=7).cpu().numpy(), O.gemm_i8_srs(A, B, shift=7))
+        Ab = synth.normal_bf16_bits(3, (M, K))
+        Bb = synth.normal_bf16_bits(1003, (N, K))
+        got = ctx.gemm_bf16(_dev(Ab.view(np.int16)).view(torch.bfloat16), _dev(Bb.view(np.int16)).view(torch.bfloat16))
+        ref = O.gemm_bf16(Ab, Bb).astype(np.float64)
+        gf = got.float().cpu().numpy().astype(np.float64)
+        assert float(np.max(np.abs(gf - ref) / np.maximum(np.abs(ref), 1.0))) <= 1e-2
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_tma_store(1)
+
+
 def test_accumulate_and_flush(ctx):
     M, N, K = 200, 136, 512
     A = synth.int8_uniform(2, (M, K))
