@@ -89,6 +89,8 @@ int aiehlc_create(int device, aiehlc_ctx** out) {
   }
   ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
   e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream2, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->block_done, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaMalloc(&ctx->d_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
   if (e == cudaSuccess) e = cudaMallocHost(&ctx->h_status, sizeof(int));
@@ -109,6 +111,11 @@ int aiehlc_destroy(aiehlc_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     cudaStreamDestroy(ctx->stream);
   }
+  if (ctx->stream2) {
+    cudaStreamSynchronize(ctx->stream2);
+    cudaStreamDestroy(ctx->stream2);
+  }
+  if (ctx->block_done) cudaEventDestroy(ctx->block_done);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   ctx->buf_a.release(); ctx->buf_b.release(); ctx->buf_c.release(); ctx->buf_aux.release();
@@ -367,20 +374,56 @@ static int stage_ab(aiehlc_ctx* ctx, const void* A, const void* B, size_t a_byte
   return AIEHLC_OK;
 }
 
+}  // extern "C"
+
+// Host-buffer GEMM as a pipeline over row blocks of A and C:
+//   stream  : B -> device, then per block: A rows -> device, kernel
+//   stream2 : per block, once its kernel is done: C rows -> host
+// so the upload of block i+1 and the download of block i run while block i+1 computes (PCIe is
+// full duplex).  With pinned host buffers the copies are truly asynchronous; with pageable ones the
+// runtime stages them and the result is the same, only slower.
+template <typename LaunchRows>
+static int host_gemm_pipelined(aiehlc_ctx* ctx, const void* A, const void* B, void* C, int M, int N, int K, int in_esize,
+                               int out_esize, LaunchRows launch_rows) {
+  const size_t a_bytes = static_cast<size_t>(M) * K * in_esize, b_bytes = static_cast<size_t>(N) * K * in_esize;
+  const size_t c_bytes = static_cast<size_t>(M) * N * out_esize;
+  if (ctx->buf_a.reserve(a_bytes ? a_bytes : 16) || ctx->buf_b.reserve(b_bytes ? b_bytes : 16) ||
+      ctx->buf_c.reserve(c_bytes ? c_bytes : 16))
+    return AIEHLC_ERR_NOMEM;
+  if (b_bytes) AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_b.ptr, B, b_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  // four blocks of whole 256-row tiles; small problems go in one piece
+  int rows_per_block = ((M + 3) / 4 + 255) / 256 * 256;
+  if (static_cast<size_t>(rows_per_block) * K * in_esize < (1u << 20)) rows_per_block = M;
+  for (int r0 = 0; r0 < M; r0 += rows_per_block) {
+    const int rows = M - r0 < rows_per_block ? M - r0 : rows_per_block;
+    uint8_t* da = static_cast<uint8_t*>(ctx->buf_a.ptr) + static_cast<size_t>(r0) * K * in_esize;
+    uint8_t* dc = static_cast<uint8_t*>(ctx->buf_c.ptr) + static_cast<size_t>(r0) * N * out_esize;
+    if (K > 0)
+      AIEHLC_CUDA(cudaMemcpyAsync(da, static_cast<const uint8_t*>(A) + static_cast<size_t>(r0) * K * in_esize,
+                                  static_cast<size_t>(rows) * K * in_esize, cudaMemcpyHostToDevice, ctx->stream));
+    const int rc = launch_rows(da, dc, rows);
+    if (rc) return rc;
+    AIEHLC_CUDA(cudaEventRecord(ctx->block_done, ctx->stream));
+    AIEHLC_CUDA(cudaStreamWaitEvent(ctx->stream2, ctx->block_done, 0));
+    AIEHLC_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(C) + static_cast<size_t>(r0) * N * out_esize, dc,
+                                static_cast<size_t>(rows) * N * out_esize, cudaMemcpyDeviceToHost, ctx->stream2));
+  }
+  AIEHLC_CUDA(cudaStreamSynchronize(ctx->stream2));
+  return finish_host(ctx);
+}
+
+extern "C" {
+
 int aiehlc_gemm_i8_i32_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int32_t* C, int M, int N, int K) {
   int rc = check_ctx(ctx);
   if (rc) return rc;
   if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32: negative size");
   if (M == 0 || N == 0) return AIEHLC_OK;
   if (!C || (K > 0 && (!A || !B))) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32: null pointer");
-  const size_t cb = static_cast<size_t>(M) * N * 4;
-  if ((rc = stage_ab(ctx, A, B, static_cast<size_t>(M) * K, static_cast<size_t>(N) * K, cb))) return rc;
-  rc = aiehlc_gemm_i8_i32_dev(ctx, static_cast<const int8_t*>(ctx->buf_a.ptr),
-                              static_cast<const int8_t*>(ctx->buf_b.ptr), static_cast<int32_t*>(ctx->buf_c.ptr),
-                              M, N, K, 0, ctx->stream);
-  if (rc) return rc;
-  AIEHLC_CUDA(cudaMemcpyAsync(C, ctx->buf_c.ptr, cb, cudaMemcpyDeviceToHost, ctx->stream));
-  return finish_host(ctx);
+  return host_gemm_pipelined(ctx, A, B, C, M, N, K, 1, 4, [&](uint8_t* da, uint8_t* dc, int rows) {
+    return aiehlc_gemm_i8_i32_dev(ctx, reinterpret_cast<const int8_t*>(da), static_cast<const int8_t*>(ctx->buf_b.ptr),
+                                  reinterpret_cast<int32_t*>(dc), rows, N, K, 0, ctx->stream);
+  });
 }
 
 int aiehlc_gemm_i8_srs_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
@@ -390,22 +433,18 @@ int aiehlc_gemm_i8_srs_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, i
   if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: negative size");
   if (M == 0 || N == 0) return AIEHLC_OK;
   if (!C || (K > 0 && (!A || !B))) return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: null pointer");
-  const size_t cb = static_cast<size_t>(M) * N;
-  if ((rc = stage_ab(ctx, A, B, static_cast<size_t>(M) * K, static_cast<size_t>(N) * K, cb))) return rc;
   const uint8_t* dsv = nullptr;
   if (shift_vec) {
+    for (int j = 0; j < N; ++j)
+      if (shift_vec[j] > 31) return fail(AIEHLC_ERR_INVALID, "srs shift must be in [0, 31]");
     if (ctx->buf_aux.reserve(N)) return AIEHLC_ERR_NOMEM;
     AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_aux.ptr, shift_vec, N, cudaMemcpyHostToDevice, ctx->stream));
     dsv = static_cast<const uint8_t*>(ctx->buf_aux.ptr);
-    for (int j = 0; j < N; ++j)
-      if (shift_vec[j] > 31) return fail(AIEHLC_ERR_INVALID, "srs shift must be in [0, 31]");
   }
-  rc = aiehlc_gemm_i8_srs_dev(ctx, static_cast<const int8_t*>(ctx->buf_a.ptr),
-                              static_cast<const int8_t*>(ctx->buf_b.ptr), static_cast<int8_t*>(ctx->buf_c.ptr),
-                              M, N, K, shift, dsv, nullptr, splitk, ctx->stream);
-  if (rc) return rc;
-  AIEHLC_CUDA(cudaMemcpyAsync(C, ctx->buf_c.ptr, cb, cudaMemcpyDeviceToHost, ctx->stream));
-  return finish_host(ctx);
+  return host_gemm_pipelined(ctx, A, B, C, M, N, K, 1, 1, [&](uint8_t* da, uint8_t* dc, int rows) {
+    return aiehlc_gemm_i8_srs_dev(ctx, reinterpret_cast<const int8_t*>(da), static_cast<const int8_t*>(ctx->buf_b.ptr),
+                                  reinterpret_cast<int8_t*>(dc), rows, N, K, shift, dsv, nullptr, splitk, ctx->stream);
+  });
 }
 
 int aiehlc_gemm_bf16_host(aiehlc_ctx* ctx, const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N,
@@ -415,14 +454,10 @@ int aiehlc_gemm_bf16_host(aiehlc_ctx* ctx, const uint16_t* A, const uint16_t* B,
   if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_bf16: negative size");
   if (M == 0 || N == 0) return AIEHLC_OK;
   if (!C || (K > 0 && (!A || !B))) return fail(AIEHLC_ERR_INVALID, "gemm_bf16: null pointer");
-  const size_t cb = static_cast<size_t>(M) * N * 2;
-  if ((rc = stage_ab(ctx, A, B, static_cast<size_t>(M) * K * 2, static_cast<size_t>(N) * K * 2, cb))) return rc;
-  rc = aiehlc_gemm_bf16_dev(ctx, static_cast<const uint16_t*>(ctx->buf_a.ptr),
-                            static_cast<const uint16_t*>(ctx->buf_b.ptr), static_cast<uint16_t*>(ctx->buf_c.ptr),
-                            M, N, K, ctx->stream);
-  if (rc) return rc;
-  AIEHLC_CUDA(cudaMemcpyAsync(C, ctx->buf_c.ptr, cb, cudaMemcpyDeviceToHost, ctx->stream));
-  return finish_host(ctx);
+  return host_gemm_pipelined(ctx, A, B, C, M, N, K, 2, 2, [&](uint8_t* da, uint8_t* dc, int rows) {
+    return aiehlc_gemm_bf16_dev(ctx, reinterpret_cast<const uint16_t*>(da), static_cast<const uint16_t*>(ctx->buf_b.ptr),
+                                reinterpret_cast<uint16_t*>(dc), rows, N, K, ctx->stream);
+  });
 }
 
 int aiehlc_conv2d_i8_srs_host(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,

@@ -48,7 +48,9 @@ struct KernelSetup {
 struct aiehlc_ctx {
   int device = 0;
   int sm_count = 0;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;   // uploads and kernels of the *_host entry points
+  cudaStream_t stream2 = nullptr;  // their downloads, overlapped with the next block's upload
+  cudaEvent_t block_done = nullptr;
   int* d_status = nullptr;      // device status word
   int* h_status = nullptr;      // pinned mirror
   aiehlc::EncodeTiledFn encode = nullptr;
