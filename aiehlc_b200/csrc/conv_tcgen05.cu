@@ -37,6 +37,7 @@ struct ConvParams {
   int8_t* y;
   const uint8_t* shift_vec;
   int* status;
+  long long* trace;   // measurement aid: clock64 stamps of CTA 0, or null
 };
 
 __global__ void __launch_bounds__(kConvThreads, 1)
@@ -51,9 +52,12 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   uint64_t* tmem_full_bar = empty_bar + kConvMaxStages;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  uint8_t* shift_smem = reinterpret_cast<uint8_t*>(tmem_base_slot + 2);  // this CTA's cout_tile shift bytes (<= 256)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const long long entry_clock = clock64();
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -74,6 +78,19 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   const uint32_t tmem_base = *tmem_base_slot;
   pdl_launch_dependents();
   pdl_wait();  // the weight pre-pass before this kernel has completed; global memory may be touched
+  if (tracing && threadIdx.x == 0) {
+    p.trace[0] = entry_clock;
+    p.trace[1] = clock64();
+  }
+  // the epilogue warps fetch the per-channel shifts once; they are needed only after the main loop
+  if (warp >= 2) {
+    const int i = threadIdx.x - 64;
+    for (int c = i; c < 256; c += 128) {
+      const int col = blockIdx.y * p.cout_tile + c;
+      shift_smem[c] = (c < p.cout_tile && col < p.cout) ? p.shift_vec[col] : 0;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+  }
 
   // tile -> (image, first output row, first output column, first output channel)
   int t = blockIdx.x;
@@ -120,6 +137,8 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
         if (!ok) break;
         tc_fence_after();
+        if (tracing && kb == 0) p.trace[2] = clock64();
+        if (tracing && kb < 12) p.trace[8 + kb] = clock64();
         const uint32_t sa = smem_u32(smem + stage * p.stage_bytes);
         const uint32_t sb = sa + p.a_bytes;
         const uint64_t adesc = make_kmajor_desc(sa, p.sbo_bytes, p.swizzle_code);
@@ -130,6 +149,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
       if (ok) umma_commit(smem_u32(tmem_full_bar));
+      if (tracing) p.trace[3] = clock64();
     }
   } else {
     const int quad = warp & 3;
@@ -137,6 +157,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     ok = __all_sync(0xFFFFFFFFu, ok);
     if (ok) {
       tc_fence_after();
+      if (tracing && warp == 2 && lane == 0) p.trace[4] = clock64();
       const int m = quad * 32 + lane;
       const int oh = oh0 + m / p.wt, ow = ow0 + m % p.wt;
       const bool pix_ok = m < p.rows_per_tile * p.wt && oh < p.h && ow < p.w;
@@ -152,16 +173,14 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (!pix_ok || col0 >= p.cout) continue;
         const int ncols = min(32, min(p.cout_tile - c, p.cout - col0));
         uint32_t packed[8];
+        int q[32];
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          uint32_t wv = 0;
-#pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            const int s = (j + b < ncols) ? static_cast<int>(p.shift_vec[col0 + j + b]) : 0;
-            wv |= (static_cast<uint32_t>(srs_i8(static_cast<int>(r[j + b]), s)) & 0xFFu) << (8 * b);
-          }
-          packed[j >> 2] = wv;
+        for (int j = 0; j < 32; ++j) {
+          const int sh = static_cast<int>(shift_smem[c + j]);
+          q[j] = srs_round<true>(static_cast<int>(r[j]), sh, max(static_cast<int>((1u << sh) >> 1) - 1, 0), min(sh, 1));
         }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) packed[j >> 2] = pack_sat_s8x4(q[j], q[j + 1], q[j + 2], q[j + 3]);
         if (vec && ncols == 32) {
           *reinterpret_cast<uint4*>(yrow + col0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           *reinterpret_cast<uint4*>(yrow + col0 + 16) =
@@ -175,12 +194,14 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
   }
 
+  if (tracing && warp == 2 && lane == 0) p.trace[5] = clock64();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, p.tmem_cols);
   }
+  if (tracing && threadIdx.x == 0) p.trace[6] = clock64();
 }
 
 // HWIO [tap][cin][cout] -> [tap][cout][cin]: makes the weights K-major like every other operand.
@@ -277,7 +298,6 @@ int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed,
   p.rows_per_tile = wd <= kBlockM ? kBlockM / wd : 1;
   if (p.rows_per_tile > h) p.rows_per_tile = h;
   p.tiles_w = (wd + p.wt - 1) / p.wt;
-  p.tiles_h = (h + p.rows_per_tile - 1) / p.rows_per_tile;
   p.chunk = cin >= 128 ? 128 : cin;
   p.chunks_per_tap = cin / p.chunk;
   p.cout_tile = cout <= 256 ? cout : 256;
@@ -287,6 +307,16 @@ int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed,
     while (ct > 16 && cout % ct != 0) ct -= 16;
     p.cout_tile = ct;
   }
+  // A small problem is bound by how fast one SM's TMA unit can fetch its operand rows, not by the
+  // tensor pipe: while fewer than half of the SMs would have a tile, give each CTA fewer image rows,
+  // then fewer output channels (halves that still divide cout and stay multiples of 16).
+  auto ctas = [&]() {
+    return static_cast<long long>(n) * ((h + p.rows_per_tile - 1) / p.rows_per_tile) * p.tiles_w *
+           ((cout + p.cout_tile - 1) / p.cout_tile);
+  };
+  while (ctas() * 2 < ctx->sm_count && p.rows_per_tile > 1) p.rows_per_tile = (p.rows_per_tile + 1) / 2;
+  while (ctas() * 2 < ctx->sm_count && p.cout_tile % 32 == 0 && p.cout_tile >= 64) p.cout_tile /= 2;
+  p.tiles_h = (h + p.rows_per_tile - 1) / p.rows_per_tile;
   const int n_tiles = (cout + p.cout_tile - 1) / p.cout_tile;
   p.swizzle_code = p.chunk == 128 ? 2u : (p.chunk == 64 ? 4u : 6u);
   p.sbo_bytes = 8u * p.chunk;
@@ -304,6 +334,7 @@ int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed,
   while (cols < static_cast<uint32_t>(p.cout_tile)) cols <<= 1;
   p.tmem_cols = cols;
   p.y = y; p.shift_vec = shift_vec; p.status = ctx->d_status;
+  p.trace = ctx->trace;
 
   // x as a 4-D tensor {cin, w, h, n}; box {chunk, wt, rows_per_tile, 1}
   CUtensorMap mx, mw;
@@ -458,6 +489,7 @@ int launch_conv2d_static(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8
   while (cols < static_cast<uint32_t>(p.cout_tile)) cols <<= 1;
   p.tmem_cols = cols;
   p.y = y; p.shift_vec = shift_vec; p.status = ctx->d_status;
+  p.trace = ctx->trace;
 
   CUtensorMap mx, mw;
   const cuuint32_t estr[4] = {1, 1, 1, 1};
