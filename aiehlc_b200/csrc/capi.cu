@@ -156,6 +156,13 @@ int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm
   return plan_gemm(ctx, kind, M, N, K, plan);
 }
 
+int aiehlc_set_k_per_load(aiehlc_ctx* ctx, int k_blocks) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (k_blocks < 0 || k_blocks > 2) return fail(AIEHLC_ERR_INVALID, "k_per_load must be 0, 1 or 2");
+  ctx->k_per_load = k_blocks;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   if (on < 0 || on > 2) return fail(AIEHLC_ERR_INVALID, "tma_store must be 0, 1 or 2");

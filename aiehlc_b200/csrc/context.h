@@ -56,6 +56,7 @@ struct aiehlc_ctx {
   aiehlc::EncodeTiledFn encode = nullptr;
   int force_tile_n = 0;
   int pair_mode = -1;           // -1: choose per shape, 0: single-CTA tiles only, 1: CTA pairs wherever M > 128
+  int k_per_load = 0;           // 0: choose, 1: one 128-byte K block per tile load, 2: two where K allows
   int tma_store = 1;            // epilogue results leave through shared memory + TMA tile stores when C allows
   int split_tail = 0;           // cut the tiles of a thin last wave along K across idle CTA pairs (off: no measured gain yet)
   int group_m = 0;              // row-blocks per rasterisation group (0 = default for the kernel family)

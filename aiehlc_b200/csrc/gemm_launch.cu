@@ -39,6 +39,31 @@ int encode_kmajor_map(aiehlc_ctx* ctx, CUtensorMap* map, int kind, const void* b
 // the operand traffic per SM (measured on int8 8192^3: 373 us against 391 us).
 }  // namespace
 
+// The same K-major operand as a 3-D tensor {128 bytes, rows, K / 128 bytes}: a box then spans
+// `k_blocks` consecutive 128-byte K blocks of `box_rows` rows.  Needs K * element size to be a
+// multiple of 128 bytes (a partial last block would otherwise spill into the next row).
+int encode_kmajor_map_3d(aiehlc_ctx* ctx, CUtensorMap* map, int kind, const void* base, long long rows, long long k,
+                         long long ld_elems, int box_rows, int k_blocks) {
+  const int esize = kind == KIND_I8 ? 1 : 2;
+  const cuuint64_t inner = kBlockKBytes / esize;
+  const cuuint64_t dims[3] = {inner, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(k * esize / kBlockKBytes)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld_elems) * esize, kBlockKBytes};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(inner), static_cast<cuuint32_t>(box_rows),
+                             static_cast<cuuint32_t>(k_blocks)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = ctx->encode(
+      map, kind == KIND_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char msg[160];
+    snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled (3-D) failed (CUresult %d) rows=%lld k=%lld ld=%lld",
+             static_cast<int>(r), rows, k, ld_elems);
+    return fail(AIEHLC_ERR_CUDA, msg);
+  }
+  return AIEHLC_OK;
+}
+
 // C as a tiled tensor for the epilogue's tile stores: box of 32 rows x one staged row (128 bytes,
 // or the tile width where that is less), swizzle mode matching the staged row width.
 int encode_c_map(aiehlc_ctx* ctx, CUtensorMap* map, int epi, int bn, void* base, long long rows, long long cols,
@@ -74,6 +99,13 @@ void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int
     *first = tiles - rem;
     *parts = s;
   }
+}
+
+// Whether the CTA-pair kernel fetches two 128-byte K blocks with one tile load: K must be a whole
+// number of blocks (the 3-D tensor map has no partial last block) and there must be enough of them.
+static bool wide_k_loads(const aiehlc_ctx* ctx, int esize, int K) {
+  const long long kbytes = static_cast<long long>(K) * esize;
+  return ctx->k_per_load != 1 && kbytes % kBlockKBytes == 0 && kbytes >= 4 * kBlockKBytes;
 }
 
 // The planner: B200 counterpart of the compiler's matmul tiling (tilinglinalg::creatematmul,
@@ -113,8 +145,10 @@ int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_
     }
   }
   if (best_cost < 0) return fail(AIEHLC_ERR_INVALID, "plan_gemm: no tile shape satisfies the forced settings");
-  const int stage_bytes = best.cta_pair ? kBlockM * kBlockKBytes + best.tile_n / 2 * kBlockKBytes
-                                        : kBlockM * kBlockKBytes + best.tile_n * kBlockKBytes;
+  const int k_per = best.cta_pair && wide_k_loads(ctx, esize, K) ? 2 : 1;
+  best.tile_k_bytes = kBlockKBytes * k_per;
+  const int stage_bytes = (best.cta_pair ? kBlockM * kBlockKBytes + best.tile_n / 2 * kBlockKBytes
+                                         : kBlockM * kBlockKBytes + best.tile_n * kBlockKBytes) * k_per;
   int stages = (227 * 1024 - 2048 - kStoreStagingBytes) / stage_bytes;
   if (stages > 8) stages = 8;
   best.stages = stages;
@@ -200,14 +234,22 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
 
 
 // CTA-pair kernel: a 1-D grid of 2-CTA clusters, one cluster per 256 x kBN tile in flight.
-template <int kKind, int kBN, int kEpi>
+template <int kKind, int kBN, int kEpi, int kKPer>
 int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
-  using S = PairSmem<kBN>;
+  using S = PairSmem<kBN, kKPer>;
   CUtensorMap ma, mb;
-  int rc = encode_kmajor_map(ctx, &ma, kKind, c.A, c.M, c.K, c.lda, kBlockM);
-  if (rc) return rc;
-  rc = encode_kmajor_map(ctx, &mb, kKind, c.B, c.N, c.K, c.ldb, kBN / 2);
-  if (rc) return rc;
+  int rc;
+  if (kKPer == 1) {
+    rc = encode_kmajor_map(ctx, &ma, kKind, c.A, c.M, c.K, c.lda, kBlockM);
+    if (rc) return rc;
+    rc = encode_kmajor_map(ctx, &mb, kKind, c.B, c.N, c.K, c.ldb, kBN / 2);
+    if (rc) return rc;
+  } else {
+    rc = encode_kmajor_map_3d(ctx, &ma, kKind, c.A, c.M, c.K, c.lda, kBlockM, kKPer);
+    if (rc) return rc;
+    rc = encode_kmajor_map_3d(ctx, &mb, kKind, c.B, c.N, c.K, c.ldb, kBN / 2, kKPer);
+    if (rc) return rc;
+  }
 
   const int esize = kKind == KIND_I8 ? 1 : 2;
   const int cesize = kEpi == EPI_I8_SRS ? 1 : (kEpi == EPI_BF16 ? 2 : 4);
@@ -230,7 +272,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.debug = ctx->debug_mode;
   p.trace = ctx->trace;
 
-  auto kern = gemm_tn_pair_kernel<kKind, kBN, kEpi>;
+  auto kern = gemm_tn_pair_kernel<kKind, kBN, kEpi, kKPer>;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
   if (ks.smem_attr < S::kTotal) {
     AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
@@ -297,8 +339,10 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
 template <int kKind, int kEpi>
 int dispatch_bn(aiehlc_ctx* ctx, const GemmCall& c, int bn, bool pair, cudaStream_t st) {
   if (pair) {
-    if (bn == 256) return launch_pair<kKind, 256, kEpi>(ctx, c, st);
-    return launch_pair<kKind, 128, kEpi>(ctx, c, st);
+    // two K blocks per tile load when K is a whole number of 128-byte blocks (and there are enough of them)
+    const bool wide = wide_k_loads(ctx, kKind == KIND_I8 ? 1 : 2, c.K);
+    if (bn == 256) return wide ? launch_pair<kKind, 256, kEpi, 2>(ctx, c, st) : launch_pair<kKind, 256, kEpi, 1>(ctx, c, st);
+    return wide ? launch_pair<kKind, 128, kEpi, 2>(ctx, c, st) : launch_pair<kKind, 128, kEpi, 1>(ctx, c, st);
   }
   switch (bn) {
     case 256: return launch_one<kKind, 256, kEpi>(ctx, c, st);

@@ -22,10 +22,18 @@ namespace aiehlc {
 
 constexpr int kPairM = 256;
 
-template <int kBN>
+// kKPer = K blocks (of 128 bytes) fetched by ONE tile load and held by one pipeline stage.  The TMA
+// unit of an SM completes a tile load ("box") roughly every 280-340 cycles whatever its size up to
+// at least 16 KB (measured: stages of two boxes arrive 580-680 cycles apart for 5.5 KB, 24 KB and
+// 32 KB alike, three boxes 750), so with one K block per box the 512 MMA cycles of a 256 x 256
+// K block are not quite covered.  With kKPer = 2 the operands are viewed as 3-D tensors
+// {128 bytes, rows, K / 128 bytes} and a box {128 B, rows, 2} brings two K blocks at once.
+template <int kBN, int kKPer>
 struct PairSmem {
-  static constexpr int kABytes = kBlockM * kBlockKBytes;           // this CTA's 128 rows of A
-  static constexpr int kBBytes = (kBN / 2) * kBlockKBytes;         // this CTA's half of B
+  static constexpr int kABlock = kBlockM * kBlockKBytes;           // one K block of this CTA's 128 rows of A
+  static constexpr int kBBlock = (kBN / 2) * kBlockKBytes;         // one K block of this CTA's half of B
+  static constexpr int kABytes = kABlock * kKPer;
+  static constexpr int kBBytes = kBBlock * kKPer;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBudget = 227 * 1024 - 2048 - kStoreStagingBytes;
   static constexpr int kStagesRaw = kBudget / kStageBytes;
@@ -89,12 +97,13 @@ __device__ __forceinline__ void add_deposited_chunk(uint32_t (&r)[32], const int
   }
 }
 
-template <int kKind, int kBN, int kEpi>
+template <int kKind, int kBN, int kEpi, int kKPer>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-  using S = PairSmem<kBN>;
+  using S = PairSmem<kBN, kKPer>;
   constexpr int kStages = S::kStages;
+  static_assert(kStages >= 2, "pipeline needs at least two stages");
   constexpr int kBHalf = kBN / 2;
   constexpr uint32_t kTmemCols = 2 * kBN;
   constexpr int kElemBytes = kKind == KIND_I8 ? 1 : 2;
@@ -167,7 +176,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int u = pair_id; ok && work_unit(u, p, num_tiles, w); u += num_pairs) {
         int mb, nb;
         tile_coords(w.tile, p, mb, nb);
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; kb += kKPer) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
           if (!ok) break;
           const uint32_t fb_local = smem_u32(&full_bar[stage]);
@@ -180,10 +189,16 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const uint32_t fb = mapa_u32(fb_local, 0);  // the same barrier in the leader CTA
           uint8_t* sa = smem + stage * S::kStageBytes;
           uint8_t* sb = sa + S::kABytes;
-          tma_load_2d_pair(smem_u32(sa), &tmap_a, fb, kb * kBlockKElems,
-                           mb * kPairM + static_cast<int>(rank) * kBlockM);
-          tma_load_2d_pair(smem_u32(sb), &tmap_b, fb, kb * kBlockKElems,
-                           nb * kBN + static_cast<int>(rank) * kBHalf);
+          const int row_a = mb * kPairM + static_cast<int>(rank) * kBlockM;
+          const int row_b = nb * kBN + static_cast<int>(rank) * kBHalf;
+          if constexpr (kKPer == 1) {
+            tma_load_2d_pair(smem_u32(sa), &tmap_a, fb, kb * kBlockKElems, row_a);
+            tma_load_2d_pair(smem_u32(sb), &tmap_b, fb, kb * kBlockKElems, row_b);
+          } else {
+            // K blocks kb .. kb + kKPer - 1 in one box each; blocks past the end of K read as zero
+            tma_load_3d_pair(smem_u32(sa), &tmap_a, fb, 0, row_a, kb);
+            tma_load_3d_pair(smem_u32(sb), &tmap_b, fb, 0, row_b, kb);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -208,18 +223,23 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tc_fence_after();
         if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; kb += kKPer) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
           if (!ok) break;
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
           const uint32_t sb = sa + S::kABytes;
-          const uint64_t adesc = make_kmajor_desc(sa, 1024, 2);
-          const uint64_t bdesc = make_kmajor_desc(sb, 1024, 2);
           if (p.debug != 2) {
 #pragma unroll
-            for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
-              umma_ss<kKind, 2>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            for (int kk = 0; kk < kKPer; ++kk) {
+              if (kb + kk >= w.kb1) break;  // K blocks of this stage beyond the range: loaded, not multiplied
+              const uint64_t adesc = make_kmajor_desc(sa + kk * S::kABlock, 1024, 2);
+              const uint64_t bdesc = make_kmajor_desc(sb + kk * S::kBBlock, 1024, 2);
+#pragma unroll
+              for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
+                umma_ss<kKind, 2>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc,
+                                  (kb + kk > w.kb0 || k > 0) ? 1u : 0u);
+            }
           }
           umma_commit_pair_mask(smem_u32(&empty_bar[stage]), 3);  // frees the stage in both CTAs
           if (++stage == kStages) { stage = 0; phase ^= 1; }

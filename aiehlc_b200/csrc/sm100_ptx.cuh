@@ -285,6 +285,14 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 // Barrier arrival (not a data transfer) delivered to the barrier at this offset in every CTA of
 // `cta_mask` once all MMAs issued so far by this thread have retired.
 __device__ __forceinline__ void umma_commit_pair_mask(uint32_t bar, uint16_t cta_mask) {

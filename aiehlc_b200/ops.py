@@ -67,6 +67,9 @@ class Context:
     def set_cta_pair(self, mode: int) -> None:
         _capi.check(self._lib.aiehlc_set_cta_pair(self._h, int(mode)))
 
+    def set_k_per_load(self, k_blocks: int) -> None:
+        _capi.check(self._lib.aiehlc_set_k_per_load(self._h, int(k_blocks)))
+
     def set_tma_store(self, mode: int) -> None:
         """0: per-thread stores, 1: tile stores for int32/bf16 results (default), 2: for int8 results too."""
         _capi.check(self._lib.aiehlc_set_tma_store(self._h, int(mode)))

@@ -177,6 +177,10 @@ int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n);
  * fetching half of the B tile) wherever M > 128, 0 = one CTA per 128-row tile, -1 = choose per
  * shape (the default). */
 int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode);
+/* Tuning knob for the CTA-pair kernel: 128-byte K blocks fetched by one TMA tile load (and held by one
+ * pipeline stage).  2 needs K * element size to be a multiple of 128 bytes; 0 (default) = 2 where that
+ * holds, else 1. */
+int aiehlc_set_k_per_load(aiehlc_ctx* ctx, int k_blocks);
 /* Tuning knob: 1 (default) = the int32 and bf16 GEMM epilogues stage 32 rows x 128 bytes of results in
  * shared memory and write them with a TMA tile store (whole 128-byte lines, clipped at the edges of C;
  * `accumulate` uses the add-reduction form); 2 = the int8 srs epilogue does so too (measured slower than

@@ -187,6 +187,35 @@ def test_both_store_paths(ctx, tma_store):
         ctx.set_tma_store(1)
 
 
+@pytest.mark.parametrize("k_per_load", [1, 2])
+@pytest.mark.parametrize("shape", [(512, 512, 512), (520, 336, 640), (300, 520, 1152), (256, 256, 384), (1024, 384, 2176)])
+def test_k_blocks_per_tile_load(ctx, shape, k_per_load):
+    """CTA-pair kernel with one or two 128-byte K blocks per TMA tile load (odd and even block counts,
+    split-K ranges that end inside a pair of blocks); both settings give the oracle's bytes."""
+    M, N, K = shape
+    A = synth.int8_uniform(9, (M, K))
+    B = synth.int8_uniform(1009, (N, K))
+    ctx.set_k_per_load(k_per_load)
+    ctx.set_cta_pair(1)
+    try:
+        dA, dB = _dev(A), _dev(B)
+        assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), O.gemm_i8_i32(A, B))
+        for splitk in (1, 2):
+            assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift=8, splitk=splitk).cpu().numpy(),
+                                  O.gemm_i8_srs(A, B, shift=8, splitk=splitk))
+        Kb = K // 2                                                     # same K bytes per row as the int8 case
+        Ab = synth.normal_bf16_bits(4, (M, Kb))
+        Bb = synth.normal_bf16_bits(1004, (N, Kb))
+        got = ctx.gemm_bf16(_dev(Ab.view(np.int16)).view(torch.bfloat16), _dev(Bb.view(np.int16)).view(torch.bfloat16))
+        ref = O.gemm_bf16(Ab, Bb).astype(np.float64)
+        gf = got.float().cpu().numpy().astype(np.float64)
+        assert float(np.max(np.abs(gf - ref) / np.maximum(np.abs(ref), 1.0))) <= 1e-2      # the bf16 tolerance
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_k_per_load(0)
+        ctx.set_cta_pair(-1)
+
+
 def test_accumulate_and_flush(ctx):
     M, N, K = 200, 136, 512
     A = synth.int8_uniform(2, (M, K))

@@ -58,7 +58,9 @@ def test_gemm_planner_needs_no_gpu():
     assert (p["tile_m"], p["tile_n"], p["cta_pair"]) == (256, 256, 1)
     assert (p["grid_m"], p["grid_n"], p["tiles"], p["slots"], p["waves"]) == (16, 16, 256, 74, 4)
     assert abs(p["wave_efficiency"] - 256 / 296) < 1e-9
-    assert p["k_blocks"] == 32 and p["stages"] == 6 and p["tmem_columns"] == 512 and p["smem_bytes"] <= 227 * 1024
+    assert p["k_blocks"] == 32 and p["tmem_columns"] == 512 and p["smem_bytes"] <= 227 * 1024
+    # two 128-byte K blocks per tile load: three 64 KiB stages hold what six 32 KiB stages did
+    assert p["tile_k_bytes"] == 256 and p["stages"] == 3
     assert (p["a_shared_by"], p["b_shared_by"]) == (16, 16)   # A rows serve a grid row, B rows a grid column
     assert p["split_tail_parts"] == 1                         # tail balancing is opt-in
     p = plan_gemm(64, 64, 64)                           # one tile: a single CTA, the narrowest tile
