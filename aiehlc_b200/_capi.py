@@ -60,7 +60,8 @@ class GemmPlan(C.Structure):
                 ("waves", C.c_int), ("wave_efficiency", C.c_double), ("group_m", C.c_int), ("stages", C.c_int),
                 ("smem_bytes", C.c_int), ("tmem_columns", C.c_int), ("k_blocks", C.c_int), ("a_shared_by", C.c_int),
                 ("b_shared_by", C.c_int), ("wave_footprint_bytes", C.c_longlong), ("cost_units", C.c_double),
-                ("split_tail_tiles", C.c_int), ("split_tail_parts", C.c_int)]
+                ("split_tail_tiles", C.c_int), ("split_tail_parts", C.c_int),
+                ("narrow_tail_tiles", C.c_int)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -172,7 +172,8 @@ int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on) {
 
 int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
-  ctx->split_tail = on ? 1 : 0;
+  if (on < 0 || on > 2) return fail(AIEHLC_ERR_INVALID, "split_tail: 0 (off), 1 (K ranges) or 2 (column ranges)");
+  ctx->split_tail = on;
   return AIEHLC_OK;
 }
 

@@ -58,7 +58,7 @@ struct aiehlc_ctx {
   int pair_mode = -1;           // -1: choose per shape, 0: single-CTA tiles only, 1: CTA pairs wherever M > 128
   int k_per_load = 0;           // 0: choose, 1: one 128-byte K block per tile load, 2: two where K allows
   int tma_store = 1;            // epilogue results leave through shared memory + TMA tile stores when C allows
-  int split_tail = 0;           // cut the tiles of a thin last wave along K across idle CTA pairs (off: no measured gain yet)
+  int split_tail = 2;           // thin last wave: 1 = cut its tiles along K across idle CTA pairs, 2 = into two column ranges
   int group_m = 0;              // row-blocks per rasterisation group (0 = default for the kernel family)
   int pdl = 1;                  // launch the tensor-core kernels with programmatic stream serialization
   int debug_mode = 0;           // see GemmParams::debug
@@ -91,6 +91,7 @@ int launch_gemm(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st);
 int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* out);
 // Tail balancing: tiles [first, tiles) are cut into `parts` K ranges (parts == 1: no cut).
 void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int* parts);
+void narrow_tail(int tiles, int slots, int tile_n, int enabled, int* first, int* parts);
 
 // SIMT helpers (simt_kernels.cu)
 int launch_mm_i32(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K, cudaStream_t st);

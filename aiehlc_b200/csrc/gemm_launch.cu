@@ -89,7 +89,7 @@ int encode_c_map(aiehlc_ctx* ctx, CUtensorMap* map, int epi, int bn, void* base,
 void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int* parts) {
   *first = tiles;
   *parts = 1;
-  if (!enabled || slots <= 0) return;
+  if (enabled != 1 || slots <= 0) return;
   const int rem = tiles % slots;
   if (rem == 0 || rem * 2 > slots) return;
   int s = slots / rem;
@@ -106,6 +106,18 @@ void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int
 static bool wide_k_loads(const aiehlc_ctx* ctx, int esize, int K) {
   const long long kbytes = static_cast<long long>(K) * esize;
   return ctx->k_per_load != 1 && kbytes % kBlockKBytes == 0 && kbytes >= 4 * kBlockKBytes;
+}
+
+// The other cure for a thin last wave: its tiles are cut into two column ranges (half as wide MMAs, no
+// exchange between the ranges).  Only for 256-column pair tiles, whose halves are still full-rate MMAs.
+void narrow_tail(int tiles, int slots, int tile_n, int enabled, int* first, int* parts) {
+  *first = tiles;
+  *parts = 1;
+  if (enabled != 2 || slots <= 0 || tile_n != 256) return;
+  const int rem = tiles % slots;
+  if (rem == 0 || rem * 2 > slots) return;
+  *first = tiles - rem;
+  *parts = 2;
 }
 
 // The planner: B200 counterpart of the compiler's matmul tiling (tilinglinalg::creatematmul,
@@ -140,7 +152,14 @@ int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_
       pl.waves = static_cast<int>((pl.tiles + pl.slots - 1) / pl.slots);
       pl.wave_efficiency = static_cast<double>(pl.tiles) / (static_cast<double>(pl.waves) * pl.slots);
       // rows of the last row-block that fall outside M are computed all the same
-      pl.cost_units = static_cast<double>(pl.waves) * bn / eff[i] * (pr ? 0.97 : 1.0);
+      double waves = pl.waves;
+      {
+        // a thin last wave of 256-column pair tiles runs as 128-column ranges: measured 0.87 of a whole tile's time
+        int first = 0, parts = 1;
+        narrow_tail(static_cast<int>(pl.tiles), pl.slots, bn, pr ? ctx->split_tail : 0, &first, &parts);
+        if (parts > 1) waves -= 0.13;
+      }
+      pl.cost_units = waves * bn / eff[i] * (pr ? 0.97 : 1.0);
       if (best_cost < 0 || pl.cost_units < best_cost) { best_cost = pl.cost_units; best = pl; }
     }
   }
@@ -169,6 +188,8 @@ int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_
   split_tail(static_cast<int>(best.tiles), best.slots, best.k_blocks, best.cta_pair ? ctx->split_tail : 0, &first, &parts);
   best.split_tail_tiles = parts > 1 ? static_cast<int>(best.tiles) - first : 0;
   best.split_tail_parts = parts;
+  narrow_tail(static_cast<int>(best.tiles), best.slots, best.tile_n, best.cta_pair ? ctx->split_tail : 0, &first, &parts);
+  best.narrow_tail_tiles = parts > 1 ? static_cast<int>(best.tiles) - first : 0;
   *out = best;
   return AIEHLC_OK;
 }
@@ -237,7 +258,7 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
 template <int kKind, int kBN, int kEpi, int kKPer>
 int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   using S = PairSmem<kBN, kKPer>;
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mb_narrow;
   int rc;
   if (kKPer == 1) {
     rc = encode_kmajor_map(ctx, &ma, kKind, c.A, c.M, c.K, c.lda, kBlockM);
@@ -250,6 +271,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
     rc = encode_kmajor_map_3d(ctx, &mb, kKind, c.B, c.N, c.K, c.ldb, kBN / 2, kKPer);
     if (rc) return rc;
   }
+  mb_narrow = mb;  // replaced below when tail tiles are cut into column ranges
 
   const int esize = kKind == KIND_I8 ? 1 : 2;
   const int cesize = kEpi == EPI_I8_SRS ? 1 : (kEpi == EPI_BF16 ? 2 : 4);
@@ -330,8 +352,20 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
       pairs = units < max_pairs ? units : max_pairs;
     }
   }
+  p.nt_first_tile = tiles;
+  p.nt_parts = 1;
+  if (p.sk_parts == 1) {
+    narrow_tail(tiles, tiles < max_pairs ? max_pairs : pairs, kBN, ctx->split_tail, &p.nt_first_tile, &p.nt_parts);
+    if (p.nt_parts > 1) {
+      rc = kKPer == 1 ? encode_kmajor_map(ctx, &mb_narrow, kKind, c.B, c.N, c.K, c.ldb, kBN / 2 / p.nt_parts)
+                      : encode_kmajor_map_3d(ctx, &mb_narrow, kKind, c.B, c.N, c.K, c.ldb, kBN / 2 / p.nt_parts, kKPer);
+      if (rc) return rc;
+      const int units = p.nt_first_tile + (tiles - p.nt_first_tile) * p.nt_parts;
+      pairs = units < max_pairs ? units : max_pairs;
+    }
+  }
   cfg.gridDim = dim3(2 * pairs);
-  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, p));
+  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mb_narrow, mc, p));
   ctx->launches++;
   return AIEHLC_OK;
 }

@@ -62,6 +62,9 @@ struct GemmParams {
   int sk_first_tile, sk_parts;
   int32_t* sk_scratch;     // [tail tile][depositing range][CTA rank][32-column chunk] partial sums
   int* sk_flags;           // [tail tile][CTA rank][owning range (4 slots)] deposits so far; zero between launches
+  // The other form of tail balancing: tiles >= nt_first_tile are cut into nt_parts column ranges
+  // (narrower MMAs, no exchange between the ranges).  nt_parts == 1: off.  Never together with sk_parts > 1.
+  int nt_first_tile, nt_parts;
   long long* trace;        // measurement aid: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
   int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling)
 };
@@ -289,10 +292,10 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
 // per step: two TMEM loads are issued back to back, then waited for once.
 template <int kBN, int kEpi>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t taddr, int row, bool row_ok,
-                                                  int n0, StoreCtx& sc) {
+                                                  int n0, StoreCtx& sc, int ncols = kBN) {
   static_assert(kBN % 64 == 0, "accumulator is drained 64 columns at a time");
 #pragma unroll 1
-  for (int c = 0; c < kBN; c += 64) {
+  for (int c = 0; c < ncols; c += 64) {
     __syncwarp();  // lanes that skipped stores rejoin before the warp-wide TMEM loads
     uint32_t ra[32], rb[32];
     tmem_ld_32x32b_x32(taddr + c, ra);

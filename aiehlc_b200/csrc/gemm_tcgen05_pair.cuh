@@ -42,26 +42,38 @@ struct PairSmem {
   static constexpr int kTotal = kStages * kStageBytes + kStoreStagingBytes + kBarBytes + 1024;
 };
 
-// One unit of work of a CTA pair: a whole tile, or one K range of a tail tile.
+// One unit of work of a CTA pair: a whole tile, one K range of a tail tile, or one column range of a tail tile.
 struct WorkUnit {
   int tile, kb0, kb1, part, parts;
+  int n_part, n_parts;  // column range n_part of n_parts (1 = all kBN columns)
 };
 // Unit number `u` of the launch (pair p runs units p, p + pairs, p + 2 pairs, ...).
 __device__ __forceinline__ bool work_unit(int u, const GemmParams& p, int num_tiles, WorkUnit& w) {
+  if (p.nt_parts > 1) {
+    if (u < p.nt_first_tile) {
+      w = WorkUnit{u, 0, p.num_k_blocks, 0, 1, 0, 1};
+      return true;
+    }
+    const int v = u - p.nt_first_tile;
+    w = WorkUnit{p.nt_first_tile + v / p.nt_parts, 0, p.num_k_blocks, 0, 1, v % p.nt_parts, p.nt_parts};
+    return w.tile < num_tiles;
+  }
   if (u < p.sk_first_tile) {
-    w = WorkUnit{u, 0, p.num_k_blocks, 0, 1};
+    w = WorkUnit{u, 0, p.num_k_blocks, 0, 1, 0, 1};
     return true;
   }
   const int v = u - p.sk_first_tile;
   if (p.sk_parts <= 1 || v >= (num_tiles - p.sk_first_tile) * p.sk_parts) {
     if (p.sk_parts > 1 || u >= num_tiles) return false;
-    w = WorkUnit{u, 0, p.num_k_blocks, 0, 1};
+    w = WorkUnit{u, 0, p.num_k_blocks, 0, 1, 0, 1};
     return true;
   }
   const int part = v % p.sk_parts;
   w.tile = p.sk_first_tile + v / p.sk_parts;
   w.part = part;
   w.parts = p.sk_parts;
+  w.n_part = 0;
+  w.n_parts = 1;
   w.kb0 = static_cast<int>(static_cast<long long>(part) * p.num_k_blocks / p.sk_parts);
   w.kb1 = static_cast<int>(static_cast<long long>(part + 1) * p.num_k_blocks / p.sk_parts);
   return true;
@@ -100,7 +112,8 @@ __device__ __forceinline__ void add_deposited_chunk(uint32_t (&r)[32], const int
 template <int kKind, int kBN, int kEpi, int kKPer>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_b_narrow, const __grid_constant__ CUtensorMap tmap_c,
+                    const GemmParams p) {
   using S = PairSmem<kBN, kKPer>;
   constexpr int kStages = S::kStages;
   static_assert(kStages >= 2, "pipeline needs at least two stages");
@@ -148,6 +161,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.nt_parts > 1) tma_prefetch_desc(&tmap_b_narrow);
   }
   if (warp == 1) {
     tmem_alloc<2>(smem_u32(tmem_base_slot), kTmemCols);
@@ -185,19 +199,22 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (++stage == kStages) { stage = 0; phase ^= 1; }
             continue;
           }
-          if (leader) mbar_expect_tx(fb_local, 2 * S::kStageBytes);  // both CTAs' bytes
+          // a column range of a tail tile brings kBHalf / n_parts rows of B per CTA (its own tensor map: smaller box)
+          const int b_rows = kBHalf / w.n_parts;
+          if (leader) mbar_expect_tx(fb_local, 2 * (S::kABytes + S::kBBytes / w.n_parts));  // both CTAs' bytes
           const uint32_t fb = mapa_u32(fb_local, 0);  // the same barrier in the leader CTA
           uint8_t* sa = smem + stage * S::kStageBytes;
           uint8_t* sb = sa + S::kABytes;
           const int row_a = mb * kPairM + static_cast<int>(rank) * kBlockM;
-          const int row_b = nb * kBN + static_cast<int>(rank) * kBHalf;
+          const int row_b = nb * kBN + w.n_part * 2 * b_rows + static_cast<int>(rank) * b_rows;
+          const CUtensorMap* tb = w.n_parts == 1 ? &tmap_b : &tmap_b_narrow;
           if constexpr (kKPer == 1) {
             tma_load_2d_pair(smem_u32(sa), &tmap_a, fb, kb * kBlockKElems, row_a);
-            tma_load_2d_pair(smem_u32(sb), &tmap_b, fb, kb * kBlockKElems, row_b);
+            tma_load_2d_pair(smem_u32(sb), tb, fb, kb * kBlockKElems, row_b);
           } else {
             // K blocks kb .. kb + kKPer - 1 in one box each; blocks past the end of K read as zero
             tma_load_3d_pair(smem_u32(sa), &tmap_a, fb, 0, row_a, kb);
-            tma_load_3d_pair(smem_u32(sb), &tmap_b, fb, 0, row_b, kb);
+            tma_load_3d_pair(smem_u32(sb), tb, fb, 0, row_b, kb);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -208,7 +225,6 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer (leader CTA only)
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc<kKind>(kPairM, kBN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -223,6 +239,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tc_fence_after();
         if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
         const uint32_t d_tmem = tmem_base + acc * kBN;
+        const uint32_t idesc = make_idesc<kKind>(kPairM, kBN / w.n_parts);
+        const uint32_t b_block = S::kBBlock / w.n_parts;  // the K blocks of a box lie back to back
         for (int kb = w.kb0; kb < w.kb1; kb += kKPer) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
           if (!ok) break;
@@ -234,7 +252,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int kk = 0; kk < kKPer; ++kk) {
               if (kb + kk >= w.kb1) break;  // K blocks of this stage beyond the range: loaded, not multiplied
               const uint64_t adesc = make_kmajor_desc(sa + kk * S::kABlock, 1024, 2);
-              const uint64_t bdesc = make_kmajor_desc(sb + kk * S::kBBlock, 1024, 2);
+              const uint64_t bdesc = make_kmajor_desc(sb + kk * b_block, 1024, 2);
 #pragma unroll
               for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
                 umma_ss<kKind, 2>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc,
@@ -274,7 +292,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
       sc.warp_row0 = row - lane;
       if (w.parts == 1) {
-        drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN, sc);
+        const int ncols = kBN / w.n_parts;
+        drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN + w.n_part * ncols, sc, ncols);
       } else {
         // tail tile cut along K; scratch is [tail tile][depositing range][CTA rank][chunk]
         constexpr int kChunks = kBN / 32;

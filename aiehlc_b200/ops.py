@@ -74,8 +74,9 @@ class Context:
         """0: per-thread stores, 1: tile stores for int32/bf16 results (default), 2: for int8 results too."""
         _capi.check(self._lib.aiehlc_set_tma_store(self._h, int(mode)))
 
-    def set_split_tail(self, on: bool) -> None:
-        _capi.check(self._lib.aiehlc_set_split_tail(self._h, 1 if on else 0))
+    def set_split_tail(self, mode) -> None:
+        """Thin last wave: 0/False = tiles whole, 1/True = cut along K, 2 = cut into two column ranges."""
+        _capi.check(self._lib.aiehlc_set_split_tail(self._h, int(mode)))
 
     def set_group_m(self, group_m: int) -> None:
         _capi.check(self._lib.aiehlc_set_group_m(self._h, int(group_m)))

@@ -146,6 +146,7 @@ typedef struct {
   double cost_units;                 /* the quantity the choice minimises: waves x tile_n / efficiency factor */
   int split_tail_tiles;              /* tiles of a thin last wave that are cut along K (int8 pair kernel), else 0 */
   int split_tail_parts;              /* K ranges per such tile (1 = none) */
+  int narrow_tail_tiles;             /* tiles of a thin last wave that are cut into two column ranges, else 0 */
 } aiehlc_gemm_plan;
 /* kind: 0 = int8, 1 = bf16.  ctx may be NULL: the plan is then made for a 148-SM B200 with default knobs. */
 int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* plan);
@@ -187,11 +188,14 @@ int aiehlc_set_k_per_load(aiehlc_ctx* ctx, int k_blocks);
  * its per-thread 32-byte stores); 0 = every thread stores its own row directly.  Tile stores need C
  * 16-byte aligned with a 16-byte row pitch; otherwise the direct path is taken whatever the setting. */
 int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on);
-/* Tuning knob: 1 = when the last wave of an int8 CTA-pair launch is at most half full, its tiles are
- * cut along K across the idle pairs; the K ranges of a tile exchange int32 partial sums through a
- * context workspace and each runs the output stage on its share of the columns (integer sums:
- * bit-identical results).  0 (default) = every tile computed whole: on the 4096^3 benchmark the
- * exchange costs about what the shorter main loop saves. */
+/* Tuning knob for a thin last wave (at most half of the CTA pairs busy) of a CTA-pair launch:
+ *   1 = (int8 only) its tiles are cut along K into up to 4 ranges run by otherwise idle pairs; the ranges
+ *       exchange int32 partial sums through a context workspace and each runs the output stage on its
+ *       share of the columns (integer sums: bit-identical results);
+ *   2 = (default) its 256-column tiles are cut into two 128-column ranges run by different pairs (narrower
+ *       MMAs, nothing to exchange; every output element is still one accumulation over K in the same
+ *       order); measured 48.3 us against 49.7 us on the 4096^3 benchmark;
+ *   0 = every tile computed whole. */
 int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on);
 /* Tuning knob: number of tile row-blocks the persistent scheduler walks before it moves to the next
  * tile column (the L2 footprint of one wave is group_m row-blocks of A plus slots/group_m column-blocks

@@ -158,7 +158,40 @@ def test_split_tail_tiles_are_bit_identical(ctx, shape):
         assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), exp32)
         assert ctx.sync() == 0
     finally:
-        ctx.set_split_tail(False)
+        ctx.set_split_tail(2)
+        ctx.set_cta_pair(-1)
+
+
+@pytest.mark.parametrize("k_per_load", [1, 2])
+@pytest.mark.parametrize("shape", [(2304, 2304, 512), (2560, 2304, 384), (2500, 2400, 640), (2560, 2000, 272)])
+def test_tail_tiles_cut_into_column_ranges(ctx, shape, k_per_load):
+    """A thin last wave of 256-column pair tiles is cut into two 128-column ranges (narrower MMAs, a second
+    tensor map for B): same bits as the oracle for int32 and srs results, same bits as the uncut schedule
+    for bf16 (every element is still one accumulation over K in the same order)."""
+    from aiehlc_b200.ops import plan_gemm
+    M, N, K = shape
+    ctx.set_cta_pair(1)
+    ctx.set_tile_n(256)
+    ctx.set_k_per_load(k_per_load)
+    try:
+        A = synth.int8_uniform(11, (M, K))
+        B = synth.int8_uniform(1011, (N, K))
+        dA, dB = _dev(A), _dev(B)
+        Ab = _dev(synth.normal_bf16_bits(12, (M, K // 2)).view(np.int16)).view(torch.bfloat16)
+        Bb = _dev(synth.normal_bf16_bits(1012, (N, K // 2)).view(np.int16)).view(torch.bfloat16)
+        ctx.set_split_tail(0)
+        whole = ctx.gemm_bf16(Ab, Bb)
+        ctx.set_split_tail(2)
+        assert plan_gemm(M, N, K, ctx=ctx)["narrow_tail_tiles"] > 0
+        for _ in range(2):
+            assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), O.gemm_i8_i32(A, B))
+            assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift=9).cpu().numpy(), O.gemm_i8_srs(A, B, shift=9))
+        assert torch.equal(ctx.gemm_bf16(Ab, Bb), whole)
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_split_tail(2)
+        ctx.set_k_per_load(0)
+        ctx.set_tile_n(0)
         ctx.set_cta_pair(-1)
 
 

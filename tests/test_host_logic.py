@@ -62,7 +62,7 @@ def test_gemm_planner_needs_no_gpu():
     # two 128-byte K blocks per tile load: three 64 KiB stages hold what six 32 KiB stages did
     assert p["tile_k_bytes"] == 256 and p["stages"] == 3
     assert (p["a_shared_by"], p["b_shared_by"]) == (16, 16)   # A rows serve a grid row, B rows a grid column
-    assert p["split_tail_parts"] == 1                         # tail balancing is opt-in
+    assert p["split_tail_parts"] == 1 and p["narrow_tail_tiles"] == 34   # last wave: 34 tiles as 68 column ranges
     p = plan_gemm(64, 64, 64)                           # one tile: a single CTA, the narrowest tile
     assert (p["tile_m"], p["tile_n"], p["cta_pair"], p["tiles"], p["waves"]) == (128, 64, 0, 1, 1)
     p = plan_gemm(8192, 8192, 8192, kind="bf16")
