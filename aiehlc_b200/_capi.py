@@ -27,6 +27,8 @@ SIGNATURES = {
     "aiehlc_mm_i32_dev": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
     "aiehlc_mm_i32_host": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int]),
     "aiehlc_gemm_i8_i32_dev": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
+    "aiehlc_gemm_i8_i32_scatter_dev": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                 C.c_int, _vp]),
     "aiehlc_gemm_i8_i32_host": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int]),
     "aiehlc_gemm_i8_srs_dev": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp,
                                          C.c_int, _vp]),

@@ -196,6 +196,18 @@ int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_
 
 namespace {
 
+// Shard-interleaved visiting order: possible when every shard is full and holds a whole number of
+// row-block groups (otherwise the rows are visited in order, which is still correct).
+void set_shard_rotation(GemmParams& p, const GemmCall& c, int tile_m) {
+  p.rot_shards = 0;
+  if (c.num_shards < 2 || c.rows_per_shard % tile_m != 0) return;
+  const int bps = c.rows_per_shard / tile_m;
+  if (static_cast<long long>(c.num_shards) * c.rows_per_shard != c.M || p.group_m <= 0 || bps % p.group_m != 0) return;
+  p.rot_shards = c.num_shards;
+  p.rot_first = ((c.first_shard % c.num_shards) + c.num_shards) % c.num_shards;
+  p.rot_blocks_per_shard = bps;
+}
+
 template <int kKind, int kBN, int kEpi>
 int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   using S = GemmSmem<kBN>;
@@ -225,7 +237,12 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   // bound by its integer arithmetic: per-thread stores are faster there unless tile stores are forced (2)
   p.tma_store = (vec && (ctx->tma_store == 2 || (ctx->tma_store == 1 && kEpi != EPI_I8_SRS))) ? 1 : 0;
   CUtensorMap mc = ma;  // unused unless tma_store
-  if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
+  if (c.c_shard_maps) {
+    p.vec_ok = 1; p.tma_store = 1;  // the shards were checked when their maps were made
+    p.c_shard_maps = c.c_shard_maps; p.rows_per_shard = c.rows_per_shard; p.num_shards = c.num_shards;
+    set_shard_rotation(p, c, kPairM);
+    set_shard_rotation(p, c, kBlockM);
+  } else if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
   p.status = ctx->d_status;
   p.debug = ctx->debug_mode;
   p.trace = ctx->trace;
@@ -289,7 +306,10 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0)) ? 1 : 0;
   p.tma_store = (p.vec_ok && (ctx->tma_store == 2 || (ctx->tma_store == 1 && kEpi != EPI_I8_SRS))) ? 1 : 0;
   CUtensorMap mc = ma;  // unused unless tma_store
-  if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
+  if (c.c_shard_maps) {
+    p.vec_ok = 1; p.tma_store = 1;  // the shards were checked when their maps were made
+    p.c_shard_maps = c.c_shard_maps; p.rows_per_shard = c.rows_per_shard; p.num_shards = c.num_shards;
+  } else if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
   p.status = ctx->d_status;
   p.debug = ctx->debug_mode;
   p.trace = ctx->trace;
@@ -334,7 +354,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   // Tail balancing (int32 accumulation only: sums of partial sums are exact; fp32 would change rounding)
   p.sk_first_tile = tiles;
   p.sk_parts = 1;
-  if (kKind == KIND_I8) {
+  if (kKind == KIND_I8 && !c.c_shard_maps) {  // the K ranges store per thread: not into a sharded output
     split_tail(tiles, tiles < max_pairs ? max_pairs : pairs, p.num_k_blocks, ctx->split_tail, &p.sk_first_tile, &p.sk_parts);
     if (p.sk_parts > 1) {
       const int tail = tiles - p.sk_first_tile;

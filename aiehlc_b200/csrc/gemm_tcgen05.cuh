@@ -62,6 +62,16 @@ struct GemmParams {
   int sk_first_tile, sk_parts;
   int32_t* sk_scratch;     // [tail tile][depositing range][CTA rank][32-column chunk] partial sums
   int* sk_flags;           // [tail tile][CTA rank][owning range (4 slots)] deposits so far; zero between launches
+  // Row-sharded output (EPI_I32_ACC through tile stores only): rows [g * rows_per_shard, (g + 1) *
+  // rows_per_shard) of C are the tensor c_shard_maps[g] (device array), which may lie in the memory of
+  // another GPU; results are ADDED there.  rows_per_shard is a multiple of 128, so the 128 rows of a
+  // CTA never straddle two shards.  Null: C is the one tensor of the kernel's tensor-map argument.
+  const CUtensorMap* c_shard_maps;
+  int rows_per_shard, num_shards;
+  // Visiting order for a sharded output: consecutive groups of row-blocks belong to consecutive shards,
+  // starting with shard rot_first, so that GPUs that run the same product with different rot_first send
+  // to different owners at any moment and every link is busy throughout.  rot_shards == 0: rows in order.
+  int rot_shards, rot_first, rot_blocks_per_shard;
   // The other form of tail balancing: tiles >= nt_first_tile are cut into nt_parts column ranges
   // (narrower MMAs, no exchange between the ranges).  nt_parts == 1: off.  Never together with sk_parts > 1.
   int nt_first_tile, nt_parts;
@@ -125,6 +135,11 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb,
   const int r = t - g * per_group;
   mb = first_m + r % rows;
   nb = r / rows;
+  if (p.rot_shards > 0) {
+    // virtual group g (of group_m row-blocks) -> shard (g + rot_first) mod shards, group g / shards inside it
+    const int shard = (g + p.rot_first) % p.rot_shards;
+    mb = shard * p.rot_blocks_per_shard + (g / p.rot_shards) * p.group_m + (mb - first_m);
+  }
 }
 
 // Where an epilogue warp puts its results when they leave through TMA tile stores.
@@ -136,6 +151,15 @@ struct StoreCtx {
   int lane;
   int warp_row0;        // first row of C this warp's 32 TMEM lanes map to
 };
+
+// Row-sharded output: points the warp's stores at the shard that owns the CTA's 128 rows.
+__device__ __forceinline__ void select_shard(const GemmParams& p, int cta_row0, StoreCtx& sc) {
+  if (p.c_shard_maps == nullptr) return;
+  int owner = cta_row0 / p.rows_per_shard;
+  if (owner >= p.num_shards) owner = p.num_shards - 1;  // rows past M: clipped by the shard's own extent
+  sc.tmap = p.c_shard_maps + owner;
+  sc.warp_row0 -= owner * p.rows_per_shard;
+}
 
 // Stages one 32-column chunk of this warp's 32 rows; once a group of chunks fills a row of
 // kGroupBytes (128 B, or the whole tile width if that is less) one tile store (or add-reduction)
@@ -470,6 +494,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
       sc.warp_row0 = row - lane;
+      select_shard(p, mb * kBlockM, sc);
       drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN, sc);
       // Accumulator drained: hand it back to the MMA issuer.
       tc_fence_before();

@@ -291,6 +291,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
       sc.warp_row0 = row - lane;
+      select_shard(p, mb * kPairM + static_cast<int>(rank) * kBlockM, sc);
       if (w.parts == 1) {
         const int ncols = kBN / w.n_parts;
         drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN + w.n_part * ncols, sc, ncols);

@@ -177,6 +177,29 @@ class Context:
             self._dev(out, torch.int32, "C"), M, N, K, 1 if accumulate else 0, self._stream()))
         return out
 
+    def bound_gemm_i8_i32_scatter(self, A, B, shard_ptrs, rows_per_shard: int, N: int, first_shard: int = 0):
+        """C += A . B^T with rows [g * rows_per_shard, ...) of C at device address shard_ptrs[g] (dense int32
+        [rows][N]; may be another GPU's memory).  Returns a callable that issues the launch."""
+        import ctypes
+        import torch
+        M, K = A.shape
+        if B.shape != (N, K):
+            raise ValueError("gemm_i8_i32_scatter: B must be [N][K]")
+        arr = (ctypes.c_void_p * len(shard_ptrs))(*[int(p) for p in shard_ptrs])
+        args = (self._h, self._dev(A, torch.int8, "A"), self._dev(B, torch.int8, "B"), arr, len(shard_ptrs),
+                int(rows_per_shard), int(first_shard), M, N, K, self._stream())
+        fn, check = self._lib.aiehlc_gemm_i8_i32_scatter_dev, _capi.check
+        return lambda: check(fn(*args))
+
+    def gemm_i8_i32_scatter(self, A, B, shards, rows_per_shard: int, first_shard: int = 0):
+        """Adds A . B^T into the row shards (a list of int32 tensors [rows][N] on this or a peer GPU)."""
+        N = shards[0].shape[1]
+        for s in shards:
+            if s.dtype != __import__("torch").int32 or not s.is_contiguous() or s.shape[1] != N:
+                raise ValueError("gemm_i8_i32_scatter: shards must be contiguous int32 [rows][N]")
+        self.bound_gemm_i8_i32_scatter(A, B, [s.data_ptr() for s in shards], rows_per_shard, N, first_shard)()
+        return shards
+
     def gemm_i8_srs(self, A, B, shift: int = 0, shift_vec=None, acc_in=None, splitk: int = 1, out=None):
         import torch
         M, K = A.shape

@@ -27,6 +27,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 L2_BYTES = 126 * 1024 * 1024
+NVLINK_GBS = 770.0   # measured peer-copy bandwidth per direction per GPU on this pool (nominal 900)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures (profiles/)
 NCU_TRAFFIC_BYTES = {"cfg2": 33.7e6}
 
@@ -209,6 +210,9 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-lib", action="store_true", help="skip the library int8 GEMM timing")
     ap.add_argument("--sets", type=int, default=0, help="number of rotating input sets (0 = enough to exceed L2)")
+    ap.add_argument("--splitk-exchange", default="fused", choices=["fused", "nccl"],
+                    help="cfg5_splitk: partial sums added into the owners' shards by the GEMM epilogue over peer "
+                         "memory (fused), or a full partial matrix followed by NCCL reduce-scatter (nccl)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -303,9 +307,26 @@ def main() -> int:
                    else f"one input set of {set_bytes / 1e6:.0f} MB > 126 MB L2" if set_bytes > L2_BYTES
                    else f"single input set of {set_bytes / 1e6:.1f} MB")
         rs_out = None
+        fused_call = None
         if kind == "i8_i32_splitk":
             rows_out = M // world
             rs_out = torch.empty((rows_out, N), dtype=torch.int32, device=dev)
+            if world > 1 and args.splitk_exchange == "fused":
+                # every rank's shard of C in memory all ranks can address; the epilogue adds into the owner's shard
+                try:
+                    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer mappings only
+                    import torch.distributed._symmetric_memory as symm
+                    sym_out = symm.empty((rows_out, N), dtype=torch.int32, device=dev)
+                    hdl = symm.rendezvous(sym_out, dist.group.WORLD)
+                    peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
+                    fused_call = ctx.bound_gemm_i8_i32_scatter(As[0], Bs[0], peer_ptrs, rows_out, N, first_shard=rank + 1)
+                    tick = torch.zeros(1, dtype=torch.int32, device=dev)
+                    extra["splitk_exchange"] = "fused: tile add-reductions into the owners' shards over peer memory"
+                except Exception as exc:  # noqa: BLE001
+                    fused_call = None
+                    extra["splitk_exchange"] = f"nccl reduce-scatter (peer memory unavailable: {type(exc).__name__}: {exc})"[:200]
+            elif world > 1:
+                extra["splitk_exchange"] = "nccl reduce-scatter of a full int32 partial matrix"
 
         # every argument of the C-ABI call is converted once, outside the timed region
         if kind == "i8_srs":
@@ -317,9 +338,24 @@ def main() -> int:
 
         def step(i):
             j = i % nsets
+            if fused_call is not None:
+                sym_out.zero_()
+                dist.all_reduce(tick)        # stream-ordered: every shard is zero before anyone adds into it
+                fused_call()
+                dist.all_reduce(tick)        # ... and every contribution has landed before anyone reads
+                return
             calls[j]()
             if kind == "i8_i32_splitk" and world > 1:
                 dist.reduce_scatter_tensor(rs_out, Cs[j], op=dist.ReduceOp.SUM)
+
+        if fused_call is not None:
+            # once, outside the timed region: the fused exchange gives what GEMM + NCCL reduce-scatter gives
+            step(0)
+            calls[0]()
+            dist.reduce_scatter_tensor(rs_out, Cs[0], op=dist.ReduceOp.SUM)
+            same = torch.tensor([1 if torch.equal(rs_out, sym_out) else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            extra["splitk_exchange_matches_nccl"] = bool(int(same.item()))
         unit = "TFLOPS" if kind == "bf16" else "TOPS"
         dtype = "bf16" if kind == "bf16" else "int8"
 
@@ -372,6 +408,17 @@ def main() -> int:
                     "note": (f"peak = 2 x measured bf16 {which} (kind::i8 has twice the K per instruction)"
                              if dtype == "int8" else f"peak = measured bf16 {which}") +
                             f", of {peaks['source']}; timed region {elapsed_ms:.0f} ms"}
+    if kind == "i8_i32_splitk" and world > 1:
+        # compute step followed by an exchange: the target time is the slower of the two legs
+        wire_bytes = (world - 1) / world * wl["M"] * wl["N"] * 4            # int32 partial sums leaving this GPU
+        t_math = ops_per_step / (peak * 1e12)
+        t_wire = wire_bytes / (NVLINK_GBS * 1e9)
+        gbs = wire_bytes / (per_launch_ms * 1e-3) / 1e9
+        roofline = {"bound": "nvlink", "achieved": gbs, "peak": NVLINK_GBS, "unit": "GB/s",
+                    "frac": max(t_math, t_wire) / (per_launch_ms * 1e-3), "traffic": None,
+                    "note": f"target = max(math {t_math * 1e3:.2f} ms at the tensor peak, wire {t_wire * 1e3:.2f} ms: "
+                            f"{wire_bytes / 1e9:.2f} GB of int32 partial sums per GPU at the measured {NVLINK_GBS:.0f} GB/s "
+                            "peer-copy rate per direction); frac = target / measured step"}
     extra.update(extra_measurements(args, wl, ctx, dev, kind, rank))
 
     # ---------------------------------------------------------------- end-to-end through the host API

@@ -249,6 +249,42 @@ def test_k_blocks_per_tile_load(ctx, shape, k_per_load):
         ctx.set_cta_pair(-1)
 
 
+@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("M,N,K,rows_per_shard,group_m,first_shard",
+                         [(1000, 520, 272, 256, 0, 0), (2304, 2304, 512, 1152, 0, 1), (640, 256, 1024, 128, 0, 3),
+                          (300, 64, 96, 384, 0, 0),
+                          (2048, 512, 256, 512, 2, 1), (4096, 256, 128, 512, 1, 5)])   # shard-interleaved tile order
+def test_row_sharded_add_reduction_output(ctx, M, N, K, rows_per_shard, group_m, first_shard, pair):
+    """GEMM whose epilogue adds into a row-sharded C (the fused split-K exchange; here every shard is
+    local): zeroed shards receive the product, a second K slice adds to it, rows past M stay untouched;
+    the visiting order (first_shard) never changes the result."""
+    A = synth.int8_uniform(13, (M, K))
+    B = synth.int8_uniform(1013, (N, K))
+    n_shards = -(-M // rows_per_shard)
+    shards = [torch.zeros((rows_per_shard, N), dtype=torch.int32, device=DEV) for _ in range(n_shards)]
+    shards[-1] += 77                                                   # rows past M must keep this
+    ctx.set_cta_pair(pair)
+    ctx.set_group_m(group_m)
+    try:
+        half = K // 2 // 16 * 16
+        dA, dB = _dev(A), _dev(B)
+        ctx.gemm_i8_i32_scatter(dA[:, :half].contiguous(), dB[:, :half].contiguous(), shards, rows_per_shard, first_shard)
+        ctx.gemm_i8_i32_scatter(dA[:, half:].contiguous(), dB[:, half:].contiguous(), shards, rows_per_shard, first_shard + 1)
+        assert ctx.sync() == 0
+        got = torch.cat(shards).cpu().numpy()
+        exp = O.gemm_i8_i32(A, B)
+        exp[(n_shards - 1) * rows_per_shard:] += 77
+        assert np.array_equal(got[:M], exp)
+        assert np.all(got[M:] == 77)
+    finally:
+        ctx.set_cta_pair(-1)
+        ctx.set_group_m(0)
+    with pytest.raises(_capi.AiehlcError):
+        ctx.gemm_i8_i32_scatter(dA, dB, shards, 100)                   # not a multiple of 128
+    with pytest.raises(_capi.AiehlcError):
+        ctx.gemm_i8_i32_scatter(dA, dB, shards[:1], 128)               # shards do not cover M
+
+
 def test_accumulate_and_flush(ctx):
     M, N, K = 200, 136, 512
     A = synth.int8_uniform(2, (M, K))
