@@ -120,7 +120,7 @@ int aiehlc_destroy(aiehlc_ctx* ctx) {
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   ctx->buf_a.release(); ctx->buf_b.release(); ctx->buf_c.release(); ctx->buf_aux.release();
   ctx->pack_a.release(); ctx->pack_b.release();
-  ctx->sk_scratch.release(); ctx->sk_flags.release(); ctx->shard_maps.release();
+  ctx->sk_scratch.release(); ctx->sk_flags.release();
   delete ctx;
   return AIEHLC_OK;
 }
@@ -264,35 +264,19 @@ int aiehlc_gemm_i8_i32_scatter_dev(aiehlc_ctx* ctx, const int8_t* A, const int8_
     return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32_scatter: the shards do not cover M rows");
   if (M == 0 || N == 0 || K == 0) return AIEHLC_OK;  // nothing to add
   if (!A || !B) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32_scatter: null operand");
-  if (N % 4 != 0) return fail(AIEHLC_ERR_UNSUPPORTED, "gemm_i8_i32_scatter: N must be a multiple of 4 (16-byte rows)");
+  static_assert(AIEHLC_MAX_SHARDS == kMaxShards, "header and kernel agree on the shard limit");
   const int used = (M + rows_per_shard - 1) / rows_per_shard;
   for (int g = 0; g < used; ++g)
-    if (!shards[g] || reinterpret_cast<uintptr_t>(shards[g]) % 16 != 0)
-      return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32_scatter: shard pointers must be non-null and 16-byte aligned");
+    if (!shards[g] || reinterpret_cast<uintptr_t>(shards[g]) % 4 != 0)
+      return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32_scatter: shard pointers must be non-null and 4-byte aligned");
   cudaStream_t st = pick_stream(ctx, stream);
 
-  // the shards' tensor maps live in a context buffer; they are rebuilt only when the call differs
-  std::vector<unsigned long long> key = {static_cast<unsigned long long>(M), static_cast<unsigned long long>(N),
-                                         static_cast<unsigned long long>(rows_per_shard),
-                                         static_cast<unsigned long long>(num_shards)};
-  for (int g = 0; g < used; ++g) key.push_back(reinterpret_cast<unsigned long long>(shards[g]));
-  if (key != ctx->shard_key) {
-    CUtensorMap maps[AIEHLC_MAX_SHARDS];
-    for (int g = 0; g < num_shards; ++g) {
-      const int src = g < used ? g : 0;  // shards past M are never addressed
-      const long long rows = src == used - 1 ? M - static_cast<long long>(src) * rows_per_shard : rows_per_shard;
-      if ((rc = encode_c_map(ctx, &maps[g], EPI_I32_ACC, 256, shards[src], rows, N, N))) return rc;
-    }
-    if (ctx->shard_maps.reserve(sizeof maps)) return AIEHLC_ERR_NOMEM;
-    // pageable source: the copy has left `maps` when the call returns, and it is ordered on `st`
-    // before the kernel that reads it
-    AIEHLC_CUDA(cudaMemcpyAsync(ctx->shard_maps.ptr, maps, sizeof(CUtensorMap) * num_shards, cudaMemcpyHostToDevice, st));
-    ctx->shard_key = key;
-  }
   GemmCall c{};
   c.kind = KIND_I8; c.epi = EPI_I32_ACC;
   c.A = A; c.B = B; c.C = nullptr; c.M = M; c.N = N; c.K = K; c.lda = K; c.ldb = K; c.ldc = N;
-  c.c_shard_maps = static_cast<const CUtensorMap*>(ctx->shard_maps.ptr);
+  int32_t* ptrs[AIEHLC_MAX_SHARDS];
+  for (int g = 0; g < num_shards; ++g) ptrs[g] = shards[g < used ? g : 0];  // shards past M are never addressed
+  c.shards = ptrs;
   c.rows_per_shard = rows_per_shard; c.num_shards = num_shards; c.first_shard = first_shard;
   return launch_gemm(ctx, c, st);
 }

@@ -208,6 +208,15 @@ void set_shard_rotation(GemmParams& p, const GemmCall& c, int tile_m) {
   p.rot_blocks_per_shard = bps;
 }
 
+// With `slots` persistent CTAs (or pairs) a slot runs tiles slot, slot + slots, ...; its tiles cycle
+// through all shards only if slots and the number of shards have no common factor.  Otherwise some
+// slots would send everything to one remote owner while others only add locally.
+int coprime_slots(int slots, int shards) {
+  auto gcd = [](int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; };
+  while (slots > 1 && gcd(slots, shards) != 1) --slots;
+  return slots;
+}
+
 template <int kKind, int kBN, int kEpi>
 int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   using S = GemmSmem<kBN>;
@@ -237,10 +246,10 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   // bound by its integer arithmetic: per-thread stores are faster there unless tile stores are forced (2)
   p.tma_store = (vec && (ctx->tma_store == 2 || (ctx->tma_store == 1 && kEpi != EPI_I8_SRS))) ? 1 : 0;
   CUtensorMap mc = ma;  // unused unless tma_store
-  if (c.c_shard_maps) {
-    p.vec_ok = 1; p.tma_store = 1;  // the shards were checked when their maps were made
-    p.c_shard_maps = c.c_shard_maps; p.rows_per_shard = c.rows_per_shard; p.num_shards = c.num_shards;
-    set_shard_rotation(p, c, kPairM);
+  if (c.num_shards > 0) {
+    p.vec_ok = 1; p.tma_store = 1;  // the whole warp takes part in every chunk (the shards were checked by the caller)
+    for (int g = 0; g < c.num_shards; ++g) p.shard[g] = c.shards[g];
+    p.rows_per_shard = c.rows_per_shard; p.num_shards = c.num_shards;
     set_shard_rotation(p, c, kBlockM);
   } else if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
   p.status = ctx->d_status;
@@ -254,7 +263,8 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
     ks.smem_attr = S::kTotal;
   }
   const int tiles = p.num_m_blocks * p.num_n_blocks;
-  const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  if (p.rot_shards > 0) grid = coprime_slots(grid, p.rot_shards);
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -306,9 +316,11 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0)) ? 1 : 0;
   p.tma_store = (p.vec_ok && (ctx->tma_store == 2 || (ctx->tma_store == 1 && kEpi != EPI_I8_SRS))) ? 1 : 0;
   CUtensorMap mc = ma;  // unused unless tma_store
-  if (c.c_shard_maps) {
-    p.vec_ok = 1; p.tma_store = 1;  // the shards were checked when their maps were made
-    p.c_shard_maps = c.c_shard_maps; p.rows_per_shard = c.rows_per_shard; p.num_shards = c.num_shards;
+  if (c.num_shards > 0) {
+    p.vec_ok = 1; p.tma_store = 1;  // the whole warp takes part in every chunk (the shards were checked by the caller)
+    for (int g = 0; g < c.num_shards; ++g) p.shard[g] = c.shards[g];
+    p.rows_per_shard = c.rows_per_shard; p.num_shards = c.num_shards;
+    set_shard_rotation(p, c, kPairM);
   } else if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
   p.status = ctx->d_status;
   p.debug = ctx->debug_mode;
@@ -354,7 +366,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   // Tail balancing (int32 accumulation only: sums of partial sums are exact; fp32 would change rounding)
   p.sk_first_tile = tiles;
   p.sk_parts = 1;
-  if (kKind == KIND_I8 && !c.c_shard_maps) {  // the K ranges store per thread: not into a sharded output
+  if (kKind == KIND_I8 && c.num_shards == 0) {  // the K ranges store per thread: not into a sharded output
     split_tail(tiles, tiles < max_pairs ? max_pairs : pairs, p.num_k_blocks, ctx->split_tail, &p.sk_first_tile, &p.sk_parts);
     if (p.sk_parts > 1) {
       const int tail = tiles - p.sk_first_tile;
@@ -384,6 +396,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
       pairs = units < max_pairs ? units : max_pairs;
     }
   }
+  if (p.rot_shards > 0) pairs = coprime_slots(pairs, p.rot_shards);
   cfg.gridDim = dim3(2 * pairs);
   AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mb_narrow, mc, p));
   ctx->launches++;

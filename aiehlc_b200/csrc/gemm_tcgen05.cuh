@@ -41,6 +41,8 @@ constexpr int kGemmThreads = 192;
 constexpr int kStoreBufBytes = 4096;
 constexpr int kStoreStagingBytes = 4 * 2 * kStoreBufBytes;
 
+constexpr int kMaxShards = 16;
+
 struct GemmParams {
   int M, N, K;
   void* C;                 // int32 / int8 / bf16, row-major, leading dimension ldc (elements)
@@ -62,15 +64,18 @@ struct GemmParams {
   int sk_first_tile, sk_parts;
   int32_t* sk_scratch;     // [tail tile][depositing range][CTA rank][32-column chunk] partial sums
   int* sk_flags;           // [tail tile][CTA rank][owning range (4 slots)] deposits so far; zero between launches
-  // Row-sharded output (EPI_I32_ACC through tile stores only): rows [g * rows_per_shard, (g + 1) *
-  // rows_per_shard) of C are the tensor c_shard_maps[g] (device array), which may lie in the memory of
-  // another GPU; results are ADDED there.  rows_per_shard is a multiple of 128, so the 128 rows of a
-  // CTA never straddle two shards.  Null: C is the one tensor of the kernel's tensor-map argument.
-  const CUtensorMap* c_shard_maps;
+  // Row-sharded output (EPI_I32_ACC only): rows [g * rows_per_shard, (g + 1) * rows_per_shard) of C are
+  // the dense int32 matrix shard[g] (pitch N), which may lie in the memory of another GPU; results are
+  // ADDED there with system-scope reductions, one 128-byte row segment per warp instruction (measured
+  // between two B200: 697 GB/s from 18 SMs on, where add-reducing tile stores of 128-byte rows need 74
+  // SMs pushing at once and held the tile loads of the main loop back).  rows_per_shard is a multiple
+  // of 128, so the 128 rows of a CTA never straddle two shards.  num_shards == 0: C is one matrix.
+  int32_t* shard[kMaxShards];
   int rows_per_shard, num_shards;
-  // Visiting order for a sharded output: consecutive groups of row-blocks belong to consecutive shards,
-  // starting with shard rot_first, so that GPUs that run the same product with different rot_first send
-  // to different owners at any moment and every link is busy throughout.  rot_shards == 0: rows in order.
+  // Visiting order for a sharded output: consecutive tiles belong to consecutive shards, starting with
+  // shard rot_first, so that the tiles in flight at any moment spread over all owners (every link busy
+  // throughout, local and remote adds mixed) and GPUs that run the same product with different
+  // rot_first lean on different owners.  rot_shards == 0: rows in order.
   int rot_shards, rot_first, rot_blocks_per_shard;
   // The other form of tail balancing: tiles >= nt_first_tile are cut into nt_parts column ranges
   // (narrower MMAs, no exchange between the ranges).  nt_parts == 1: off.  Never together with sk_parts > 1.
@@ -128,6 +133,18 @@ struct GemmSmem {
 };
 
 __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb, int& nb) {
+  if (p.rot_shards > 0) {
+    // consecutive tiles (the ones in flight together) belong to consecutive shards; inside a shard the
+    // usual walk over groups of group_m row-blocks
+    const int shard = (t + p.rot_first) % p.rot_shards;
+    const int j = t / p.rot_shards;
+    const int per_group = p.group_m * p.num_n_blocks;
+    const int g = j / per_group;
+    const int r = j - g * per_group;
+    mb = shard * p.rot_blocks_per_shard + g * p.group_m + r % p.group_m;
+    nb = r / p.group_m;
+    return;
+  }
   const int per_group = p.group_m * p.num_n_blocks;
   const int g = t / per_group;
   const int first_m = g * p.group_m;
@@ -135,11 +152,6 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb,
   const int r = t - g * per_group;
   mb = first_m + r % rows;
   nb = r / rows;
-  if (p.rot_shards > 0) {
-    // virtual group g (of group_m row-blocks) -> shard (g + rot_first) mod shards, group g / shards inside it
-    const int shard = (g + p.rot_first) % p.rot_shards;
-    mb = shard * p.rot_blocks_per_shard + (g / p.rot_shards) * p.group_m + (mb - first_m);
-  }
 }
 
 // Where an epilogue warp puts its results when they leave through TMA tile stores.
@@ -150,15 +162,39 @@ struct StoreCtx {
   int chunk_in_group;   // 32-column chunks already staged in that buffer
   int lane;
   int warp_row0;        // first row of C this warp's 32 TMEM lanes map to
+  int32_t* shard_row0;  // sharded output: where that row starts in the owning shard
+  int rows_left;        // sharded output: M - warp_row0
 };
 
-// Row-sharded output: points the warp's stores at the shard that owns the CTA's 128 rows.
+// Row-sharded output: points the warp's reductions at the shard that owns the CTA's 128 rows.
 __device__ __forceinline__ void select_shard(const GemmParams& p, int cta_row0, StoreCtx& sc) {
-  if (p.c_shard_maps == nullptr) return;
+  if (p.num_shards == 0) return;
   int owner = cta_row0 / p.rows_per_shard;
-  if (owner >= p.num_shards) owner = p.num_shards - 1;  // rows past M: clipped by the shard's own extent
-  sc.tmap = p.c_shard_maps + owner;
-  sc.warp_row0 -= owner * p.rows_per_shard;
+  if (owner >= p.num_shards) owner = p.num_shards - 1;  // rows past M: masked by rows_left
+  sc.rows_left = p.M - sc.warp_row0;                    // rows of this warp's 32 that exist
+  sc.shard_row0 = p.shard[owner] + static_cast<long long>(sc.warp_row0 - owner * p.rows_per_shard) * p.N;
+}
+
+// Adds one 32-column chunk of this warp's 32 rows into the shard.  Every thread holds one row; the
+// chunk is turned through the warp's staging buffer so that each reduction instruction covers the 32
+// consecutive words of ONE row (a single 128-byte request on the way to the owner).
+__device__ __forceinline__ void shard_add_chunk(const GemmParams& p, StoreCtx& sc, const uint32_t* words, int col0) {
+  uint8_t* buf = sc.buf[0];
+  const int swz = sc.lane & 7;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<uint4*>(buf + sc.lane * 128 + ((j ^ swz) << 4)) =
+        make_uint4(words[4 * j], words[4 * j + 1], words[4 * j + 2], words[4 * j + 3]);
+  __syncwarp();
+  const bool col_ok = col0 + sc.lane < p.N;
+  int32_t* dst = sc.shard_row0 + col0 + sc.lane;
+  const int rows = sc.rows_left < 32 ? sc.rows_left : 32;
+#pragma unroll 4
+  for (int r = 0; r < rows; ++r) {
+    const int v = *reinterpret_cast<const int*>(buf + r * 128 + ((((sc.lane >> 2) ^ (r & 7)) << 4) | ((sc.lane & 3) << 2)));
+    if (col_ok) asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(dst + static_cast<long long>(r) * p.N), "r"(v) : "memory");
+  }
+  __syncwarp();  // the buffer is rewritten by the next chunk
 }
 
 // Stages one 32-column chunk of this warp's 32 rows; once a group of chunks fills a row of
@@ -214,6 +250,10 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
                                             StoreCtx& sc) {
   const int ncols = min(32, p.N - col0);
   if constexpr (kEpi == EPI_I32 || kEpi == EPI_I32_ACC) {
+    if (kEpi == EPI_I32_ACC && p.num_shards > 0) {
+      shard_add_chunk(p, sc, r, col0);
+      return;
+    }
     if (!kForceDirect && p.tma_store) {
       tma_emit<128, 128, kEpi == EPI_I32_ACC>(sc, r, col0);
       return;
@@ -474,7 +514,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     StoreCtx sc{&tmap_c, {store_staging + (quad * 2) * kStoreBufBytes, store_staging + (quad * 2 + 1) * kStoreBufBytes},
-                0, 0, lane, 0};
+                0, 0, lane, 0, nullptr, 0};
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {

@@ -270,7 +270,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ---------------------------------------------------------------- epilogue (both CTAs)
     const int quad = warp & 3;
     StoreCtx sc{&tmap_c, {store_staging + (quad * 2) * kStoreBufBytes, store_staging + (quad * 2 + 1) * kStoreBufBytes},
-                0, 0, lane, 0};
+                0, 0, lane, 0, nullptr, 0};
     int it = 0;
     bool ok = true;
     WorkUnit w;

@@ -71,18 +71,18 @@ int aiehlc_mm_i32_host(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, 
 int aiehlc_gemm_i8_i32_dev(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int32_t* C, int M,
                            int N, int K, int accumulate, void* stream);
 /* The same product ADDED into a row-sharded C: rows [g * rows_per_shard, (g + 1) * rows_per_shard) of
- * C are the dense int32 matrix shards[g] ([rows][N], 16-byte aligned; the last used shard holds
+ * C are the dense int32 matrix shards[g] ([rows][N]; the last used shard holds
  * M - g * rows_per_shard rows).  A shard may be memory of ANOTHER GPU that this device can address
- * (peer access enabled, or a mapping of the owner's allocation): the epilogue's tile stores are
- * add-reductions, so every GPU of a split-K group can run this call on its K slice at the same time
+ * (peer access enabled, or a mapping of the owner's allocation): the epilogue adds its results with
+ * system-scope reductions, so every GPU of a split-K group can run this call on its K slice at the same time
  * and the owner of a shard ends with the sum -- the GEMM and the reduce-scatter of the cascade
  * (the K-slice stages of example/multi/multi_tile.cpp:105-145 spread over GPUs) in one kernel, with
  * no partial-sum matrix.  The caller zeroes the shards before the first contribution and orders
  * "all zeroed" -> calls -> "all done" -> reads across the GPUs (e.g. with two barriers).
- * rows_per_shard must be a multiple of 128, N a multiple of 4, num_shards <= AIEHLC_MAX_SHARDS.
- * first_shard: when M fills every shard, the tiles are visited shard by shard in turn (a group of
- * row-blocks of shard first_shard, then of first_shard + 1, ...), so GPUs that pass different values
- * (own rank + 1) send to different owners at any moment; it never changes the result. */
+ * rows_per_shard must be a multiple of 128, num_shards <= AIEHLC_MAX_SHARDS.
+ * first_shard: when M fills every shard, consecutive tiles belong to consecutive shards (first_shard,
+ * first_shard + 1, ...), so the tiles in flight at any moment spread over all owners and GPUs that
+ * pass different values (own rank + 1) lean on different owners; it never changes the result. */
 #define AIEHLC_MAX_SHARDS 16
 int aiehlc_gemm_i8_i32_scatter_dev(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, int32_t* const* shards,
                                    int num_shards, int rows_per_shard, int first_shard, int M, int N, int K,
