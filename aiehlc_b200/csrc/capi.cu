@@ -120,7 +120,7 @@ int aiehlc_destroy(aiehlc_ctx* ctx) {
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   ctx->buf_a.release(); ctx->buf_b.release(); ctx->buf_c.release(); ctx->buf_aux.release();
   ctx->pack_a.release(); ctx->pack_b.release();
-  ctx->sk_scratch.release(); ctx->sk_flags.release();
+  ctx->sk_scratch.release(); ctx->sk_flags.release(); ctx->shard_maps.release();
   delete ctx;
   return AIEHLC_OK;
 }
@@ -174,6 +174,12 @@ int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   if (on < 0 || on > 2) return fail(AIEHLC_ERR_INVALID, "split_tail: 0 (off), 1 (K ranges) or 2 (column ranges)");
   ctx->split_tail = on;
+  return AIEHLC_OK;
+}
+
+int aiehlc_set_shard_tile_stores(aiehlc_ctx* ctx, int on) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->shard_tile_stores = on ? 1 : 0;
   return AIEHLC_OK;
 }
 
@@ -274,9 +280,38 @@ int aiehlc_gemm_i8_i32_scatter_dev(aiehlc_ctx* ctx, const int8_t* A, const int8_
   GemmCall c{};
   c.kind = KIND_I8; c.epi = EPI_I32_ACC;
   c.A = A; c.B = B; c.C = nullptr; c.M = M; c.N = N; c.K = K; c.lda = K; c.ldb = K; c.ldc = N;
+  if (ctx->shard_tile_stores && N % 4 == 0) {
+    bool aligned = true;
+    for (int g = 0; g < used; ++g) aligned = aligned && reinterpret_cast<uintptr_t>(shards[g]) % 16 == 0;
+    if (aligned) {
+      // the shards' tensor maps live in a context buffer; they are rebuilt only when the call differs
+      std::vector<unsigned long long> key = {static_cast<unsigned long long>(M), static_cast<unsigned long long>(N),
+                                             static_cast<unsigned long long>(rows_per_shard),
+                                             static_cast<unsigned long long>(num_shards)};
+      for (int g = 0; g < used; ++g) key.push_back(reinterpret_cast<unsigned long long>(shards[g]));
+      if (key != ctx->shard_key) {
+        CUtensorMap maps[AIEHLC_MAX_SHARDS];
+        for (int g = 0; g < num_shards; ++g) {
+          const int src = g < used ? g : 0;  // shards past M are never addressed
+          const long long rows = src == used - 1 ? M - static_cast<long long>(src) * rows_per_shard : rows_per_shard;
+          if ((rc = encode_c_map(ctx, &maps[g], EPI_I32_ACC, 256, shards[src], rows, N, N))) return rc;
+        }
+        if (ctx->shard_maps.reserve(sizeof maps)) return AIEHLC_ERR_NOMEM;
+        // pageable source: the copy has left `maps` when the call returns, and it is ordered on `st`
+        // before the kernel that reads it
+        AIEHLC_CUDA(cudaMemcpyAsync(ctx->shard_maps.ptr, maps, sizeof(CUtensorMap) * num_shards, cudaMemcpyHostToDevice, st));
+        ctx->shard_key = key;
+      }
+    }
+  }
   int32_t* ptrs[AIEHLC_MAX_SHARDS];
   for (int g = 0; g < num_shards; ++g) ptrs[g] = shards[g < used ? g : 0];  // shards past M are never addressed
   c.shards = ptrs;
+  if (ctx->shard_tile_stores && N % 4 == 0 && !ctx->shard_key.empty()) {
+    bool aligned = true;
+    for (int g = 0; g < used; ++g) aligned = aligned && reinterpret_cast<uintptr_t>(shards[g]) % 16 == 0;
+    if (aligned) c.shard_maps = static_cast<const CUtensorMap*>(ctx->shard_maps.ptr);
+  }
   c.rows_per_shard = rows_per_shard; c.num_shards = num_shards; c.first_shard = first_shard;
   return launch_gemm(ctx, c, st);
 }

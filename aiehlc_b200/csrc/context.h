@@ -7,6 +7,7 @@
 #include <cstdint>
 #include <string>
 #include <unordered_map>
+#include <vector>
 
 #include "../../include/aiehlc_b200.h"
 
@@ -68,6 +69,9 @@ struct aiehlc_ctx {
   // staging for *_host entry points and for operands that TMA cannot address directly
   aiehlc::DevBuf buf_a, buf_b, buf_c, buf_aux, pack_a, pack_b;
   aiehlc::DevBuf sk_scratch, sk_flags;  // partial sums and deposit counters of split tail tiles
+  int shard_tile_stores = 1;            // sharded output leaves as add-reducing TMA tile stores (else row reductions)
+  aiehlc::DevBuf shard_maps;            // tensor maps of a row-sharded output, as the kernels read them
+  std::vector<unsigned long long> shard_key;  // what those maps were made from
 };
 
 namespace aiehlc {
@@ -88,9 +92,12 @@ struct GemmCall {
   int group_m;                  // filled in from the plan
   // row-sharded add-reduction output (see GemmParams::shard); C is unused when num_shards > 0
   int32_t* const* shards = nullptr;
+  const CUtensorMap* shard_maps = nullptr;   // optional: the shards as tensors for add-reducing tile stores
   int rows_per_shard = 0, num_shards = 0, first_shard = 0;
 };
 int launch_gemm(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st);
+int encode_c_map(aiehlc_ctx* ctx, CUtensorMap* map, int epi, int bn, void* base, long long rows, long long cols,
+                 long long ld);
 int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* out);
 // Tail balancing: tiles [first, tiles) are cut into `parts` K ranges (parts == 1: no cut).
 void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int* parts);

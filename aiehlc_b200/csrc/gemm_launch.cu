@@ -250,6 +250,7 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
     p.vec_ok = 1; p.tma_store = 1;  // the whole warp takes part in every chunk (the shards were checked by the caller)
     for (int g = 0; g < c.num_shards; ++g) p.shard[g] = c.shards[g];
     p.rows_per_shard = c.rows_per_shard; p.num_shards = c.num_shards;
+    p.shard_maps = c.shard_maps;
     set_shard_rotation(p, c, kBlockM);
   } else if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
   p.status = ctx->d_status;
@@ -320,6 +321,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
     p.vec_ok = 1; p.tma_store = 1;  // the whole warp takes part in every chunk (the shards were checked by the caller)
     for (int g = 0; g < c.num_shards; ++g) p.shard[g] = c.shards[g];
     p.rows_per_shard = c.rows_per_shard; p.num_shards = c.num_shards;
+    p.shard_maps = c.shard_maps;
     set_shard_rotation(p, c, kPairM);
   } else if (p.tma_store && (rc = encode_c_map(ctx, &mc, kEpi, kBN, c.C, c.M, c.N, c.ldc))) return rc;
   p.status = ctx->d_status;

@@ -72,6 +72,9 @@ struct GemmParams {
   // of 128, so the 128 rows of a CTA never straddle two shards.  num_shards == 0: C is one matrix.
   int32_t* shard[kMaxShards];
   int rows_per_shard, num_shards;
+  // The same shards as tensors (device array of num_shards maps, box 32 x 32 words), or null.  When
+  // given, results leave as add-reducing TMA tile stores instead of per-row reduction instructions.
+  const CUtensorMap* shard_maps;
   // Visiting order for a sharded output: consecutive tiles belong to consecutive shards, starting with
   // shard rot_first, so that the tiles in flight at any moment spread over all owners (every link busy
   // throughout, local and remote adds mixed) and GPUs that run the same product with different
@@ -173,6 +176,10 @@ __device__ __forceinline__ void select_shard(const GemmParams& p, int cta_row0, 
   if (owner >= p.num_shards) owner = p.num_shards - 1;  // rows past M: masked by rows_left
   sc.rows_left = p.M - sc.warp_row0;                    // rows of this warp's 32 that exist
   sc.shard_row0 = p.shard[owner] + static_cast<long long>(sc.warp_row0 - owner * p.rows_per_shard) * p.N;
+  if (p.shard_maps != nullptr) {
+    sc.tmap = p.shard_maps + owner;                     // rows past the shard's extent are clipped by the hardware
+    sc.warp_row0 -= owner * p.rows_per_shard;
+  }
 }
 
 // Adds one 32-column chunk of this warp's 32 rows into the shard.  Every thread holds one row; the
@@ -250,7 +257,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
                                             StoreCtx& sc) {
   const int ncols = min(32, p.N - col0);
   if constexpr (kEpi == EPI_I32 || kEpi == EPI_I32_ACC) {
-    if (kEpi == EPI_I32_ACC && p.num_shards > 0) {
+    if (kEpi == EPI_I32_ACC && p.num_shards > 0 && p.shard_maps == nullptr) {
       shard_add_chunk(p, sc, r, col0);
       return;
     }

@@ -67,6 +67,9 @@ class Context:
     def set_cta_pair(self, mode: int) -> None:
         _capi.check(self._lib.aiehlc_set_cta_pair(self._h, int(mode)))
 
+    def set_shard_tile_stores(self, on: bool) -> None:
+        _capi.check(self._lib.aiehlc_set_shard_tile_stores(self._h, 1 if on else 0))
+
     def set_k_per_load(self, k_blocks: int) -> None:
         _capi.check(self._lib.aiehlc_set_k_per_load(self._h, int(k_blocks)))
 

@@ -214,6 +214,12 @@ int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on);
  *       order); measured 48.3 us against 49.7 us on the 4096^3 benchmark;
  *   0 = every tile computed whole. */
 int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on);
+/* Tuning knob for aiehlc_gemm_i8_i32_scatter_dev: 1 (default) = results leave as add-reducing TMA tile
+ * stores (32 rows x 128 bytes per store; needs N a multiple of 4 and 16-byte aligned shards, else the
+ * other form is used), 0 = as per-row reduction instructions issued by the epilogue warps.  Measured
+ * between two B200 (65536 x 8192 x 4096 per GPU, half of the tiles remote): 2.04 ms against 2.10 ms,
+ * all shards local 1.63 ms against 2.08 ms. */
+int aiehlc_set_shard_tile_stores(aiehlc_ctx* ctx, int on);
 /* Tuning knob: number of tile row-blocks the persistent scheduler walks before it moves to the next
  * tile column (the L2 footprint of one wave is group_m row-blocks of A plus slots/group_m column-blocks
  * of B).  0 = default: 8 for CTA-pair tiles, 16 for single-CTA tiles (about square wave footprints). */

@@ -249,12 +249,13 @@ def test_k_blocks_per_tile_load(ctx, shape, k_per_load):
         ctx.set_cta_pair(-1)
 
 
+@pytest.mark.parametrize("tile_stores", [0, 1])
 @pytest.mark.parametrize("pair", [0, 1])
 @pytest.mark.parametrize("M,N,K,rows_per_shard,group_m,first_shard",
                          [(1000, 520, 272, 256, 0, 0), (2304, 2304, 512, 1152, 0, 1), (640, 256, 1024, 128, 0, 3),
                           (300, 64, 96, 384, 0, 0),
                           (2048, 512, 256, 512, 2, 1), (4096, 256, 128, 512, 1, 5)])   # shard-interleaved tile order
-def test_row_sharded_add_reduction_output(ctx, M, N, K, rows_per_shard, group_m, first_shard, pair):
+def test_row_sharded_add_reduction_output(ctx, M, N, K, rows_per_shard, group_m, first_shard, pair, tile_stores):
     """GEMM whose epilogue adds into a row-sharded C (the fused split-K exchange; here every shard is
     local): zeroed shards receive the product, a second K slice adds to it, rows past M stay untouched;
     the visiting order (first_shard) never changes the result."""
@@ -265,6 +266,7 @@ def test_row_sharded_add_reduction_output(ctx, M, N, K, rows_per_shard, group_m,
     shards[-1] += 77                                                   # rows past M must keep this
     ctx.set_cta_pair(pair)
     ctx.set_group_m(group_m)
+    ctx.set_shard_tile_stores(bool(tile_stores))
     try:
         half = K // 2 // 16 * 16
         dA, dB = _dev(A), _dev(B)
@@ -279,6 +281,7 @@ def test_row_sharded_add_reduction_output(ctx, M, N, K, rows_per_shard, group_m,
     finally:
         ctx.set_cta_pair(-1)
         ctx.set_group_m(0)
+        ctx.set_shard_tile_stores(True)
     with pytest.raises(_capi.AiehlcError):
         ctx.gemm_i8_i32_scatter(dA, dB, shards, 100)                   # not a multiple of 128
     with pytest.raises(_capi.AiehlcError):
