@@ -105,6 +105,14 @@ def build_examples() -> list[Path]:
         if res.returncode != 0:
             raise RuntimeError(f"example {src.name} failed to build:\n{res.stderr}")
         outs.append(out)
+    for src in sorted(EXAMPLES_DIR.glob("*.cu")):     # stand-alone CUDA measurement programs
+        out = EXAMPLES_BIN / src.stem
+        if not (out.exists() and out.stat().st_mtime > src.stat().st_mtime):
+            cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", str(src), "-o", str(out)]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"example {src.name} failed to build:\n{res.stderr}")
+        outs.append(out)
     return outs
 
 
