@@ -90,6 +90,7 @@ int aiehlc_create(int device, aiehlc_ctx** out) {
   ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
   e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream2, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream_up, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->block_done, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaMalloc(&ctx->d_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
@@ -115,7 +116,12 @@ int aiehlc_destroy(aiehlc_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream2);
     cudaStreamDestroy(ctx->stream2);
   }
+  if (ctx->stream_up) {
+    cudaStreamSynchronize(ctx->stream_up);
+    cudaStreamDestroy(ctx->stream_up);
+  }
   if (ctx->block_done) cudaEventDestroy(ctx->block_done);
+  for (cudaEvent_t ev : ctx->block_ev) cudaEventDestroy(ev);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   ctx->buf_a.release(); ctx->buf_b.release(); ctx->buf_c.release(); ctx->buf_aux.release();
@@ -174,6 +180,13 @@ int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   if (on < 0 || on > 2) return fail(AIEHLC_ERR_INVALID, "split_tail: 0 (off), 1 (K ranges) or 2 (column ranges)");
   ctx->split_tail = on;
+  return AIEHLC_OK;
+}
+
+int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (blocks < 0 || blocks > 64) return fail(AIEHLC_ERR_INVALID, "host_blocks: 0 (default) .. 64");
+  ctx->host_blocks = blocks;
   return AIEHLC_OK;
 }
 
@@ -450,12 +463,16 @@ static int stage_ab(aiehlc_ctx* ctx, const void* A, const void* B, size_t a_byte
 
 }  // extern "C"
 
-// Host-buffer GEMM as a pipeline over row blocks of A and C:
-//   stream  : B -> device, then per block: A rows -> device, kernel
-//   stream2 : per block, once its kernel is done: C rows -> host
-// so the upload of block i+1 and the download of block i run while block i+1 computes (PCIe is
-// full duplex).  With pinned host buffers the copies are truly asynchronous; with pageable ones the
-// runtime stages them and the result is the same, only slower.
+// Host-buffer GEMM as a pipeline over row blocks of A and C on three streams:
+//   stream_up : B -> device, then the row blocks of A -> device, back to back
+//   stream    : per block, once its rows have arrived: the kernel
+//   stream2   : per block, once its kernel is done: C rows -> host
+// so the PCIe link never waits for a kernel in either direction, and what is left after the last
+// upload is one block's kernel and download.  Measured on the 4096^3 int8 case (50 MB per call): the
+// link carries 53 GB/s one way but only about 35 + 35 GB/s when both directions are busy, and every
+// extra block costs about 20 us, so four blocks are the best split (0.87 ms per call; 1.00 ms unsplit).  With pinned host buffers the
+// copies are truly asynchronous; with pageable ones the runtime stages them and the result is the
+// same, only slower.
 template <typename LaunchRows>
 static int host_gemm_pipelined(aiehlc_ctx* ctx, const void* A, const void* B, void* C, int M, int N, int K, int in_esize,
                                int out_esize, LaunchRows launch_rows) {
@@ -464,21 +481,30 @@ static int host_gemm_pipelined(aiehlc_ctx* ctx, const void* A, const void* B, vo
   if (ctx->buf_a.reserve(a_bytes ? a_bytes : 16) || ctx->buf_b.reserve(b_bytes ? b_bytes : 16) ||
       ctx->buf_c.reserve(c_bytes ? c_bytes : 16))
     return AIEHLC_ERR_NOMEM;
-  if (b_bytes) AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_b.ptr, B, b_bytes, cudaMemcpyHostToDevice, ctx->stream));
-  // four blocks of whole 256-row tiles; small problems go in one piece
-  int rows_per_block = ((M + 3) / 4 + 255) / 256 * 256;
+  // whatever the caller queued on the context's stream before (shift bytes, ...) precedes the uploads
+  AIEHLC_CUDA(cudaEventRecord(ctx->block_done, ctx->stream));
+  AIEHLC_CUDA(cudaStreamWaitEvent(ctx->stream_up, ctx->block_done, 0));
+  if (b_bytes) AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_b.ptr, B, b_bytes, cudaMemcpyHostToDevice, ctx->stream_up));
+  // blocks of whole 256-row tiles; small problems go in one piece
+  const int blocks = ctx->host_blocks > 0 ? ctx->host_blocks : 4;
+  int rows_per_block = ((M + blocks - 1) / blocks + 255) / 256 * 256;
   if (static_cast<size_t>(rows_per_block) * K * in_esize < (1u << 20)) rows_per_block = M;
-  for (int r0 = 0; r0 < M; r0 += rows_per_block) {
+  int b = 0;
+  for (int r0 = 0; r0 < M; r0 += rows_per_block, ++b) {
     const int rows = M - r0 < rows_per_block ? M - r0 : rows_per_block;
     uint8_t* da = static_cast<uint8_t*>(ctx->buf_a.ptr) + static_cast<size_t>(r0) * K * in_esize;
     uint8_t* dc = static_cast<uint8_t*>(ctx->buf_c.ptr) + static_cast<size_t>(r0) * N * out_esize;
+    cudaEvent_t up = nullptr, done = nullptr;
+    if (int rc = ctx->block_events(b, &up, &done)) return rc;
     if (K > 0)
       AIEHLC_CUDA(cudaMemcpyAsync(da, static_cast<const uint8_t*>(A) + static_cast<size_t>(r0) * K * in_esize,
-                                  static_cast<size_t>(rows) * K * in_esize, cudaMemcpyHostToDevice, ctx->stream));
+                                  static_cast<size_t>(rows) * K * in_esize, cudaMemcpyHostToDevice, ctx->stream_up));
+    AIEHLC_CUDA(cudaEventRecord(up, ctx->stream_up));
+    AIEHLC_CUDA(cudaStreamWaitEvent(ctx->stream, up, 0));
     const int rc = launch_rows(da, dc, rows);
     if (rc) return rc;
-    AIEHLC_CUDA(cudaEventRecord(ctx->block_done, ctx->stream));
-    AIEHLC_CUDA(cudaStreamWaitEvent(ctx->stream2, ctx->block_done, 0));
+    AIEHLC_CUDA(cudaEventRecord(done, ctx->stream));
+    AIEHLC_CUDA(cudaStreamWaitEvent(ctx->stream2, done, 0));
     AIEHLC_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(C) + static_cast<size_t>(r0) * N * out_esize, dc,
                                 static_cast<size_t>(rows) * N * out_esize, cudaMemcpyDeviceToHost, ctx->stream2));
   }

@@ -51,6 +51,18 @@ struct aiehlc_ctx {
   int sm_count = 0;
   cudaStream_t stream = nullptr;   // uploads and kernels of the *_host entry points
   cudaStream_t stream2 = nullptr;  // their downloads, overlapped with the next block's upload
+  cudaStream_t stream_up = nullptr;  // their uploads, back to back whatever the kernels do
+  std::vector<cudaEvent_t> block_ev;  // per row block of a host GEMM: "rows uploaded", "kernel done"
+  int block_events(int block, cudaEvent_t* up, cudaEvent_t* done) {
+    while (block_ev.size() < 2 * static_cast<size_t>(block + 1)) {
+      cudaEvent_t ev = nullptr;
+      if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return AIEHLC_ERR_CUDA;
+      block_ev.push_back(ev);
+    }
+    *up = block_ev[2 * block];
+    *done = block_ev[2 * block + 1];
+    return AIEHLC_OK;
+  }
   cudaEvent_t block_done = nullptr;
   int* d_status = nullptr;      // device status word
   int* h_status = nullptr;      // pinned mirror
@@ -61,6 +73,7 @@ struct aiehlc_ctx {
   int tma_store = 1;            // epilogue results leave through shared memory + TMA tile stores when C allows
   int split_tail = 2;           // thin last wave: 1 = cut its tiles along K across idle CTA pairs, 2 = into two column ranges
   int group_m = 0;              // row-blocks per rasterisation group (0 = default for the kernel family)
+  int host_blocks = 0;           // row blocks the *_host GEMM entry points pipeline over (0 = default)
   int pdl = 1;                  // launch the tensor-core kernels with programmatic stream serialization
   int debug_mode = 0;           // see GemmParams::debug
   long long* trace = nullptr;   // see GemmParams::trace (device pointer owned by the caller)

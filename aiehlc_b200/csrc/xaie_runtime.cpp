@@ -21,6 +21,7 @@
 
 #include "../../include/aiehlc_b200.h"
 #include "../../include/aiehlc_kernels.h"
+#include "../../include/xaie_placeholder.h"
 #include "../../include/xaiengine.h"
 
 namespace {
@@ -880,6 +881,123 @@ AieRC XAie_KernelCall(const void* kernel_key, const void* args, u32 args_bytes, 
   int status = 0;
   if (aiehlc_sync(rt->ctx, rt->stream, &status) != AIEHLC_OK) return fail(XAIE_ERR_DEVICE, aiehlc_last_error());
   return XAIE_OK;
+}
+
+// ---------------------------------------------------------------- the short host API (xaie_placeholder.h)
+}  // extern "C"
+
+struct XAie_Kernel_Inst {
+  Runtime* rt = nullptr;
+  XAie_LocType loc{};
+  XAie_RoutingInstance* ri = nullptr;
+  XAie_LocType shim_in{}, shim_out{};
+  bool has_in = false, has_out = false;
+};
+
+namespace {
+// The device instance behind XAie_LoadKernel when the program has not initialised one itself:
+// the array of example/other/aieoob.c:8-19.
+XAie_DevInst g_implicit_dev;
+bool lookup_kernel_by_name(const char* name, const void** key) {
+  seed_library_kernels();
+  Registry& r = registry();
+  std::lock_guard<std::mutex> lk(r.mu);
+  for (auto& kv : r.map)
+    if (kv.second.name == name) {
+      *key = kv.first;
+      return true;
+    }
+  return false;
+}
+}  // namespace
+
+extern "C" {
+
+XAie_Kernel_Inst* XAie_LoadKernel(const char* name, int col, int row) {
+  if (!name) {
+    fail(XAIE_INVALID_ARGS, "XAie_LoadKernel: null kernel name");
+    return nullptr;
+  }
+  const void* key = nullptr;
+  if (!lookup_kernel_by_name(name, &key)) {
+    fail(XAIE_INVALID_ELF, std::string("XAie_LoadKernel: no kernel registered under the name '") + name + "'");
+    return nullptr;
+  }
+  if (!g_current_rt) {
+    XAie_Config cfg = {2, 0x20000000000ull, 25, 20, 11, 38, 0, 1, 2, 3, 8};
+    if (XAie_CfgInitialize(&g_implicit_dev, &cfg) != XAIE_OK) return nullptr;
+  }
+  Runtime* rt = g_current_rt;
+  if (col < 0 || row < 0 || col > 255 || row > 255) {
+    fail(XAIE_INVALID_TILE, "XAie_LoadKernel: tile outside the array");
+    return nullptr;
+  }
+  const XAie_LocType loc = XAie_TileLoc(static_cast<u8>(col), static_cast<u8>(row));
+  if (XAie_LoadElfMem(rt->dev, loc, static_cast<const unsigned char*>(key)) != XAIE_OK) return nullptr;
+  XAie_Kernel_Inst* k = new XAie_Kernel_Inst();
+  k->rt = rt;
+  k->loc = loc;
+  k->ri = XAie_InitRoutingHandler(rt->dev);
+  if (!k->ri) {
+    delete k;
+    return nullptr;
+  }
+  return k;
+}
+
+AieRC XAie_RoutingHostToAie(XAie_Kernel_Inst* k, XAie_LocType shim) {
+  if (!k) return fail(XAIE_INVALID_ARGS, "null kernel instance");
+  if (!k->rt->valid_loc(shim) || !k->rt->is_shim(shim)) return fail(XAIE_INVALID_TILE, "host data enters through a shim tile");
+  const AieRC rc = XAie_Route(k->ri, nullptr, shim, k->loc);
+  if (rc == XAIE_OK) { k->shim_in = shim; k->has_in = true; }
+  return rc;
+}
+
+AieRC XAie_RoutingAieToHost(XAie_Kernel_Inst* k, XAie_LocType shim) {
+  if (!k) return fail(XAIE_INVALID_ARGS, "null kernel instance");
+  if (!k->rt->valid_loc(shim) || !k->rt->is_shim(shim)) return fail(XAIE_INVALID_TILE, "results leave through a shim tile");
+  const AieRC rc = XAie_Route(k->ri, nullptr, k->loc, shim);
+  if (rc == XAIE_OK) { k->shim_out = shim; k->has_out = true; }
+  return rc;
+}
+
+AieRC XAie_MoveDataToAie(XAie_Kernel_Inst* k, int port, const void* src, size_t bytes) {
+  if (!k || (!src && bytes)) return fail(XAIE_INVALID_ARGS, "XAie_MoveDataToAie: null argument");
+  if (port != 1) return fail(XAIE_INVALID_ARGS, "XAie_MoveDataToAie: the kernels have one input port (1)");
+  if (!k->has_in) return fail(XAIE_ERR, "XAie_MoveDataToAie: no host-to-tile route declared (XAie_RoutingHostToAie)");
+  XCUDA(cudaSetDevice(k->rt->device));
+  return h2t(k->rt, k->loc, k->rt->tile(k->loc).kernel.in_addr, src, bytes);
+}
+
+AieRC XAie_RunCore(XAie_Kernel_Inst* k) {
+  if (!k) return fail(XAIE_INVALID_ARGS, "null kernel instance");
+  XCUDA(cudaSetDevice(k->rt->device));
+  g_err.clear();
+  return launch_tile(k->rt, k->rt->tile(k->loc), 1);
+}
+
+AieRC XAie_WaitOutData(XAie_Kernel_Inst* k) {
+  if (!k) return fail(XAIE_INVALID_ARGS, "null kernel instance");
+  return XAie_CoreWaitForDone(k->rt->dev, k->loc, 10u * 1000u * 1000u);
+}
+
+AieRC XAie_MoveAieToData(XAie_Kernel_Inst* k, int port, void* dst, size_t bytes) {
+  if (!k || (!dst && bytes)) return fail(XAIE_INVALID_ARGS, "XAie_MoveAieToData: null argument");
+  if (port != 1) return fail(XAIE_INVALID_ARGS, "XAie_MoveAieToData: the kernels have one output port (1)");
+  if (!k->has_out) return fail(XAIE_ERR, "XAie_MoveAieToData: no tile-to-host route declared (XAie_RoutingAieToHost)");
+  XCUDA(cudaSetDevice(k->rt->device));
+  return t2h(k->rt, k->loc, k->rt->tile(k->loc).kernel.out_addr, dst, bytes);
+}
+
+AieRC XAie_KernelInstSetArgs(XAie_Kernel_Inst* k, const void* args, u32 bytes) {
+  if (!k) return fail(XAIE_INVALID_ARGS, "null kernel instance");
+  return XAie_KernelSetArgs(k->rt->dev, k->loc, args, bytes);
+}
+
+void XAie_UnloadKernel(XAie_Kernel_Inst* k) {
+  if (!k) return;
+  XAie_RoutingInstanceFree(k->ri);
+  delete k;
 }
 
 // ---------------------------------------------------------------------------------- registry API

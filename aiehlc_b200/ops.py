@@ -67,6 +67,9 @@ class Context:
     def set_cta_pair(self, mode: int) -> None:
         _capi.check(self._lib.aiehlc_set_cta_pair(self._h, int(mode)))
 
+    def set_host_blocks(self, blocks: int) -> None:
+        _capi.check(self._lib.aiehlc_set_host_blocks(self._h, int(blocks)))
+
     def set_shard_tile_stores(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_shard_tile_stores(self._h, 1 if on else 0))
 

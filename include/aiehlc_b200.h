@@ -214,6 +214,9 @@ int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on);
  *       order); measured 48.3 us against 49.7 us on the 4096^3 benchmark;
  *   0 = every tile computed whole. */
 int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on);
+/* Tuning knob for the *_host GEMM entry points: number of row blocks of A / C that upload, kernel and
+ * download are pipelined over (0 = default 4; blocks are whole 256-row tiles). */
+int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks);
 /* Tuning knob for aiehlc_gemm_i8_i32_scatter_dev: 1 (default) = results leave as add-reducing TMA tile
  * stores (32 rows x 128 bytes per store; needs N a multiple of 4 and 16-byte aligned shards, else the
  * other form is used), 0 = as per-row reduction instructions issued by the epilogue warps.  Measured

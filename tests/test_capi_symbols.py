@@ -45,6 +45,10 @@ def test_every_declared_xaie_symbol_is_exported():
         assert hasattr(lib, n), f"{n} declared in aiehlc_kernels.h but not exported"
     for n in ("XAie_KernelRegister", "XAie_KernelBind", "XAie_KernelCall"):
         assert hasattr(lib, n)
+    short_api = _declared_functions(ROOT / "include" / "xaie_placeholder.h", "XAie_")
+    assert len(short_api) >= 9
+    for n in short_api:
+        assert hasattr(lib, n), f"{n} declared in xaie_placeholder.h but not exported"
 
 
 def test_create_fails_loudly_without_a_gpu():

@@ -37,6 +37,7 @@ def test_unmodified_reference_host_program_on_b200(name, expect, count):
 
 def test_cpp_examples():
     exes = {p.name: p for p in build.build_examples()}
+    c8 = O.mm_i32(np.arange(0, 128, dtype=np.int32), 8, 8, 8)          # aieoob.c:83-86 through the oracle
     res = subprocess.run([str(exes["perf_host"])], capture_output=True, text=True, timeout=120)
     assert res.returncode == 0 and "CPU result matches vmem_out." in res.stdout, res.stdout + res.stderr
     assert "C[0]=36312 C[255]=2006232" in res.stdout
@@ -48,6 +49,11 @@ def test_cpp_examples():
     res = subprocess.run([str(exes["kernel_call"])], capture_output=True, text=True, timeout=120)
     assert res.returncode == 0 and "CPU result matches device output." in res.stdout, res.stdout + res.stderr
     assert "perf: C[0]=36312 C[255]=2006232, 0 mismatches" in res.stdout
+    # the short host API of example/other/aieoob.c:88-95 on its own 8x8 fixture (h_a[i] = i)
+    res = subprocess.run([str(exes["oob_host"])], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "CPU result matches vmem_out." in res.stdout, res.stdout + res.stderr
+    assert "C[0]=%d C[63]=%d" % (int(c8[0, 0]), int(c8[7, 7])) in res.stdout
+    assert "4x4: 0 mismatches" in res.stdout and "errors reported: 1 1 1" in res.stdout
 
 
 # ------------------------------------------------------------------ the same surface through ctypes
