@@ -310,9 +310,11 @@ int aiehlc_gemm_i8_i32_scatter_dev(aiehlc_ctx* ctx, const int8_t* A, const int8_
           if ((rc = encode_c_map(ctx, &maps[g], EPI_I32_ACC, 256, shards[src], rows, N, N))) return rc;
         }
         if (ctx->shard_maps.reserve(sizeof maps)) return AIEHLC_ERR_NOMEM;
-        // pageable source: the copy has left `maps` when the call returns, and it is ordered on `st`
-        // before the kernel that reads it
+        // Rare (once per set of shards): wait for the copy, so that later calls may reuse the maps from
+        // any stream, and for earlier launches on `st` that may still be reading the previous maps.
+        AIEHLC_CUDA(cudaStreamSynchronize(st));
         AIEHLC_CUDA(cudaMemcpyAsync(ctx->shard_maps.ptr, maps, sizeof(CUtensorMap) * num_shards, cudaMemcpyHostToDevice, st));
+        AIEHLC_CUDA(cudaStreamSynchronize(st));
         ctx->shard_key = key;
       }
     }
