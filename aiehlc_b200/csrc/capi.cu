@@ -162,6 +162,21 @@ int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm
   return plan_gemm(ctx, kind, M, N, K, plan);
 }
 
+int aiehlc_plan_tile_order(aiehlc_ctx* ctx, int kind, int M, int N, int K, int num_shards, int rows_per_shard,
+                           int first_shard, int* row_block, int* col_block, int capacity, int* slots) {
+  if (kind != KIND_I8 && kind != KIND_BF16) return fail(AIEHLC_ERR_INVALID, "plan_tile_order: kind must be 0 (int8) or 1 (bf16)");
+  if (M <= 0 || N <= 0 || K <= 0 || !row_block || !col_block || capacity < 0)
+    return fail(AIEHLC_ERR_INVALID, "plan_tile_order: bad argument");
+  if (num_shards < 0 || num_shards > AIEHLC_MAX_SHARDS || (num_shards > 0 && (rows_per_shard <= 0 || rows_per_shard % 128 != 0)))
+    return fail(AIEHLC_ERR_INVALID, "plan_tile_order: bad sharding");
+  if (!ctx) {
+    aiehlc_ctx defaults;
+    defaults.sm_count = 148;
+    return tile_order(&defaults, kind, M, N, K, num_shards, rows_per_shard, first_shard, row_block, col_block, capacity, slots);
+  }
+  return tile_order(ctx, kind, M, N, K, num_shards, rows_per_shard, first_shard, row_block, col_block, capacity, slots);
+}
+
 int aiehlc_set_k_per_load(aiehlc_ctx* ctx, int k_blocks) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   if (k_blocks < 0 || k_blocks > 2) return fail(AIEHLC_ERR_INVALID, "k_per_load must be 0, 1 or 2");

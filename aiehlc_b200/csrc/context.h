@@ -112,6 +112,8 @@ int launch_gemm(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st);
 int encode_c_map(aiehlc_ctx* ctx, CUtensorMap* map, int epi, int bn, void* base, long long rows, long long cols,
                  long long ld);
 int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* out);
+int tile_order(const aiehlc_ctx* ctx, int kind, int M, int N, int K, int num_shards, int rows_per_shard, int first_shard,
+               int* row_block, int* col_block, int capacity, int* slots_out);
 // Tail balancing: tiles [first, tiles) are cut into `parts` K ranges (parts == 1: no cut).
 void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int* parts);
 void narrow_tail(int tiles, int slots, int tile_n, int enabled, int* first, int* parts);

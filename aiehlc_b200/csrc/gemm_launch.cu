@@ -422,6 +422,29 @@ int dispatch_bn(aiehlc_ctx* ctx, const GemmCall& c, int bn, bool pair, cudaStrea
 
 }  // namespace
 
+// The order in which a launch visits its tiles, computed by the very function the kernels call:
+// tile t is (row_block[t], col_block[t]); with `slots` persistent CTAs (or pairs) slot s runs tiles
+// s, s + slots, ...  Returns the number of tiles, or a negative error.
+int tile_order(const aiehlc_ctx* ctx, int kind, int M, int N, int K, int num_shards, int rows_per_shard, int first_shard,
+               int* row_block, int* col_block, int capacity, int* slots_out) {
+  aiehlc_gemm_plan plan{};
+  if (int rc = plan_gemm(ctx, kind, M, N, K, &plan)) return rc;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.num_m_blocks = plan.grid_m; p.num_n_blocks = plan.grid_n; p.group_m = plan.group_m;
+  int slots = static_cast<int>(plan.tiles < plan.slots ? plan.tiles : plan.slots);
+  if (num_shards > 0) {
+    GemmCall c{};
+    c.M = M; c.num_shards = num_shards; c.rows_per_shard = rows_per_shard; c.first_shard = first_shard;
+    set_shard_rotation(p, c, plan.tile_m);
+    if (p.rot_shards > 0) slots = coprime_slots(slots, p.rot_shards);
+  }
+  if (slots_out) *slots_out = slots;
+  if (plan.tiles > capacity) return fail(AIEHLC_ERR_INVALID, "tile_order: the output arrays are too short");
+  for (int t = 0; t < static_cast<int>(plan.tiles); ++t) tile_coords(t, p, row_block[t], col_block[t]);
+  return static_cast<int>(plan.tiles);
+}
+
 int launch_gemm(aiehlc_ctx* ctx, const GemmCall& call, cudaStream_t st) {
   GemmCall c = call;
   if (c.M <= 0 || c.N <= 0 || c.K <= 0) return fail(AIEHLC_ERR_INVALID, "gemm: M, N, K must be positive");

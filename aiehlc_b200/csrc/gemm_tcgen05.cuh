@@ -135,7 +135,7 @@ struct GemmSmem {
   static constexpr int kTotal = kStages * kStageBytes + kStoreStagingBytes + kBarBytes + 1024;
 };
 
-__device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb, int& nb) {
+__host__ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb, int& nb) {
   if (p.rot_shards > 0) {
     // consecutive tiles (the ones in flight together) belong to consecutive shards; inside a shard the
     // usual walk over groups of group_m row-blocks
@@ -151,7 +151,7 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mb,
   const int per_group = p.group_m * p.num_n_blocks;
   const int g = t / per_group;
   const int first_m = g * p.group_m;
-  const int rows = min(p.group_m, p.num_m_blocks - first_m);
+  const int rows = p.group_m < p.num_m_blocks - first_m ? p.group_m : p.num_m_blocks - first_m;
   const int r = t - g * per_group;
   mb = first_m + r % rows;
   nb = r / rows;

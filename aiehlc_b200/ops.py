@@ -30,6 +30,25 @@ def plan_gemm(M: int, N: int, K: int, kind: str = "int8", ctx: "Context | None" 
     return plan.as_dict()
 
 
+def plan_tile_order(M: int, N: int, K: int, kind: str = "int8", num_shards: int = 0, rows_per_shard: int = 0,
+                    first_shard: int = 0, ctx: "Context | None" = None):
+    """(row_block, col_block) of every tile in the order a launch visits them, and the number of persistent
+    CTAs (or pairs) that share them round-robin (aiehlc_plan_tile_order); needs no GPU when ctx is None."""
+    import numpy as np
+    plan = plan_gemm(M, N, K, kind, ctx)
+    n = int(plan["tiles"])
+    rb = np.empty(n, dtype=np.int32)
+    cb = np.empty(n, dtype=np.int32)
+    slots = C.c_int(0)
+    h = ctx._h if ctx is not None else C.c_void_p(None)
+    got = _capi.load().aiehlc_plan_tile_order(h, {"int8": 0, "bf16": 1}[kind], int(M), int(N), int(K), int(num_shards),
+                                              int(rows_per_shard), int(first_shard), rb.ctypes.data, cb.ctypes.data, n,
+                                              C.byref(slots))
+    if got < 0:
+        _capi.check(got)
+    return rb[:got], cb[:got], int(slots.value)
+
+
 class Context:
     """Owns an `aiehlc_ctx` (device bring-up; stands in for the XAie_CfgInitialize /
     XAie_PartitionInitialize sequence of example/perf/aieml_perf.cc:265-313)."""

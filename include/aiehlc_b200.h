@@ -167,6 +167,15 @@ typedef struct {
 } aiehlc_gemm_plan;
 /* kind: 0 = int8, 1 = bf16.  ctx may be NULL: the plan is then made for a 148-SM B200 with default knobs. */
 int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* plan);
+/* The order in which that plan's tiles are visited (the traversal the compiler's tiling pass fixes when it
+ * walks the tile grid, tilinglinalg.cpp:101-129), computed by the function the kernels themselves call:
+ * tile t covers row block row_block[t] (of plan.tile_m rows) and column block col_block[t]; with *slots
+ * persistent CTAs (or CTA pairs) slot s runs tiles s, s + slots, ...  num_shards > 0 gives the order of
+ * aiehlc_gemm_i8_i32_scatter_dev (consecutive tiles on consecutive shards, slot count coprime with
+ * the shard count); 0 the plain order.  Returns the number of tiles (<= capacity) or a negative error.
+ * Needs no GPU (ctx may be NULL). */
+int aiehlc_plan_tile_order(aiehlc_ctx* ctx, int kind, int M, int N, int K, int num_shards, int rows_per_shard,
+                           int first_shard, int* row_block, int* col_block, int capacity, int* slots);
 
 /* ---- the same convolution for callers that must not allocate -----------------------------
  * (No counterpart in the reference: aiehlc has neither a convolution nor a device allocator.)

@@ -72,6 +72,43 @@ def test_gemm_planner_needs_no_gpu():
         plan_gemm(0, 4, 4)
 
 
+def test_tile_visiting_order_needs_no_gpu():
+    """The order the kernels walk the tile grid in (the function they call, run on the host): every tile
+    exactly once; plain launches walk groups of 8 row-blocks column by column; launches with a row-sharded
+    output put consecutive tiles on consecutive shards and use a slot count coprime with the shard count,
+    so each persistent CTA pair cycles through all owners."""
+    import numpy as np
+    from aiehlc_b200.ops import plan_gemm, plan_tile_order
+    M, N, K = 4096, 4096, 4096
+    p = plan_gemm(M, N, K)
+    rb, cb, slots = plan_tile_order(M, N, K)
+    assert slots == 74 and len(rb) == p["tiles"] == 256
+    assert len({(int(a), int(b)) for a, b in zip(rb, cb)}) == 256                 # a bijection onto the grid
+    assert list(rb[:8]) == list(range(8)) and set(cb[:8]) == {0}                  # group of 8 row-blocks, column 0
+    assert list(rb[8:16]) == list(range(8)) and set(cb[8:16]) == {1}
+    # ragged grid: the last group has fewer row-blocks
+    rb, cb, _ = plan_tile_order(2560 + 100, 1000, 512)
+    grid = plan_gemm(2560 + 100, 1000, 512)
+    assert len({(int(a), int(b)) for a, b in zip(rb, cb)}) == grid["tiles"] == grid["grid_m"] * grid["grid_n"]
+    assert rb.max() == grid["grid_m"] - 1 and cb.max() == grid["grid_n"] - 1
+    # split-K exchange over 8 owners: 65536 rows, 8192 per shard = 32 row-blocks of 256 rows each
+    M, N, K, shards, rps = 65536, 8192, 1024, 8, 8192
+    for first in (1, 5):
+        rb, cb, slots = plan_tile_order(M, N, K, num_shards=shards, rows_per_shard=rps, first_shard=first)
+        assert len(rb) == 256 * 32 and len({(int(a), int(b)) for a, b in zip(rb, cb)}) == len(rb)
+        owner = rb // (rps // 256)
+        assert list(owner[:16]) == [(first + t) % shards for t in range(16)]      # consecutive tiles, consecutive owners
+        assert slots == 73 and np.gcd(slots, shards) == 1
+        for s in (0, 36, 72):                                                     # every slot meets every owner in 8 rounds
+            assert set(owner[s::slots][:shards]) == set(range(shards))
+    # shards that do not hold whole groups of row-blocks: rows in plain order, still every tile once
+    rb, cb, slots = plan_tile_order(1000, 520, 272, num_shards=4, rows_per_shard=256)
+    assert len({(int(a), int(b)) for a, b in zip(rb, cb)}) == len(rb)
+    from aiehlc_b200 import _capi
+    with pytest.raises(_capi.AiehlcError):
+        plan_tile_order(1000, 520, 272, num_shards=4, rows_per_shard=100)
+
+
 _WORKER = textwrap.dedent("""
     import os, sys
     import numpy as np, torch, torch.distributed as dist
