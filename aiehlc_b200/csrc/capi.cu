@@ -232,7 +232,7 @@ int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer) {
 
 int aiehlc_set_debug(aiehlc_ctx* ctx, int mode) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
-  if (mode < 0 || mode > 2) return fail(AIEHLC_ERR_INVALID, "debug mode must be 0, 1 or 2");
+  if (mode < 0 || mode > 3) return fail(AIEHLC_ERR_INVALID, "debug mode must be 0, 1, 2 or 3");
   ctx->debug_mode = mode;
   return AIEHLC_OK;
 }

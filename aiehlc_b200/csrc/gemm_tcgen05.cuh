@@ -84,7 +84,9 @@ struct GemmParams {
   // (narrower MMAs, no exchange between the ranges).  nt_parts == 1: off.  Never together with sk_parts > 1.
   int nt_first_tile, nt_parts;
   long long* trace;        // measurement aid: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
-  int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling)
+  int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling);
+                           // test aid: 3 = the producer neither loads nor signals, so every consumer wait
+                           // runs out and the kernel leaves through its bounded-wait exit
 };
 
 // Shift-round-saturate, pure integer: round half to even on the dropped bits, saturate to int8.
@@ -456,8 +458,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                          ST_TIMEOUT_EMPTY);
           if (!ok) break;
           const uint32_t fb = smem_u32(&full_bar[stage]);
-          if (p.debug == 1) {
-            mbar_arrive(fb);
+          if (p.debug == 1 || p.debug == 3) {
+            if (p.debug == 1) mbar_arrive(fb);
             if (++stage == kStages) { stage = 0; phase ^= 1; }
             continue;
           }

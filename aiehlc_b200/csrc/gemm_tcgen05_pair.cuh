@@ -194,8 +194,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
           if (!ok) break;
           const uint32_t fb_local = smem_u32(&full_bar[stage]);
-          if (p.debug == 1) {
-            if (leader) mbar_arrive(fb_local);
+          if (p.debug == 1 || p.debug == 3) {
+            if (p.debug == 1 && leader) mbar_arrive(fb_local);
             if (++stage == kStages) { stage = 0; phase ^= 1; }
             continue;
           }

@@ -243,7 +243,12 @@ int aiehlc_set_group_m(aiehlc_ctx* ctx, int group_m);
 int aiehlc_set_pdl(aiehlc_ctx* ctx, int on);
 /* Measurement aid for the GEMM kernels (results are then meaningless): 1 = skip the TMA loads and
  * run the MMAs on whatever shared memory holds (tensor-pipe ceiling), 2 = skip the MMAs and only
- * stream the operands (operand-feed ceiling), 0 = normal. */
+ * stream the operands (operand-feed ceiling), 0 = normal.
+ * Test aid: 3 = the producer warp neither loads nor signals.  Every other warp's wait then runs out
+ * (about one second), the kernel records which wait gave up in the status word, frees its TMEM and
+ * returns; aiehlc_sync reports AIEHLC_ERR_DEVICE with the code (102 = the MMA issuer waited for
+ * operands) and clears it, and the context stays usable.  This is how the bounded-wait exit is tested
+ * without faulting or hanging the GPU. */
 int aiehlc_set_debug(aiehlc_ctx* ctx, int mode);
 /* Measurement aid: while `device_buffer` is non-NULL, the first CTA of every GEMM launch writes
  * clock64() stamps for each of its tiles into it, 8 int64 slots per tile: [0] MMA loop start,

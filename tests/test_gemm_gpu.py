@@ -288,6 +288,36 @@ def test_row_sharded_add_reduction_output(ctx, M, N, K, rows_per_shard, group_m,
         ctx.gemm_i8_i32_scatter(dA, dB, shards[:1], 128)               # shards do not cover M
 
 
+@pytest.mark.parametrize("pair", [0, 1])
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives(ctx, pair):
+    """No GPU fault, no hang: the producer is told not to deliver (debug mode 3), the consumers' bounded
+    waits run out after about a second, the kernel returns through its error exit, the host reads which
+    wait gave up, and the next launch on the same context is correct again."""
+    import ctypes as C
+    import time
+    M, N, K = 256, 256, 256
+    A = synth.int8_uniform(14, (M, K))
+    B = synth.int8_uniform(1014, (N, K))
+    dA, dB = _dev(A), _dev(B)
+    ctx.set_cta_pair(pair)
+    try:
+        ctx.set_debug(3)
+        t0 = time.perf_counter()
+        ctx.gemm_i8_i32(dA, dB)
+        st = C.c_int32(0)
+        rc = ctx._lib.aiehlc_sync(ctx._h, ctx._stream(), C.byref(st))
+        waited = time.perf_counter() - t0
+        assert rc == _capi.ERR_DEVICE and st.value in (101, 102, 104), (rc, st.value)   # which wait gave up first
+        assert 0.3 < waited < 10.0, waited
+        ctx.set_debug(0)
+        assert ctx.sync() == 0                                                          # the word was cleared
+        assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), O.gemm_i8_i32(A, B))
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_debug(0)
+        ctx.set_cta_pair(-1)
+
+
 def test_accumulate_and_flush(ctx):
     M, N, K = 200, 136, 512
     A = synth.int8_uniform(2, (M, K))
