@@ -32,6 +32,15 @@ struct ConvParams {
   int cout_tile;                   // N of the MMA (multiple of 16, <= 256)
   int stages, stage_bytes, a_bytes;
   uint32_t tx_bytes;               // bytes one stage's two TMA boxes deliver
+  // Halo form (halo != 0): ONE activation box per cin chunk brings the whole input patch of the tile,
+  // (rows_per_tile + kh - 1) image rows of row_w = wt + kw - 1 pixels, and ONE weight box brings that
+  // chunk of every tap.  The GEMM's M index runs over the patch rows (m = r * row_w + c, the kw - 1
+  // extra columns per row are computed and dropped), so the A operand of tap (fh, fw) is the same
+  // patch read from (fh * row_w + fw) rows further on: nine descriptors into one tile instead of
+  // nine tiles.  Two boxes per CTA and chunk instead of 2 * kh * kw.
+  int halo;
+  int row_w;                       // pixels per M row group: wt + kw - 1 (halo) or wt
+  uint32_t w_block_bytes;          // halo: one tap's cout_tile x chunk block inside the weight box
   uint32_t swizzle_code, sbo_bytes;
   uint32_t tmem_cols;
   int8_t* y;
@@ -101,7 +110,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   const int ow0 = tw * p.wt;
   const int co0 = blockIdx.y * p.cout_tile;
   const int taps = p.kh * p.kw;
-  const int num_kb = taps * p.chunks_per_tap;
+  const int num_kb = p.halo ? p.chunks_per_tap : taps * p.chunks_per_tap;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -111,13 +120,20 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
         if (!ok) break;
-        const int tap = kb / p.chunks_per_tap;
-        const int c0 = (kb - tap * p.chunks_per_tap) * p.chunk;
-        const int fh = tap / p.kw, fw = tap - fh * p.kw;
         const uint32_t fb = smem_u32(&full_bar[stage]);
         mbar_expect_tx(fb, p.tx_bytes);
         uint8_t* sa = smem + stage * p.stage_bytes;
         uint8_t* sb = sa + p.a_bytes;
+        if (p.halo) {
+          // the whole patch (zero-filled outside the image: that is the padding) and every tap's weights
+          tma_load_4d(smem_u32(sa), &tmap_x, fb, kb * p.chunk, ow0 - p.pad, oh0 - p.pad, img);
+          tma_load_3d(smem_u32(sb), &tmap_w, fb, kb * p.chunk, co0, 0);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          continue;
+        }
+        const int tap = kb / p.chunks_per_tap;
+        const int c0 = (kb - tap * p.chunks_per_tap) * p.chunk;
+        const int fh = tap / p.kw, fw = tap - fh * p.kw;
         // Innermost coordinate (channel) is a multiple of the chunk size, hence 16-byte aligned;
         // the spatial coordinates may be negative or past the edge: those elements read as zero.
         tma_load_4d(smem_u32(sa), &tmap_x, fb, c0, ow0 + fw - p.pad, oh0 + fh - p.pad, img);
@@ -141,10 +157,37 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (tracing && kb < 12) p.trace[8 + kb] = clock64();
         const uint32_t sa = smem_u32(smem + stage * p.stage_bytes);
         const uint32_t sb = sa + p.a_bytes;
-        const uint64_t adesc = make_kmajor_desc(sa, p.sbo_bytes, p.swizzle_code);
-        const uint64_t bdesc = make_kmajor_desc(sb, p.sbo_bytes, p.swizzle_code);
-        for (int k = 0; k < p.chunk / kUmmaKBytes; ++k)
-          umma_ss<KIND_I8, 1>(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        if (p.halo) {
+          // Tap (fh, fw) reads the patch from (fh * row_w + fw) rows further on.  The descriptor's start
+          // address simply moves by that many rows: TMA laid the swizzle pattern down as a function of
+          // the absolute shared-memory address and the tensor core applies it to the addresses it
+          // computes, so a start that is not on an 8-row pattern boundary needs nothing else (the
+          // descriptor's base-offset field stays 0; setting it to the start's phase gives wrong data).
+          // One thread issues everything: the descriptors advance by additions only.
+          const uint64_t a0 = make_kmajor_desc(sa, p.sbo_bytes, p.swizzle_code);
+          uint64_t bd = make_kmajor_desc(sb, p.sbo_bytes, p.swizzle_code);
+          const uint32_t px_step = static_cast<uint32_t>(p.chunk) >> 4;
+          const uint32_t row_step = px_step * p.row_w, w_step = p.w_block_bytes >> 4;
+          const int ksteps = p.chunk / kUmmaKBytes;
+          uint32_t accum = kb != 0 ? 1u : 0u;
+          for (int fh = 0; fh < p.kh; ++fh) {
+            uint64_t ad = a0 + fh * row_step;
+            for (int fw = 0; fw < p.kw; ++fw) {
+#pragma unroll 4
+              for (int k = 0; k < ksteps; ++k) {
+                umma_ss<KIND_I8, 1>(tmem_base, ad + 2 * k, bd + 2 * k, idesc, accum);
+                accum = 1u;
+              }
+              ad += px_step;
+              bd += w_step;
+            }
+          }
+        } else {
+          const uint64_t adesc = make_kmajor_desc(sa, p.sbo_bytes, p.swizzle_code);
+          const uint64_t bdesc = make_kmajor_desc(sb, p.sbo_bytes, p.swizzle_code);
+          for (int k = 0; k < p.chunk / kUmmaKBytes; ++k)
+            umma_ss<KIND_I8, 1>(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        }
         umma_commit(smem_u32(&empty_bar[stage]));
         if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
@@ -159,8 +202,9 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       tc_fence_after();
       if (tracing && warp == 2 && lane == 0) p.trace[4] = clock64();
       const int m = quad * 32 + lane;
-      const int oh = oh0 + m / p.wt, ow = ow0 + m % p.wt;
-      const bool pix_ok = m < p.rows_per_tile * p.wt && oh < p.h && ow < p.w;
+      const int mr = m / p.row_w, mc = m - mr * p.row_w;   // image row and column inside the tile
+      const int oh = oh0 + mr, ow = ow0 + mc;
+      const bool pix_ok = mr < p.rows_per_tile && mc < p.wt && oh < p.h && ow < p.w;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
       int8_t* yrow = p.y + ((static_cast<long long>(img) * p.h + oh) * p.w + ow) * p.cout;
       const bool vec = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && (p.cout % 16 == 0);
@@ -294,42 +338,76 @@ int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed,
   const int taps = kh * kw;
   ConvParams p{};
   p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
-  p.wt = wd <= kBlockM ? wd : kBlockM;
-  p.rows_per_tile = wd <= kBlockM ? kBlockM / wd : 1;
-  if (p.rows_per_tile > h) p.rows_per_tile = h;
-  p.tiles_w = (wd + p.wt - 1) / p.wt;
-  p.chunk = cin >= 128 ? 128 : cin;
-  p.chunks_per_tap = cin / p.chunk;
-  p.cout_tile = cout <= 256 ? cout : 256;
-  if (cout > 256 && cout % 256 != 0) {
-    // keep every channel tile a legal MMA N: use the largest multiple of 16 that divides cout
-    int ct = 256;
-    while (ct > 16 && cout % ct != 0) ct -= 16;
-    p.cout_tile = ct;
-  }
-  // A small problem is bound by how fast one SM's TMA unit can fetch its operand rows, not by the
-  // tensor pipe: while fewer than half of the SMs would have a tile, give each CTA fewer image rows,
-  // then fewer output channels (halves that still divide cout and stay multiples of 16).
-  auto ctas = [&]() {
-    return static_cast<long long>(n) * ((h + p.rows_per_tile - 1) / p.rows_per_tile) * p.tiles_w *
-           ((cout + p.cout_tile - 1) / p.cout_tile);
-  };
-  while (ctas() * 2 < ctx->sm_count && p.rows_per_tile > 1) p.rows_per_tile = (p.rows_per_tile + 1) / 2;
-  while (ctas() * 2 < ctx->sm_count && p.cout_tile % 32 == 0 && p.cout_tile >= 64) p.cout_tile /= 2;
-  p.tiles_h = (h + p.rows_per_tile - 1) / p.rows_per_tile;
-  const int n_tiles = (cout + p.cout_tile - 1) / p.cout_tile;
-  p.swizzle_code = p.chunk == 128 ? 2u : (p.chunk == 64 ? 4u : 6u);
-  p.sbo_bytes = 8u * p.chunk;
-  p.a_bytes = kBlockM * p.chunk;                       // 128 rows reserved, R*Wt of them written
-  const int b_bytes = (p.cout_tile * p.chunk + 1023) / 1024 * 1024;
-  p.stage_bytes = p.a_bytes + b_bytes;
-  p.tx_bytes = static_cast<uint32_t>(p.chunk) * (p.wt * p.rows_per_tile + p.cout_tile);
   const int budget = 200 * 1024;
-  int stages = budget / p.stage_bytes;
-  if (stages > kConvMaxStages) stages = kConvMaxStages;
-  const int num_kb = taps * p.chunks_per_tap;
-  if (stages > num_kb) stages = num_kb;
-  p.stages = stages;
+  int n_tiles = 1;
+  // Tiling for one of the two forms; false if the halo form does not fit in shared memory.
+  auto configure = [&](bool halo) -> bool {
+    p.halo = halo ? 1 : 0;
+    if (halo) {
+      // the M rows of a tile run over patch rows of wt + kw - 1 pixels (see ConvParams::halo)
+      p.wt = wd + kw - 1 <= kBlockM ? wd : kBlockM - (kw - 1);
+      p.rows_per_tile = kBlockM / (p.wt + kw - 1);
+    } else {
+      p.wt = wd <= kBlockM ? wd : kBlockM;
+      p.rows_per_tile = wd <= kBlockM ? kBlockM / wd : 1;
+    }
+    if (p.rows_per_tile > h) p.rows_per_tile = h;
+    p.tiles_w = (wd + p.wt - 1) / p.wt;
+    p.chunk = cin >= 128 ? 128 : cin;
+    p.chunks_per_tap = cin / p.chunk;
+    p.cout_tile = cout <= 256 ? cout : 256;
+    if (cout > 256 && cout % 256 != 0) {
+      // keep every channel tile a legal MMA N: use the largest multiple of 16 that divides cout
+      int ct = 256;
+      while (ct > 16 && cout % ct != 0) ct -= 16;
+      p.cout_tile = ct;
+    }
+    // A small problem is bound by the latency of a CTA's TMA boxes, not by the tensor pipe: while fewer
+    // than half of the SMs would have a tile, give each CTA fewer image rows, then fewer output
+    // channels (halves that still divide cout and stay multiples of 16).
+    auto ctas = [&]() {
+      return static_cast<long long>(n) * ((h + p.rows_per_tile - 1) / p.rows_per_tile) * p.tiles_w *
+             ((cout + p.cout_tile - 1) / p.cout_tile);
+    };
+    while (ctas() * 2 < ctx->sm_count && p.rows_per_tile > 1) p.rows_per_tile = (p.rows_per_tile + 1) / 2;
+    while (ctas() * 2 < ctx->sm_count && p.cout_tile % 32 == 0 && p.cout_tile >= 64) p.cout_tile /= 2;
+    // the halo form holds every tap's weights of a channel tile at once: narrow the tile until they fit
+    if (halo)
+      while (taps * p.cout_tile * p.chunk > 96 * 1024 && p.cout_tile % 32 == 0 && cout % (p.cout_tile / 2) == 0)
+        p.cout_tile /= 2;
+    p.tiles_h = (h + p.rows_per_tile - 1) / p.rows_per_tile;
+    n_tiles = (cout + p.cout_tile - 1) / p.cout_tile;
+    p.swizzle_code = p.chunk == 128 ? 2u : (p.chunk == 64 ? 4u : 6u);
+    p.sbo_bytes = 8u * p.chunk;
+    p.row_w = p.wt;
+    int num_kb = taps * p.chunks_per_tap;
+    int b_bytes = (p.cout_tile * p.chunk + 1023) / 1024 * 1024;
+    p.a_bytes = kBlockM * p.chunk;                       // 128 rows reserved, R*Wt of them written
+    p.tx_bytes = static_cast<uint32_t>(p.chunk) * (p.wt * p.rows_per_tile + p.cout_tile);
+    if (halo) {
+      const int row_w = p.wt + kw - 1;
+      const int patch_rows = (p.rows_per_tile + kh - 1) * row_w;
+      // the last tap's descriptor starts (kh-1)*row_w + kw-1 rows in and the MMA reads 128 rows from there
+      const int reach = (kh - 1) * row_w + (kw - 1) + kBlockM;
+      const int a_rows = patch_rows > reach ? patch_rows : reach;
+      const int a_bytes = (a_rows * p.chunk + 1023) / 1024 * 1024;
+      const int w_bytes = (taps * p.cout_tile * p.chunk + 1023) / 1024 * 1024;
+      if (a_bytes + w_bytes > budget || p.rows_per_tile + kh - 1 > 256 || row_w > 256 || taps > 256) return false;
+      p.row_w = row_w;
+      p.a_bytes = a_bytes;
+      b_bytes = w_bytes;
+      p.w_block_bytes = static_cast<uint32_t>(p.cout_tile) * p.chunk;
+      p.tx_bytes = static_cast<uint32_t>(p.chunk) * (patch_rows + taps * p.cout_tile);
+      num_kb = p.chunks_per_tap;
+    }
+    p.stage_bytes = p.a_bytes + b_bytes;
+    int stages = budget / p.stage_bytes;
+    if (stages > kConvMaxStages) stages = kConvMaxStages;
+    if (stages > num_kb) stages = num_kb;
+    p.stages = stages;
+    return true;
+  };
+  if (!(ctx->conv_halo && taps > 1 && kw <= kBlockM / 2 && configure(true))) configure(false);
   uint32_t cols = 32;
   while (cols < static_cast<uint32_t>(p.cout_tile)) cols <<= 1;
   p.tmem_cols = cols;
@@ -343,8 +421,8 @@ int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed,
                                 static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(n)};
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cin) * wd,
                                    static_cast<cuuint64_t>(cin) * wd * h};
-    const cuuint32_t box[4] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.wt),
-                               static_cast<cuuint32_t>(p.rows_per_tile), 1};
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.row_w),
+                               static_cast<cuuint32_t>(p.halo ? p.rows_per_tile + kh - 1 : p.rows_per_tile), 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUtensorMapSwizzle sw = p.chunk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                   : p.chunk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
@@ -356,9 +434,20 @@ int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed,
     const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(taps) * cout};
     const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(cin)};
     const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.cout_tile)};
-    r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(packed), wdims, wstrides, wbox, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (p.halo) {
+      // the packed weights as {cin, cout, taps}: one box holds a cin chunk of every tap for this channel tile
+      const cuuint64_t w3dims[3] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cout), static_cast<cuuint64_t>(taps)};
+      const cuuint64_t w3strides[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cin) * cout};
+      const cuuint32_t w3box[3] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.cout_tile),
+                                   static_cast<cuuint32_t>(taps)};
+      r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(packed), w3dims, w3strides, w3box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+      r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(packed), wdims, wstrides, wbox, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
   }
 
@@ -481,6 +570,7 @@ int launch_conv2d_static(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8
   const int b_bytes = (p.cout_tile * p.chunk + 1023) / 1024 * 1024;
   p.stage_bytes = p.a_bytes + b_bytes;
   p.tx_bytes = static_cast<uint32_t>(p.chunk) * (p.wt * p.rows_per_tile + p.cout_tile);
+  p.row_w = p.wt;  // one K block per tap and channel chunk (the form this entry point was written for)
   int stages = (200 * 1024) / p.stage_bytes;
   if (stages > kConvMaxStages) stages = kConvMaxStages;
   if (stages > taps * p.chunks_per_tap) stages = taps * p.chunks_per_tap;

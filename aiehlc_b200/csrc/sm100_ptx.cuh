@@ -113,6 +113,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
                                             int c1, int c2, int c3) {
   asm volatile(
@@ -310,6 +317,9 @@ __device__ __forceinline__ void umma_commit_pair_mask(uint32_t bar, uint16_t cta
 //   bits [0,14)  start address >> 4      bits [32,46) stride byte offset >> 4
 //   bits [16,30) leading byte offset>>4  bits [46,48) descriptor version (1 on sm_100)
 //   bits [61,64) swizzle: 0 none, 2 = 128B, 4 = 64B, 6 = 32B
+// The start address may be any 16-byte aligned address inside a tile that TMA wrote: the swizzle is a
+// function of the absolute shared-memory address on both sides (measured: an operand that starts at any
+// row of a tile reads the right data with the base-offset field, bits [49,52), left at 0).
 __device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr, uint32_t sbo_bytes,
                                                      uint32_t swizzle_code) {
   uint64_t d = 0;

@@ -226,6 +226,12 @@ int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on);
 /* Tuning knob for the *_host GEMM entry points: number of row blocks of A / C that upload, kernel and
  * download are pipelined over (0 = default 4; blocks are whole 256-row tiles). */
 int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks);
+/* Tuning knob for the convolution kernel: 1 (default) = a CTA fetches its tile's whole input patch
+ * (rows + kh - 1 image rows of width + kw - 1 pixels, zero-filled outside the image) with ONE TMA box and
+ * every tap's weights with another, and the kh * kw taps are kh * kw views into that one patch; 0 = one
+ * activation box and one weight box per tap.  Filters whose taps do not fit in shared memory take the
+ * second form whatever the setting. */
+int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on);
 /* Tuning knob for aiehlc_gemm_i8_i32_scatter_dev: 1 (default) = results leave as add-reducing TMA tile
  * stores (32 rows x 128 bytes per store; needs N a multiple of 4 and 16-byte aligned shards, else the
  * other form is used), 0 = as per-row reduction instructions issued by the epilogue warps.  Measured

@@ -21,16 +21,40 @@ CONV_SHAPES = [(1, 56, 56, 64, 64),      # the benchmark configuration
                (1, 8, 8, 24, 16), (2, 5, 5, 3, 8), (1, 4, 4, 64, 10)]   # the last three take the direct kernel
 
 
+@pytest.mark.parametrize("halo", [True, False])
 @pytest.mark.parametrize("shape", CONV_SHAPES)
-def test_conv2d_matches_oracle(ctx, shape):
+def test_conv2d_matches_oracle(ctx, shape, halo):
+    """Both forms of the tensor-core kernel: the tile's input patch fetched once with all taps as views
+    into it (halo), and one activation box per tap."""
     n, h, w, cin, cout = shape
     x = synth.int8_uniform(4, (n, h, w, cin))
     wt = synth.int8_uniform(1004, (3, 3, cin, cout))
     sv = np.full(cout, 6, np.uint8)
     exp = O.conv2d_i8_srs(x, wt, sv, pad=1)
-    got = ctx.conv2d_i8_srs(_dev(x), _dev(wt), _dev(sv), pad=1).cpu().numpy()
-    assert ctx.sync() == 0
+    ctx.set_conv_halo(halo)
+    try:
+        got = ctx.conv2d_i8_srs(_dev(x), _dev(wt), _dev(sv), pad=1).cpu().numpy()
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_conv_halo(True)
     assert np.array_equal(got, exp)
+
+
+@pytest.mark.parametrize("kh,kw,pad,shape", [(5, 5, 2, (1, 12, 12, 64, 32)), (7, 7, 3, (2, 20, 20, 32, 16)),
+                                             (3, 3, 1, (1, 10, 200, 64, 48)), (5, 5, 2, (1, 6, 300, 128, 32)),
+                                             (3, 3, 1, (1, 3, 126, 256, 64)), (9, 9, 4, (1, 9, 9, 64, 16)),
+                                             (1, 1, 0, (1, 8, 8, 256, 32))])
+def test_conv2d_other_filters_through_the_patch_form(ctx, kh, kw, pad, shape):
+    """Other filter sizes (same-size output: kh = kw = 2 * pad + 1), images wider than one tile (the patch
+    form tiles the width in pieces of 128 - (kw - 1) pixels), several input-channel chunks, and the 1 x 1
+    filter, which has no patch to share and takes the per-tap form."""
+    n, h, w, cin, cout = shape
+    x = synth.int8_uniform(6, (n, h, w, cin))
+    wt = synth.int8_uniform(1006, (kh, kw, cin, cout))
+    sv = ((np.arange(cout) * 5) % 12).astype(np.uint8)
+    got = ctx.conv2d_i8_srs(_dev(x), _dev(wt), _dev(sv), pad=pad).cpu().numpy()
+    assert ctx.sync() == 0
+    assert np.array_equal(got, O.conv2d_i8_srs(x, wt, sv, pad=pad))
 
 
 def test_conv2d_per_channel_shifts_5x5_and_host_entry(ctx):
