@@ -48,6 +48,7 @@ SIGNATURES = {
     "aiehlc_set_group_m": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_split_tail": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_tma_store": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_plan_conv2d": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "aiehlc_plan_tile_order": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp,
                                          C.c_int, _vp]),
     "aiehlc_set_k_per_load": (C.c_int, [_vp, C.c_int]),
@@ -75,6 +76,16 @@ class GemmPlan(C.Structure):
 
 
 SIGNATURES["aiehlc_plan_gemm"] = (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(GemmPlan)])
+
+
+class ConvPlan(C.Structure):
+    """aiehlc_conv_plan of include/aiehlc_b200.h."""
+    _fields_ = [(n, C.c_int) for n in ("form", "tile_rows", "tile_width", "patch_rows", "patch_width", "m_rows_used",
+                                       "cout_tile", "cin_chunk", "ctas", "tma_boxes_per_cta", "mmas_per_cta", "stages",
+                                       "smem_bytes")]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_}
 
 _lib = None
 

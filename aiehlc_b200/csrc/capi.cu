@@ -424,6 +424,21 @@ int aiehlc_conv2d_i8_srs_dev(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, 
   return launch_conv2d(ctx, x, w, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec, pick_stream(ctx, stream));
 }
 
+int aiehlc_plan_conv2d(aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, int kh, int kw, int pad,
+                       aiehlc_conv_plan* plan) {
+  if (!plan) return fail(AIEHLC_ERR_INVALID, "plan_conv2d: null plan");
+  if (n <= 0 || h <= 0 || wd <= 0 || cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0 || pad < 0)
+    return fail(AIEHLC_ERR_INVALID, "plan_conv2d: bad size");
+  if (kh != 2 * pad + 1 || kw != 2 * pad + 1)
+    return fail(AIEHLC_ERR_UNSUPPORTED, "conv2d: only stride 1 with kh = kw = 2*pad+1 (same-size output)");
+  if (!ctx) {
+    aiehlc_ctx defaults;  // no device needed to plan: a 148-SM B200 with default settings
+    defaults.sm_count = 148;
+    return plan_conv2d(&defaults, n, h, wd, cin, cout, kh, kw, pad, plan);
+  }
+  return plan_conv2d(ctx, n, h, wd, cin, cout, kh, kw, pad, plan);
+}
+
 int aiehlc_conv2d_pack_weights_dev(aiehlc_ctx* ctx, const int8_t* w, int8_t* packed, int kh, int kw, int cin,
                                    int cout, void* stream) {
   int rc = check_ctx(ctx);

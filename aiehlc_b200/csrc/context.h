@@ -133,6 +133,8 @@ int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, 
                   int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st);
 
 bool conv_tensor_path(const int8_t* x, int cin, int cout);
+int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, int kh, int kw, int pad,
+                aiehlc_conv_plan* out);
 int launch_conv_pack_weights(aiehlc_ctx* ctx, const int8_t* w, int8_t* packed, int taps, int cin, int cout,
                              cudaStream_t st);
 int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, int8_t* y, int n, int h, int wd,

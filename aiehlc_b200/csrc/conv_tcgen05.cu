@@ -336,15 +336,15 @@ int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, 
                               shift_vec, st);
 }
 
-// The implicit-GEMM kernel on weights that are already [tap][cout][cin].
-int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, int8_t* y, int n, int h, int wd,
-                         int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
+// Tiling of the tensor-core kernel for the problem already written into p (n .. pad): fills the tile,
+// pipeline and form fields; *n_tiles = output-channel tiles (grid y).  The patch form is taken when the
+// context allows it and the tile's patch plus every tap's weights fit in shared memory.
+void configure_conv(const aiehlc_ctx* ctx, ConvParams& p, int* n_tiles_out) {
+  const int n = p.n, h = p.h, wd = p.w, cin = p.cin, cout = p.cout, kh = p.kh, kw = p.kw;
   const int taps = kh * kw;
-  ConvParams p{};
-  p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
   const int budget = 200 * 1024;
   int n_tiles = 1;
-  // Tiling for one of the two forms; false if the halo form does not fit in shared memory.
+  // Tiling for one of the two forms; false if the patch form does not fit in shared memory.
   auto configure = [&](bool halo) -> bool {
     p.halo = halo ? 1 : 0;
     if (halo) {
@@ -412,6 +412,52 @@ int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed,
     return true;
   };
   if (!(ctx->conv_halo && taps > 1 && kw <= kBlockM / 2 && configure(true))) configure(false);
+  *n_tiles_out = n_tiles;
+}
+
+// What launch_conv2d_packed will do, for the exported planner.
+int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, int kh, int kw, int pad,
+                aiehlc_conv_plan* out) {
+  aiehlc_conv_plan pl{};
+  if ((cin % 32 != 0) || !(cin == 32 || cin == 64 || cin % 128 == 0) || cout % 16 != 0) {
+    pl.form = 2;  // CUDA-core kernel: one thread per output element
+    const long long total = static_cast<long long>(n) * h * wd * cout;
+    long long g = (total + 255) / 256;
+    if (g > ctx->sm_count * 16LL) g = ctx->sm_count * 16LL;
+    pl.ctas = static_cast<int>(g);
+    *out = pl;
+    return AIEHLC_OK;
+  }
+  ConvParams p{};
+  p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
+  int n_tiles = 1;
+  configure_conv(ctx, p, &n_tiles);
+  pl.form = p.halo ? 1 : 0;
+  pl.tile_rows = p.rows_per_tile;
+  pl.tile_width = p.wt;
+  pl.patch_rows = p.halo ? p.rows_per_tile + kh - 1 : p.rows_per_tile;
+  pl.patch_width = p.row_w;
+  pl.cout_tile = p.cout_tile;
+  pl.cin_chunk = p.chunk;
+  pl.ctas = n * p.tiles_h * p.tiles_w * n_tiles;
+  const int taps = kh * kw;
+  pl.tma_boxes_per_cta = p.halo ? 2 * p.chunks_per_tap : 2 * taps * p.chunks_per_tap;
+  pl.mmas_per_cta = taps * p.chunks_per_tap * (p.chunk / kUmmaKBytes);
+  pl.stages = p.stages;
+  pl.smem_bytes = p.stages * p.stage_bytes + 512 + 1024;
+  pl.m_rows_used = p.rows_per_tile * p.row_w;
+  *out = pl;
+  return AIEHLC_OK;
+}
+
+// The implicit-GEMM kernel on weights that are already [tap][cout][cin].
+int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, int8_t* y, int n, int h, int wd,
+                         int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
+  const int taps = kh * kw;
+  ConvParams p{};
+  p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
+  int n_tiles = 1;
+  configure_conv(ctx, p, &n_tiles);
   uint32_t cols = 32;
   while (cols < static_cast<uint32_t>(p.cout_tile)) cols <<= 1;
   p.tmem_cols = cols;

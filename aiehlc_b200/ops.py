@@ -30,6 +30,17 @@ def plan_gemm(M: int, N: int, K: int, kind: str = "int8", ctx: "Context | None" 
     return plan.as_dict()
 
 
+def plan_conv2d(n: int, h: int, w: int, cin: int, cout: int, kh: int = 3, kw: int = 3, pad: int = 1,
+                ctx: "Context | None" = None) -> dict:
+    """The form and tiling the convolution entry points use for this problem (aiehlc_plan_conv2d); needs no GPU
+    when ctx is None."""
+    plan = _capi.ConvPlan()
+    hdl = ctx._h if ctx is not None else C.c_void_p(None)
+    _capi.check(_capi.load().aiehlc_plan_conv2d(hdl, int(n), int(h), int(w), int(cin), int(cout), int(kh), int(kw),
+                                                int(pad), C.byref(plan)))
+    return plan.as_dict()
+
+
 def plan_tile_order(M: int, N: int, K: int, kind: str = "int8", num_shards: int = 0, rows_per_shard: int = 0,
                     first_shard: int = 0, ctx: "Context | None" = None):
     """(row_block, col_block) of every tile in the order a launch visits them, and the number of persistent

@@ -177,6 +177,21 @@ int aiehlc_plan_gemm(aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm
 int aiehlc_plan_tile_order(aiehlc_ctx* ctx, int kind, int M, int N, int K, int num_shards, int rows_per_shard,
                            int first_shard, int* row_block, int* col_block, int capacity, int* slots);
 
+/* What the convolution entry points will do for a problem, without running it (needs no GPU; ctx may be
+ * NULL: planned for a 148-SM B200 with default knobs).  The reference's compiler decides tile shapes and
+ * data movement per kernel at compile time (tilinglinalg.cpp:38-146); this is that decision for conv2d. */
+typedef struct {
+  int form;                  /* 1 = patch form (one input patch + all taps' weights per CTA and cin chunk),
+                                0 = per-tap form, 2 = CUDA-core kernel (shape outside the tensor-core tiling) */
+  int tile_rows, tile_width; /* output pixels of one CTA: image rows x columns */
+  int patch_rows, patch_width; /* input rows x pixels one activation box brings (patch form: + kh-1, + kw-1) */
+  int m_rows_used;           /* of the 128 MMA rows (patch form computes and drops kw-1 columns per image row) */
+  int cout_tile, cin_chunk;  /* N of the MMA; K bytes per box */
+  int ctas, tma_boxes_per_cta, mmas_per_cta, stages, smem_bytes;
+} aiehlc_conv_plan;
+int aiehlc_plan_conv2d(aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, int kh, int kw, int pad,
+                       aiehlc_conv_plan* plan);
+
 /* ---- the same convolution for callers that must not allocate -----------------------------
  * (No counterpart in the reference: aiehlc has neither a convolution nor a device allocator.)
  * Meant for callers that cannot reach the device allocator when they call: a frozen memory pool, a

@@ -109,6 +109,28 @@ def test_tile_visiting_order_needs_no_gpu():
         plan_tile_order(1000, 520, 272, num_shards=4, rows_per_shard=100)
 
 
+def test_conv_planner_needs_no_gpu():
+    """Which form a convolution takes and how it is tiled is host logic."""
+    from aiehlc_b200.ops import plan_conv2d
+    p = plan_conv2d(1, 56, 56, 64, 64)                       # the benchmark convolution
+    assert p["form"] == 1 and (p["tile_rows"], p["tile_width"]) == (1, 56)
+    assert (p["patch_rows"], p["patch_width"], p["m_rows_used"]) == (3, 58, 58)
+    assert (p["cout_tile"], p["cin_chunk"], p["ctas"]) == (32, 64, 112)
+    assert (p["tma_boxes_per_cta"], p["mmas_per_cta"]) == (2, 18) and p["smem_bytes"] <= 227 * 1024
+    p = plan_conv2d(8, 56, 56, 64, 64)                       # enough tiles: two image rows per CTA, all channels
+    assert p["form"] == 1 and p["tile_rows"] == 2 and p["m_rows_used"] == 116 and p["cout_tile"] == 64
+    p = plan_conv2d(1, 6, 300, 128, 32, 5, 5, 2)             # wider than a tile: pieces of 128 - (kw - 1) pixels
+    assert p["form"] == 1 and p["tile_width"] == 124 and p["patch_width"] == 128 and p["patch_rows"] == 5
+    p = plan_conv2d(1, 8, 8, 256, 32, 1, 1, 0)               # 1 x 1: nothing to share between taps
+    assert p["form"] == 0 and p["tma_boxes_per_cta"] == 4 and p["mmas_per_cta"] == 8
+    p = plan_conv2d(4, 28, 28, 512, 512)                     # every tap's weights of a channel tile must fit
+    assert p["form"] == 1 and 9 * p["cout_tile"] * p["cin_chunk"] <= 96 * 1024 and p["tma_boxes_per_cta"] == 8
+    assert plan_conv2d(1, 8, 8, 24, 16)["form"] == 2         # 24 input channels: the CUDA-core kernel
+    from aiehlc_b200 import _capi
+    with pytest.raises(_capi.AiehlcError):
+        plan_conv2d(1, 8, 8, 64, 64, 3, 3, 0)                # not a same-size filter
+
+
 _WORKER = textwrap.dedent("""
     import os, sys
     import numpy as np, torch, torch.distributed as dist
