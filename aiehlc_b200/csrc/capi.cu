@@ -205,6 +205,12 @@ int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks) {
   return AIEHLC_OK;
 }
 
+int aiehlc_set_conv_hwio_direct(aiehlc_ctx* ctx, int on) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->conv_hwio_direct = on ? 1 : 0;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   ctx->conv_halo = on ? 1 : 0;

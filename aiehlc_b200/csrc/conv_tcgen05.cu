@@ -41,6 +41,12 @@ struct ConvParams {
   int halo;
   int row_w;                       // pixels per M row group: wt + kw - 1 (halo) or wt
   uint32_t w_block_bytes;          // halo: one tap's cout_tile x chunk block inside the weight box
+  // Patch form on weights as the caller holds them (HWIO: [tap][cin][cout], output channels contiguous):
+  // the weight box is {cout_tile, cin chunk, taps}, i.e. rows of cout_tile bytes, one per input channel,
+  // which is the tensor core's N-major ("MN-major") operand layout with a swizzle span of cout_tile bytes
+  // (32, 64 or 128).  No re-layout pass, no second launch.
+  int w_n_major;
+  uint32_t b_swizzle_code, b_sbo_bytes, b_kstep;  // B descriptor: swizzle, 8-row group pitch, start step (>>4) per MMA
   uint32_t swizzle_code, sbo_bytes;
   uint32_t tmem_cols;
   int8_t* y;
@@ -127,7 +133,8 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (p.halo) {
           // the whole patch (zero-filled outside the image: that is the padding) and every tap's weights
           tma_load_4d(smem_u32(sa), &tmap_x, fb, kb * p.chunk, ow0 - p.pad, oh0 - p.pad, img);
-          tma_load_3d(smem_u32(sb), &tmap_w, fb, kb * p.chunk, co0, 0);
+          if (p.w_n_major) tma_load_3d(smem_u32(sb), &tmap_w, fb, co0, kb * p.chunk, 0);   // {cout, cin, tap}
+          else tma_load_3d(smem_u32(sb), &tmap_w, fb, kb * p.chunk, co0, 0);                 // {cin, cout, tap}
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
           continue;
         }
@@ -145,7 +152,8 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc<KIND_I8>(kBlockM, p.cout_tile);
+      // bit 16: B is N-major (rows of output channels, one per input channel) instead of K-major
+      const uint32_t idesc = make_idesc<KIND_I8>(kBlockM, p.cout_tile) | (p.w_n_major ? (1u << 16) : 0u);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -169,7 +177,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           // (measured with 1 to 4 accumulators: no difference), so kh * kw * cin / 32 instructions
           // cost a CTA about 4 k cycles however the image is tiled.
           const uint64_t a0 = make_kmajor_desc(sa, p.sbo_bytes, p.swizzle_code);
-          uint64_t bd = make_kmajor_desc(sb, p.sbo_bytes, p.swizzle_code);
+          uint64_t bd = make_kmajor_desc(sb, p.b_sbo_bytes, p.b_swizzle_code);
           const uint32_t px_step = static_cast<uint32_t>(p.chunk) >> 4;
           const uint32_t row_step = px_step * p.row_w, w_step = p.w_block_bytes >> 4;
           const int ksteps = p.chunk / kUmmaKBytes;
@@ -179,7 +187,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             for (int fw = 0; fw < p.kw; ++fw) {
 #pragma unroll 4
               for (int k = 0; k < ksteps; ++k) {
-                umma_ss<KIND_I8, 1>(tmem_base, ad + 2 * k, bd + 2 * k, idesc, accum);
+                umma_ss<KIND_I8, 1>(tmem_base, ad + 2 * k, bd + k * p.b_kstep, idesc, accum);
                 accum = 1u;
               }
               ad += px_step;
@@ -313,6 +321,10 @@ int launch_conv_pack_weights(aiehlc_ctx* ctx, const int8_t* w, int8_t* packed, i
 
 int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, int8_t* y, int n, int h, int wd,
                          int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st);
+int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* weights, bool hwio, int8_t* y, int n, int h,
+                       int wd, int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st);
+bool conv_hwio_direct(const aiehlc_ctx* ctx, const int8_t* w, int n, int h, int wd, int cin, int cout, int kh, int kw,
+                      int pad);
 
 int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
                   int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
@@ -328,6 +340,9 @@ int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, 
     return AIEHLC_OK;
   }
 
+  // weights consumed as they are (one launch) where the patch form and the channel tile allow it
+  if (conv_hwio_direct(ctx, w, n, h, wd, cin, cout, kh, kw, pad))
+    return launch_conv_tensor(ctx, x, w, true, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec, st);
   const int taps = kh * kw;
   const size_t wbytes = static_cast<size_t>(taps) * cin * cout;
   if (ctx->pack_b.reserve(wbytes)) return AIEHLC_ERR_NOMEM;
@@ -453,11 +468,39 @@ int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, 
 // The implicit-GEMM kernel on weights that are already [tap][cout][cin].
 int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, int8_t* y, int n, int h, int wd,
                          int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
+  return launch_conv_tensor(ctx, x, packed, false, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec, st);
+}
+
+// Whether HWIO weights can feed the tensor cores directly: patch form, and a channel tile whose bytes are
+// a swizzle span (the N-major operand's row).
+bool conv_hwio_direct(const aiehlc_ctx* ctx, const int8_t* w, int n, int h, int wd, int cin, int cout, int kh, int kw,
+                      int pad) {
+  if (!ctx->conv_hwio_direct || reinterpret_cast<uintptr_t>(w) % 16 != 0) return false;
+  ConvParams p{};
+  p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
+  int n_tiles = 1;
+  configure_conv(ctx, p, &n_tiles);
+  return p.halo && (p.cout_tile == 32 || p.cout_tile == 64 || p.cout_tile == 128) && cout % p.cout_tile == 0;
+}
+
+// `weights`: [tap][cout][cin] (hwio == false) or the caller's HWIO array (hwio == true, only where
+// conv_hwio_direct() said yes).
+int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, bool hwio, int8_t* y, int n, int h,
+                       int wd, int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
   const int taps = kh * kw;
   ConvParams p{};
   p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
   int n_tiles = 1;
   configure_conv(ctx, p, &n_tiles);
+  p.w_n_major = hwio ? 1 : 0;
+  p.b_swizzle_code = p.swizzle_code;
+  p.b_sbo_bytes = p.sbo_bytes;
+  p.b_kstep = kUmmaKBytes >> 4;
+  if (hwio) {
+    p.b_swizzle_code = p.cout_tile == 128 ? 2u : (p.cout_tile == 64 ? 4u : 6u);
+    p.b_sbo_bytes = 8u * p.cout_tile;                         // 8 input channels (rows of cout_tile bytes)
+    p.b_kstep = static_cast<uint32_t>(kUmmaKBytes * p.cout_tile) >> 4;  // 32 input channels further on
+  }
   uint32_t cols = 32;
   while (cols < static_cast<uint32_t>(p.cout_tile)) cols <<= 1;
   p.tmem_cols = cols;
@@ -484,7 +527,19 @@ int launch_conv2d_packed(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed,
     const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(taps) * cout};
     const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(cin)};
     const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.cout_tile)};
-    if (p.halo) {
+    if (hwio) {
+      // the caller's HWIO weights as {cout, cin, taps}: one box holds cout_tile channels x a cin chunk x every tap,
+      // laid down as rows of cout_tile bytes (swizzle span = cout_tile)
+      const CUtensorMapSwizzle wsw = p.cout_tile == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                     : p.cout_tile == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+      const cuuint64_t w3dims[3] = {static_cast<cuuint64_t>(cout), static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(taps)};
+      const cuuint64_t w3strides[2] = {static_cast<cuuint64_t>(cout), static_cast<cuuint64_t>(cin) * cout};
+      const cuuint32_t w3box[3] = {static_cast<cuuint32_t>(p.cout_tile), static_cast<cuuint32_t>(p.chunk),
+                                   static_cast<cuuint32_t>(taps)};
+      r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(packed), w3dims, w3strides, w3box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, wsw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (p.halo) {
       // the packed weights as {cin, cout, taps}: one box holds a cin chunk of every tap for this channel tile
       const cuuint64_t w3dims[3] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cout), static_cast<cuuint64_t>(taps)};
       const cuuint64_t w3strides[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cin) * cout};
@@ -621,6 +676,7 @@ int launch_conv2d_static(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8
   p.stage_bytes = p.a_bytes + b_bytes;
   p.tx_bytes = static_cast<uint32_t>(p.chunk) * (p.wt * p.rows_per_tile + p.cout_tile);
   p.row_w = p.wt;  // one K block per tap and channel chunk (the form this entry point was written for)
+  p.b_swizzle_code = p.swizzle_code; p.b_sbo_bytes = p.sbo_bytes; p.b_kstep = kUmmaKBytes >> 4;
   int stages = (200 * 1024) / p.stage_bytes;
   if (stages > kConvMaxStages) stages = kConvMaxStages;
   if (stages > taps * p.chunks_per_tap) stages = taps * p.chunks_per_tap;

@@ -100,6 +100,9 @@ class Context:
     def set_host_blocks(self, blocks: int) -> None:
         _capi.check(self._lib.aiehlc_set_host_blocks(self._h, int(blocks)))
 
+    def set_conv_hwio_direct(self, on: bool) -> None:
+        _capi.check(self._lib.aiehlc_set_conv_hwio_direct(self._h, 1 if on else 0))
+
     def set_conv_halo(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_conv_halo(self._h, 1 if on else 0))
 

@@ -421,8 +421,8 @@ def main() -> int:
         gbs = alg_bytes / (per_launch_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"], "traffic": None,
-                    "note": f"latency-bound: {per_launch_ms * 1e3:.1f} us per conv (2 launches: weight re-layout + "
-                            f"implicit GEMM); peak {peaks['source']}"}
+                    "note": f"latency-bound: {per_launch_ms * 1e3:.1f} us per conv ({launches // max(K_steps, 1)} launch(es) "
+                            f"per step, HWIO weights as given); peak {peaks['source']}"}
     else:
         # burst peak for a short timed region, sustained (power-capped) peak once it runs for long
         sustained = elapsed_ms > 250.0

@@ -247,6 +247,11 @@ int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks);
  * activation box and one weight box per tap.  Filters whose taps do not fit in shared memory take the
  * second form whatever the setting. */
 int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on);
+/* Tuning knob for aiehlc_conv2d_i8_srs_dev / _host: 1 (default) = where the patch form applies and the
+ * output-channel tile is 32, 64 or 128 wide, the HWIO weights are fetched as they are (rows of output
+ * channels: the tensor core's N-major operand layout) and the convolution is one launch; 0 = weights
+ * are always re-laid to [tap][cout][cin] by a pre-pass launch first. */
+int aiehlc_set_conv_hwio_direct(aiehlc_ctx* ctx, int on);
 /* Tuning knob for aiehlc_gemm_i8_i32_scatter_dev: 1 (default) = results leave as add-reducing TMA tile
  * stores (32 rows x 128 bytes per store; needs N a multiple of 4 and 16-byte aligned shards, else the
  * other form is used), 0 = as per-row reduction instructions issued by the epilogue warps.  Measured

@@ -21,23 +21,43 @@ CONV_SHAPES = [(1, 56, 56, 64, 64),      # the benchmark configuration
                (1, 8, 8, 24, 16), (2, 5, 5, 3, 8), (1, 4, 4, 64, 10)]   # the last three take the direct kernel
 
 
-@pytest.mark.parametrize("halo", [True, False])
+@pytest.mark.parametrize("halo,direct", [(True, True), (True, False), (False, False)])
 @pytest.mark.parametrize("shape", CONV_SHAPES)
-def test_conv2d_matches_oracle(ctx, shape, halo):
-    """Both forms of the tensor-core kernel: the tile's input patch fetched once with all taps as views
-    into it (halo), and one activation box per tap."""
+def test_conv2d_matches_oracle(ctx, shape, halo, direct):
+    """The forms of the tensor-core kernel: the tile's input patch fetched once with all taps as views
+    into it, with the HWIO weights consumed as they are (one launch) or re-laid first (two), and one
+    activation box per tap."""
     n, h, w, cin, cout = shape
     x = synth.int8_uniform(4, (n, h, w, cin))
     wt = synth.int8_uniform(1004, (3, 3, cin, cout))
     sv = np.full(cout, 6, np.uint8)
     exp = O.conv2d_i8_srs(x, wt, sv, pad=1)
     ctx.set_conv_halo(halo)
+    ctx.set_conv_hwio_direct(direct)
     try:
         got = ctx.conv2d_i8_srs(_dev(x), _dev(wt), _dev(sv), pad=1).cpu().numpy()
         assert ctx.sync() == 0
     finally:
         ctx.set_conv_halo(True)
+        ctx.set_conv_hwio_direct(True)
     assert np.array_equal(got, exp)
+
+
+def test_conv2d_benchmark_shape_is_one_launch(ctx):
+    x = _dev(synth.int8_uniform(4, (1, 56, 56, 64)))
+    wt = _dev(synth.int8_uniform(1004, (3, 3, 64, 64)))
+    sv = _dev(np.full(64, 6, np.uint8))
+    ctx.conv2d_i8_srs(x, wt, sv, pad=1)
+    before = ctx.launch_count
+    ctx.conv2d_i8_srs(x, wt, sv, pad=1)
+    assert ctx.launch_count == before + 1            # no weight re-layout pass
+    ctx.set_conv_hwio_direct(False)
+    try:
+        before = ctx.launch_count
+        ctx.conv2d_i8_srs(x, wt, sv, pad=1)
+        assert ctx.launch_count == before + 2
+    finally:
+        ctx.set_conv_hwio_direct(True)
 
 
 @pytest.mark.parametrize("kh,kw,pad,shape", [(5, 5, 2, (1, 12, 12, 64, 32)), (7, 7, 3, (2, 20, 20, 32, 16)),
