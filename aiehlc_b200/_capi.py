@@ -83,7 +83,7 @@ class ConvPlan(C.Structure):
     """aiehlc_conv_plan of include/aiehlc_b200.h."""
     _fields_ = [(n, C.c_int) for n in ("form", "tile_rows", "tile_width", "patch_rows", "patch_width", "m_rows_used",
                                        "cout_tile", "cin_chunk", "ctas", "tma_boxes_per_cta", "mmas_per_cta", "stages",
-                                       "smem_bytes")]
+                                       "smem_bytes", "launches")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -440,6 +440,7 @@ int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, 
     long long g = (total + 255) / 256;
     if (g > ctx->sm_count * 16LL) g = ctx->sm_count * 16LL;
     pl.ctas = static_cast<int>(g);
+    pl.launches = 1;
     *out = pl;
     return AIEHLC_OK;
   }
@@ -461,6 +462,8 @@ int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, 
   pl.stages = p.stages;
   pl.smem_bytes = p.stages * p.stage_bytes + 512 + 1024;
   pl.m_rows_used = p.rows_per_tile * p.row_w;
+  pl.launches = (ctx->conv_hwio_direct && p.halo && (p.cout_tile == 32 || p.cout_tile == 64 || p.cout_tile == 128) &&
+                 cout % p.cout_tile == 0) ? 1 : 2;
   *out = pl;
   return AIEHLC_OK;
 }

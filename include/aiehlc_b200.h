@@ -188,6 +188,8 @@ typedef struct {
   int m_rows_used;           /* of the 128 MMA rows (patch form computes and drops kw-1 columns per image row) */
   int cout_tile, cin_chunk;  /* N of the MMA; K bytes per box */
   int ctas, tma_boxes_per_cta, mmas_per_cta, stages, smem_bytes;
+  int launches;              /* kernels per aiehlc_conv2d_i8_srs_dev call: 1, or 2 when the HWIO weights are re-laid first
+                                (16-byte aligned weights assumed) */
 } aiehlc_conv_plan;
 int aiehlc_plan_conv2d(aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, int kh, int kw, int pad,
                        aiehlc_conv_plan* plan);

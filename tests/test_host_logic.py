@@ -117,12 +117,13 @@ def test_conv_planner_needs_no_gpu():
     assert (p["patch_rows"], p["patch_width"], p["m_rows_used"]) == (3, 58, 58)
     assert (p["cout_tile"], p["cin_chunk"], p["ctas"]) == (32, 64, 112)
     assert (p["tma_boxes_per_cta"], p["mmas_per_cta"]) == (2, 18) and p["smem_bytes"] <= 227 * 1024
+    assert p["launches"] == 1                                # HWIO weights feed the tensor cores as they are
     p = plan_conv2d(8, 56, 56, 64, 64)                       # enough tiles: two image rows per CTA, all channels
     assert p["form"] == 1 and p["tile_rows"] == 2 and p["m_rows_used"] == 116 and p["cout_tile"] == 64
     p = plan_conv2d(1, 6, 300, 128, 32, 5, 5, 2)             # wider than a tile: pieces of 128 - (kw - 1) pixels
     assert p["form"] == 1 and p["tile_width"] == 124 and p["patch_width"] == 128 and p["patch_rows"] == 5
     p = plan_conv2d(1, 8, 8, 256, 32, 1, 1, 0)               # 1 x 1: nothing to share between taps
-    assert p["form"] == 0 and p["tma_boxes_per_cta"] == 4 and p["mmas_per_cta"] == 8
+    assert p["form"] == 0 and p["tma_boxes_per_cta"] == 4 and p["mmas_per_cta"] == 8 and p["launches"] == 2
     p = plan_conv2d(4, 28, 28, 512, 512)                     # every tap's weights of a channel tile must fit
     assert p["form"] == 1 and 9 * p["cout_tile"] * p["cin_chunk"] <= 96 * 1024 and p["tma_boxes_per_cta"] == 8
     assert plan_conv2d(1, 8, 8, 24, 16)["form"] == 2         # 24 input channels: the CUDA-core kernel
