@@ -311,11 +311,25 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
                                          srs_round<false>(r[j + 2], sh, hm1, bmask), srs_round<false>(r[j + 3], sh, hm1, bmask));
       }
     } else {
-      // per-column shifts: the 32 shift bytes of this chunk are the same for every row
+      // per-column shifts: the 32 shift bytes of this chunk are the same for every row; a whole chunk's
+      // bytes come with two 16-byte loads where the vector is aligned (col0 is a multiple of 32)
+      uint32_t sw[8];
+      if (ncols == 32 && (reinterpret_cast<uintptr_t>(p.shift_vec) & 15) == 0) {
+        const uint4 s0 = *reinterpret_cast<const uint4*>(p.shift_vec + col0);
+        const uint4 s1 = *reinterpret_cast<const uint4*>(p.shift_vec + col0 + 16);
+        sw[0] = s0.x; sw[1] = s0.y; sw[2] = s0.z; sw[3] = s0.w;
+        sw[4] = s1.x; sw[5] = s1.y; sw[6] = s1.z; sw[7] = s1.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sw[j] = 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) sw[j >> 2] |= static_cast<uint32_t>(p.shift_vec[col0 + j]) << (8 * (j & 3));
+      }
       int q[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        const int sh = j < ncols ? static_cast<int>(p.shift_vec[col0 + j]) : 0;
+        const int sh = static_cast<int>((sw[j >> 2] >> (8 * (j & 3))) & 0xFFu);
         const int hm1 = max(static_cast<int>((1u << sh) >> 1) - 1, 0);
         q[j] = srs_round<true>(r[j], sh, hm1, min(sh, 1));
       }
