@@ -174,8 +174,9 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           // One thread issues everything: the descriptors advance by additions only.  What remains is the
           // tensor core's own pace for such small MMAs: about 220 cycles per 128 x cout_tile x 32
           // instruction whatever cout_tile is, also when consecutive taps go to different accumulators
-          // (measured with 1 to 4 accumulators: no difference), so kh * kw * cin / 32 instructions
-          // cost a CTA about 4 k cycles however the image is tiled.
+          // (measured with 1 to 4 accumulators: no difference) and also with M = 64 instead of 128
+          // (measured: same issue time, slower epilogue because only 16 lanes per warp hold rows), so
+          // kh * kw * cin / 32 instructions cost a CTA about 3-4 k cycles however the image is tiled.
           const uint64_t a0 = make_kmajor_desc(sa, p.sbo_bytes, p.swizzle_code);
           uint64_t bd = make_kmajor_desc(sb, p.b_sbo_bytes, p.b_swizzle_code);
           const uint32_t px_step = static_cast<uint32_t>(p.chunk) >> 4;
