@@ -47,6 +47,11 @@ struct ConvParams {
   // (32, 64 or 128).  No re-layout pass, no second launch.
   int w_n_major;
   uint32_t b_swizzle_code, b_sbo_bytes, b_kstep;  // B descriptor: swizzle, 8-row group pitch, start step (>>4) per MMA
+  // Patch form with one cin chunk: the weights arrive as one box per FILTER ROW, each on its own barrier,
+  // so the first row's taps are multiplied while the other rows are still on their way (the TMA unit
+  // needs about 4 cycles per box row; the weight rows are most of a CTA's load time).
+  int w_split;
+  uint32_t w_row_bytes;            // bytes of one filter row's box: kw taps
   uint32_t swizzle_code, sbo_bytes;
   uint32_t tmem_cols;
   int8_t* y;
@@ -65,7 +70,8 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);
   uint64_t* empty_bar = full_bar + kConvMaxStages;
   uint64_t* tmem_full_bar = empty_bar + kConvMaxStages;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  uint64_t* w_row_bar = tmem_full_bar + 1;           // one per filter row (w_split)
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(w_row_bar + kConvMaxStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   uint8_t* shift_smem = reinterpret_cast<uint8_t*>(tmem_base_slot + 2);  // this CTA's cout_tile shift bytes (<= 256)
 
@@ -80,6 +86,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
     mbar_init(smem_u32(tmem_full_bar), 1);
+    for (int r = 0; r < kConvMaxStages; ++r) mbar_init(smem_u32(&w_row_bar[r]), 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -127,9 +134,23 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
         if (!ok) break;
         const uint32_t fb = smem_u32(&full_bar[stage]);
-        mbar_expect_tx(fb, p.tx_bytes);
         uint8_t* sa = smem + stage * p.stage_bytes;
         uint8_t* sb = sa + p.a_bytes;
+        if (p.halo && p.w_split) {
+          // one chunk, one stage: the patch on the stage's barrier, each filter row's weights on its own
+          mbar_expect_tx(fb, p.tx_bytes - p.kh * p.w_row_bytes);
+          tma_load_4d(smem_u32(sa), &tmap_x, fb, 0, ow0 - p.pad, oh0 - p.pad, img);
+          for (int fh = 0; fh < p.kh; ++fh) {
+            const uint32_t wb = smem_u32(&w_row_bar[fh]);
+            mbar_expect_tx(wb, p.w_row_bytes);
+            const uint32_t dst = smem_u32(sb + fh * p.w_row_bytes);
+            if (p.w_n_major) tma_load_3d(dst, &tmap_w, wb, co0, 0, fh * p.kw);
+            else tma_load_3d(dst, &tmap_w, wb, 0, co0, fh * p.kw);
+          }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          continue;
+        }
+        mbar_expect_tx(fb, p.tx_bytes);
         if (p.halo) {
           // the whole patch (zero-filled outside the image: that is the padding) and every tap's weights
           tma_load_4d(smem_u32(sa), &tmap_x, fb, kb * p.chunk, ow0 - p.pad, oh0 - p.pad, img);
@@ -184,6 +205,11 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           const int ksteps = p.chunk / kUmmaKBytes;
           uint32_t accum = kb != 0 ? 1u : 0u;
           for (int fh = 0; fh < p.kh; ++fh) {
+            if (p.w_split) {
+              ok = mbar_wait(smem_u32(&w_row_bar[fh]), 0, abort_flag, p.status, ST_TIMEOUT_FULL);
+              if (!ok) break;
+              tc_fence_after();
+            }
             uint64_t ad = a0 + fh * row_step;
             for (int fw = 0; fw < p.kw; ++fw) {
 #pragma unroll 4
@@ -201,6 +227,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           for (int k = 0; k < p.chunk / kUmmaKBytes; ++k)
             umma_ss<KIND_I8, 1>(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
         }
+        if (!ok) break;
         umma_commit(smem_u32(&empty_bar[stage]));
         if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
@@ -461,7 +488,7 @@ int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, 
   pl.tma_boxes_per_cta = p.halo ? 2 * p.chunks_per_tap : 2 * taps * p.chunks_per_tap;
   pl.mmas_per_cta = taps * p.chunks_per_tap * (p.chunk / kUmmaKBytes);
   pl.stages = p.stages;
-  pl.smem_bytes = p.stages * p.stage_bytes + 512 + 1024;
+  pl.smem_bytes = p.stages * p.stage_bytes + 1024 + 1024;
   pl.m_rows_used = p.rows_per_tile * p.row_w;
   pl.launches = (ctx->conv_hwio_direct && p.halo && (p.cout_tile == 32 || p.cout_tile == 64 || p.cout_tile == 128) &&
                  cout % p.cout_tile == 0) ? 1 : 2;
@@ -496,6 +523,8 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
   p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
   int n_tiles = 1;
   configure_conv(ctx, p, &n_tiles);
+  p.w_split = (p.halo && p.chunks_per_tap == 1 && kh <= kConvMaxStages && kh > 1 && ctx->conv_split_weights) ? 1 : 0;
+  p.w_row_bytes = static_cast<uint32_t>(kw) * p.w_block_bytes;
   p.w_n_major = hwio ? 1 : 0;
   p.b_swizzle_code = p.swizzle_code;
   p.b_sbo_bytes = p.sbo_bytes;
@@ -539,7 +568,7 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
       const cuuint64_t w3dims[3] = {static_cast<cuuint64_t>(cout), static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(taps)};
       const cuuint64_t w3strides[2] = {static_cast<cuuint64_t>(cout), static_cast<cuuint64_t>(cin) * cout};
       const cuuint32_t w3box[3] = {static_cast<cuuint32_t>(p.cout_tile), static_cast<cuuint32_t>(p.chunk),
-                                   static_cast<cuuint32_t>(taps)};
+                                   static_cast<cuuint32_t>(p.w_split ? kw : taps)};
       r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(packed), w3dims, w3strides, w3box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, wsw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -548,7 +577,7 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
       const cuuint64_t w3dims[3] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cout), static_cast<cuuint64_t>(taps)};
       const cuuint64_t w3strides[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cin) * cout};
       const cuuint32_t w3box[3] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.cout_tile),
-                                   static_cast<cuuint32_t>(taps)};
+                                   static_cast<cuuint32_t>(p.w_split ? kw : taps)};
       r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(packed), w3dims, w3strides, w3box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -560,7 +589,7 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
     if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
   }
 
-  const int smem_bytes = p.stages * p.stage_bytes + 512 + 1024;
+  const int smem_bytes = p.stages * p.stage_bytes + 1024 + 1024;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(conv2d_i8_kernel)];
   if (ks.smem_attr < smem_bytes) {
     AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
@@ -713,7 +742,7 @@ int launch_conv2d_static(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
 
-  const int smem_bytes = p.stages * p.stage_bytes + 512 + 1024;
+  const int smem_bytes = p.stages * p.stage_bytes + 1024 + 1024;
   AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid(n * p.tiles_h * p.tiles_w, n_tiles);
   cudaLaunchConfig_t cfg{};
