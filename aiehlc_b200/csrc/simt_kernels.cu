@@ -8,39 +8,77 @@ namespace aiehlc {
 // out[i*N+j] = sum_k A[i*K+k] * B[j*K+k] in uint32 wrap-around arithmetic, accumulator zeroed
 // per output -- the loop of example/perf/aieml_perf.cc:74-82 (kernel) and :199-231 (golden).
 // `in` = A (M*K words) followed by B (N*K words), as the examples pack their input window.
-constexpr int kMmTile = 32;
+// Register-tiled: a CTA of 256 threads owns a 64 x 64 tile of C and walks K in steps of 16; every thread
+// keeps a 4 x 4 block of outputs, so one pair of 16-byte shared-memory reads feeds 16 multiply-adds.
+constexpr int kMmTile = 64;
+constexpr int kMmK = 16;
 __global__ void __launch_bounds__(256) mm_i32_kernel(const uint32_t* __restrict__ in,
                                                      uint32_t* __restrict__ out, int M, int N, int K) {
-  __shared__ uint32_t sa[kMmTile][kMmTile + 1];
-  __shared__ uint32_t sb[kMmTile][kMmTile + 1];
+  // [k][row]: the 4 rows (or columns) a thread needs are contiguous; +4 words keeps the 16-byte alignment
+  // and spreads the transposing stores over the banks
+  __shared__ __align__(16) uint32_t sa[kMmK][kMmTile + 4];
+  __shared__ __align__(16) uint32_t sb[kMmK][kMmTile + 4];
   const uint32_t* A = in;
   const uint32_t* B = in + static_cast<size_t>(M) * K;
-  const int tx = threadIdx.x & 31;   // output column within the tile
-  const int ty = threadIdx.x >> 5;   // 8 row groups, 4 rows each
-  const int row0 = blockIdx.y * kMmTile;
-  const int col0 = blockIdx.x * kMmTile;
-  uint32_t acc[4] = {0, 0, 0, 0};
-  for (int k0 = 0; k0 < K; k0 += kMmTile) {
+  const int t = threadIdx.x;
+  const int tx = t & 15, ty = t >> 4;          // 16 x 16 threads, 4 x 4 outputs each
+  const int lrow = t >> 2, lk = (t & 3) * 4;   // loader: tile row 0..63, k offset 0/4/8/12
+  const int row0 = blockIdx.y * kMmTile, col0 = blockIdx.x * kMmTile;
+  const bool vec = (K % 4 == 0) && (reinterpret_cast<uintptr_t>(in) % 16 == 0) &&
+                   ((static_cast<size_t>(M) * K) % 4 == 0);
+  uint32_t acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += kMmK) {
+    uint32_t av[4] = {0, 0, 0, 0}, bv[4] = {0, 0, 0, 0};
+    const int k = k0 + lk;
+    if (row0 + lrow < M) {
+      const uint32_t* src = A + static_cast<size_t>(row0 + lrow) * K + k;
+      if (vec && k + 3 < K) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src);
+        av[0] = v.x; av[1] = v.y; av[2] = v.z; av[3] = v.w;
+      } else {
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int lr = ty * 4 + r;
-      const int k = k0 + tx;
-      sa[lr][tx] = (row0 + lr < M && k < K) ? A[static_cast<size_t>(row0 + lr) * K + k] : 0u;
-      sb[lr][tx] = (col0 + lr < N && k < K) ? B[static_cast<size_t>(col0 + lr) * K + k] : 0u;
+        for (int i = 0; i < 4; ++i)
+          if (k + i < K) av[i] = src[i];
+      }
+    }
+    if (col0 + lrow < N) {
+      const uint32_t* src = B + static_cast<size_t>(col0 + lrow) * K + k;
+      if (vec && k + 3 < K) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src);
+        bv[0] = v.x; bv[1] = v.y; bv[2] = v.z; bv[3] = v.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (k + i < K) bv[i] = src[i];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      sa[lk + i][lrow] = av[i];
+      sb[lk + i][lrow] = bv[i];
     }
     __syncthreads();
 #pragma unroll
-    for (int k = 0; k < kMmTile; ++k) {
-      const uint32_t b = sb[tx][k];
+    for (int kk = 0; kk < kMmK; ++kk) {
+      const uint4 a = *reinterpret_cast<const uint4*>(&sa[kk][ty * 4]);
+      const uint4 b = *reinterpret_cast<const uint4*>(&sb[kk][tx * 4]);
+      const uint32_t ar[4] = {a.x, a.y, a.z, a.w}, br[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-      for (int r = 0; r < 4; ++r) acc[r] += sa[ty * 4 + r][k] * b;
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] += ar[r] * br[c];   // uint32: wraps like the reference's loop
     }
     __syncthreads();
   }
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int row = row0 + ty * 4 + r, col = col0 + tx;
-    if (row < M && col < N) out[static_cast<size_t>(row) * N + col] = acc[r];
+    const int row = row0 + ty * 4 + r;
+    if (row >= M) continue;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = col0 + tx * 4 + c;
+      if (col < N) out[static_cast<size_t>(row) * N + col] = acc[r][c];
+    }
   }
 }
 
