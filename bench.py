@@ -44,8 +44,8 @@ WORKLOADS = {
     "cfg5": dict(M=65536, N=8192, K=8192, kind="i8_i32", scaling="strong",
                  desc="int8 GEMM 65536x8192x8192 -> int32, rows of A/C sharded over the GPUs"),
     "cfg5_splitk": dict(M=65536, N=8192, K=8192, kind="i8_i32_splitk", splitk=8, scaling="strong",
-                        desc="int8 GEMM 65536x8192x8192 -> int32, split-K 8 over the GPUs, int32 partials "
-                             "summed by NCCL reduce-scatter"),
+                        desc="int8 GEMM 65536x8192x8192 -> int32, split-K 8 over the GPUs, int32 partial sums "
+                             "exchanged between the GPUs (how: splitk_exchange)"),
 }
 
 
