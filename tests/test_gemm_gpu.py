@@ -356,3 +356,35 @@ def test_cfg2_full_size_properties_and_sampled_rows(ctx):
     assert torch.equal(neg, -ctx.gemm_i8_i32(dA.clamp(min=-127).contiguous(), dB))
     # (5) cascade over 4 launches equals the single launch
     assert torch.equal(ctx.gemm_i8_srs_cascade(dA, dB, 4, shift=8), c8)
+
+
+def test_cfg5_full_size_sampled_rows_and_checksums(ctx):
+    """int8 65536 x 8192 x 8192 -> int32 (2.1 GB of results) at full size: sampled rows bit-exact against the
+    oracle, every row through the checksum of checksums, and the row-sharded form (8 shards of 8192 rows,
+    two K slices added into zeroed shards) equal to the single launch."""
+    M, N, K = 65536, 8192, 8192
+    dA = synth.int8_uniform_torch(5, (M, K), DEV)
+    dB = synth.int8_uniform_torch(1005, (N, K), DEV)
+    c32 = ctx.gemm_i8_i32(dA, dB)
+    assert ctx.sync() == 0
+    rows = np.r_[0:4, 8190:8194, 40000:40004, 65532:65536]            # across shard and tile boundaries
+    B = synth.int8_uniform(1005, (N, K))
+    A_rows = np.concatenate([synth.int8_uniform(5, (1, K), start=int(r) * K) for r in rows])
+    assert np.array_equal(c32[torch.from_numpy(rows).to(DEV)].cpu().numpy(), O.gemm_i8_i32(A_rows, B))
+    # sum_j C[i][j] == A[i] . (sum_j B[j]) for every row i: |values| < 2^53, exact in float64
+    colsum = dB.to(torch.float64).sum(dim=0)
+    want = torch.empty(M, dtype=torch.float64, device=DEV)
+    for r0 in range(0, M, 8192):                                       # row blocks keep the temporaries small
+        want[r0:r0 + 8192] = dA[r0:r0 + 8192].to(torch.float64) @ colsum
+    got = torch.empty(M, dtype=torch.float64, device=DEV)
+    for r0 in range(0, M, 8192):
+        got[r0:r0 + 8192] = c32[r0:r0 + 8192].to(torch.float64).sum(dim=1)
+    assert torch.equal(got, want)
+    # the split-K exchange's form: two K slices added into 8 zeroed row shards
+    shards = [torch.zeros((8192, N), dtype=torch.int32, device=DEV) for _ in range(8)]
+    half = K // 2
+    ctx.gemm_i8_i32_scatter(dA[:, :half].contiguous(), dB[:, :half].contiguous(), shards, 8192, first_shard=1)
+    ctx.gemm_i8_i32_scatter(dA[:, half:].contiguous(), dB[:, half:].contiguous(), shards, 8192, first_shard=6)
+    assert ctx.sync() == 0
+    for g in range(8):
+        assert torch.equal(shards[g], c32[g * 8192:(g + 1) * 8192]), g
