@@ -179,6 +179,101 @@ def test_int8_gemm_srs_through_the_runtime_matches_oracle(xaie):
     assert np.array_equal(peek, got.ravel()[:64])
 
 
+class ConvArgs(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n", "h", "w", "cin", "cout", "kh", "kw", "pad")]
+
+
+class SrsArgs(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("rows", "cols", "shift", "has_shift_vec")]
+
+
+def _run_tile(lib, dev, ri, tile, shim, mem_in, in_bytes, out_bytes):
+    assert lib.XAie_MoveDataExternal2Aie(ri, shim, mem_in, in_bytes, 0x1000, tile) == XAIE_OK, lib.XAie_LastError()
+    assert lib.XAie_Run(ri, 1) == XAIE_OK, lib.XAie_LastError()
+    assert lib.XAie_CoreWaitForDone(C.byref(dev), tile, 5_000_000) == XAIE_OK, lib.XAie_LastError()
+    mem_out = lib.XAie_MemAllocate(C.byref(dev), out_bytes, 0)
+    assert lib.XAie_MoveDataAie2External(ri, tile, 0x6000, out_bytes, mem_out, shim) == XAIE_OK, lib.XAie_LastError()
+    return mem_out
+
+
+def test_conv_bf16_and_gemm_to_srs_chain_through_the_runtime(xaie):
+    """The other library kernels behind XAie_LoadElfMem: the convolution (input window = x | w | shift bytes),
+    the bf16 GEMM, and an int8 GEMM whose int32 result moves tile to tile into the srs kernel (the two-stage
+    chain of example/multi/multi_tile.cpp:105-145 with real kernels)."""
+    lib, dev = xaie
+    lib.aiehlc_conv_offset_w.restype = C.c_uint64
+    lib.aiehlc_conv_offset_w.argtypes = [C.c_void_p]
+    lib.aiehlc_conv_offset_shift.restype = C.c_uint64
+    lib.aiehlc_conv_offset_shift.argtypes = [C.c_void_p]
+    ri = lib.XAie_InitRoutingHandler(C.byref(dev))
+    shim = Loc(0, 2)
+    # ---- convolution 1 x 14 x 14 x 64 -> 64, 3 x 3, per-channel shifts
+    t_conv = Loc(3, 5)
+    x = synth.int8_uniform(4, (1, 14, 14, 64))
+    w = synth.int8_uniform(1004, (3, 3, 64, 64))
+    sv = (np.arange(64) % 9).astype(np.uint8)
+    ca = ConvArgs(1, 14, 14, 64, 64, 3, 3, 1)
+    assert lib.XAie_LoadElfMem(C.byref(dev), t_conv, _kernel(lib, "aiehlc_k_conv2d_i8_srs")) == XAIE_OK
+    assert lib.XAie_KernelSetArgs(C.byref(dev), t_conv, C.byref(ca), C.sizeof(ca)) == XAIE_OK
+    assert lib.XAie_Route(ri, None, shim, t_conv) == XAIE_OK and lib.XAie_Route(ri, None, t_conv, shim) == XAIE_OK
+    ow, osv = lib.aiehlc_conv_offset_w(C.byref(ca)), lib.aiehlc_conv_offset_shift(C.byref(ca))
+    win = osv + 64
+    mem = lib.XAie_MemAllocate(C.byref(dev), win, 0)
+    buf = _host_array(lib, mem, win, np.uint8)
+    buf[:x.size] = x.view(np.uint8).ravel()
+    buf[ow:ow + w.size] = w.view(np.uint8).ravel()
+    buf[osv:osv + 64] = sv
+    out = _run_tile(lib, dev, ri, t_conv, shim, mem, win, x.size)
+    got = _host_array(lib, out, x.size, np.int8).reshape(1, 14, 14, 64)
+    assert np.array_equal(got, O.conv2d_i8_srs(x, w, sv, pad=1))
+    # ---- bf16 GEMM 96 x 80 x 64
+    t_bf = Loc(3, 6)
+    M, N, K = 96, 80, 64
+    Ab, Bb = synth.normal_bf16_bits(3, (M, K)), synth.normal_bf16_bits(1003, (N, K))
+    ga = GemmArgs(M, N, K, 0, 0, 1, 0, 0)
+    assert lib.XAie_LoadElfMem(C.byref(dev), t_bf, _kernel(lib, "aiehlc_k_gemm_bf16")) == XAIE_OK
+    assert lib.XAie_KernelSetArgs(C.byref(dev), t_bf, C.byref(ga), C.sizeof(ga)) == XAIE_OK
+    assert lib.XAie_Route(ri, None, shim, t_bf) == XAIE_OK and lib.XAie_Route(ri, None, t_bf, shim) == XAIE_OK
+    off_b = lib.aiehlc_window_offset_b(C.byref(ga), 2)
+    win = off_b + N * K * 2
+    mem = lib.XAie_MemAllocate(C.byref(dev), win, 0)
+    buf = _host_array(lib, mem, win, np.uint8)
+    buf[:M * K * 2] = Ab.view(np.uint8).ravel()
+    buf[off_b:off_b + N * K * 2] = Bb.view(np.uint8).ravel()
+    out = _run_tile(lib, dev, ri, t_bf, shim, mem, win, M * N * 2)
+    got = synth.bf16_bits_to_f32(_host_array(lib, out, M * N * 2, np.uint16).reshape(M, N)).astype(np.float64)
+    ref = O.gemm_bf16(Ab, Bb).astype(np.float64)
+    assert float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0))) <= 1e-2          # the bf16 tolerance
+    # ---- int8 GEMM -> int32 on one tile, result moved tile to tile into the srs kernel on the next
+    t_mm, t_srs = Loc(4, 5), Loc(5, 5)
+    M, N, K = 130, 72, 256
+    A, B = synth.int8_uniform(7, (M, K)), synth.int8_uniform(1007, (N, K))
+    g2 = GemmArgs(M, N, K, 0, 0, 1, 0, 0)
+    sa = SrsArgs(M, N, 9, 0)
+    assert lib.XAie_LoadElfMem(C.byref(dev), t_mm, _kernel(lib, "aiehlc_k_gemm_i8_i32")) == XAIE_OK
+    assert lib.XAie_KernelSetArgs(C.byref(dev), t_mm, C.byref(g2), C.sizeof(g2)) == XAIE_OK
+    assert lib.XAie_LoadElfMem(C.byref(dev), t_srs, _kernel(lib, "aiehlc_k_srs_i32_i8")) == XAIE_OK
+    assert lib.XAie_KernelSetArgs(C.byref(dev), t_srs, C.byref(sa), C.sizeof(sa)) == XAIE_OK
+    for a, b in ((shim, t_mm), (t_mm, t_srs), (t_srs, shim)):
+        assert lib.XAie_Route(ri, None, a, b) == XAIE_OK
+    off_b = lib.aiehlc_window_offset_b(C.byref(g2), 1)
+    win = off_b + N * K
+    mem = lib.XAie_MemAllocate(C.byref(dev), win, 0)
+    buf = _host_array(lib, mem, win, np.int8)
+    buf[:M * K] = A.ravel()
+    buf[off_b:off_b + N * K] = B.ravel()
+    assert lib.XAie_MoveDataExternal2Aie(ri, shim, mem, win, 0x1000, t_mm) == XAIE_OK
+    assert lib.XAie_Run(ri, 1) == XAIE_OK, lib.XAie_LastError()                 # only the tile that received data runs
+    assert lib.XAie_CoreWaitForDone(C.byref(dev), t_mm, 5_000_000) == XAIE_OK, lib.XAie_LastError()
+    assert lib.XAie_MoveData(ri, t_mm, C.c_void_p(0x6000), M * N * 4, C.c_void_p(0x1000), t_srs) == XAIE_OK, lib.XAie_LastError()
+    assert lib.XAie_Run(ri, 1) == XAIE_OK, lib.XAie_LastError()
+    assert lib.XAie_CoreWaitForDone(C.byref(dev), t_srs, 5_000_000) == XAIE_OK, lib.XAie_LastError()
+    out = lib.XAie_MemAllocate(C.byref(dev), M * N, 0)
+    assert lib.XAie_MoveDataAie2External(ri, t_srs, 0x6000, M * N, out, shim) == XAIE_OK
+    got = _host_array(lib, out, M * N, np.int8).reshape(M, N)
+    assert np.array_equal(got, O.gemm_i8_srs(A, B, shift=9))
+
+
 def test_failure_paths_return_codes(xaie):
     lib, dev = xaie
     tile, shim, other = Loc(4, 4), Loc(0, 2), Loc(5, 5)
