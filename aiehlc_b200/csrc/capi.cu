@@ -126,6 +126,7 @@ int aiehlc_destroy(aiehlc_ctx* ctx) {
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   ctx->buf_a.release(); ctx->buf_b.release(); ctx->buf_c.release(); ctx->buf_aux.release();
   ctx->pack_a.release(); ctx->pack_b.release();
+  ctx->limb_a.release(); ctx->limb_b.release();
   ctx->sk_scratch.release(); ctx->sk_flags.release(); ctx->shard_maps.release();
   delete ctx;
   return AIEHLC_OK;
@@ -205,6 +206,12 @@ int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks) {
   return AIEHLC_OK;
 }
 
+int aiehlc_set_mm_i32_tensor(aiehlc_ctx* ctx, int on) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->mm_i32_tensor = on ? 1 : 0;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_conv_hwio_direct(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   ctx->conv_hwio_direct = on ? 1 : 0;
@@ -274,6 +281,7 @@ int aiehlc_mm_i32_dev(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, i
   if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "mm_i32: negative size");
   if (M == 0 || N == 0) return AIEHLC_OK;
   if (!in || !out) return fail(AIEHLC_ERR_INVALID, "mm_i32: null pointer");
+  if (mm_i32_tensor_ok(ctx, M, N, K)) return launch_mm_i32_tensor(ctx, in, out, M, N, K, pick_stream(ctx, stream));
   return launch_mm_i32(ctx, in, out, M, N, K, pick_stream(ctx, stream));
 }
 

@@ -84,6 +84,8 @@ struct aiehlc_ctx {
   std::unordered_map<const void*, aiehlc::KernelSetup> kernel_setup;
   // staging for *_host entry points and for operands that TMA cannot address directly
   aiehlc::DevBuf buf_a, buf_b, buf_c, buf_aux, pack_a, pack_b;
+  aiehlc::DevBuf limb_a, limb_b;        // byte planes of int32 operands (mm_i32 on the tensor cores)
+  int mm_i32_tensor = 1;                // large int32 products run as int8 limb GEMMs on the tensor cores
   aiehlc::DevBuf sk_scratch, sk_flags;  // partial sums and deposit counters of split tail tiles
   int shard_tile_stores = 1;            // sharded output leaves as add-reducing TMA tile stores (else row reductions)
   aiehlc::DevBuf shard_maps;            // tensor maps of a row-sharded output, as the kernels read them
@@ -106,6 +108,7 @@ struct GemmCall {
   const int32_t* acc_in; long long ld_acc;
   const uint8_t* shift_vec; int shift;
   int group_m;                  // filled in from the plan
+  int unsigned_ab = 0, out_shift = 0;   // see GemmParams
   // row-sharded add-reduction output (see GemmParams::shard); C is unused when num_shards > 0
   int32_t* const* shards = nullptr;
   const CUtensorMap* shard_maps = nullptr;   // optional: the shards as tensors for add-reducing tile stores
@@ -123,6 +126,8 @@ void narrow_tail(int tiles, int slots, int tile_n, int enabled, int* first, int*
 
 // SIMT helpers (simt_kernels.cu)
 int launch_mm_i32(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K, cudaStream_t st);
+int launch_mm_i32_tensor(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K, cudaStream_t st);
+bool mm_i32_tensor_ok(const aiehlc_ctx* ctx, int M, int N, int K);
 int launch_srs(aiehlc_ctx* ctx, const int32_t* in, int8_t* out, long long rows, long long cols, int shift,
                const uint8_t* shift_vec, cudaStream_t st);
 int launch_fill_i32(aiehlc_ctx* ctx, int32_t* out, long long n, int value, cudaStream_t st);

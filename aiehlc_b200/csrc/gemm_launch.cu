@@ -239,6 +239,7 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.num_n_blocks = (c.N + kBN - 1) / kBN;
   p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
   p.group_m = c.group_m;
+  p.unsigned_ab = c.unsigned_ab; p.out_shift = c.out_shift;
   // 32 consecutive outputs per thread are written with 16-byte stores when every row start is aligned.
   bool vec = (reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0);
   p.vec_ok = vec ? 1 : 0;
@@ -314,6 +315,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.num_n_blocks = (c.N + kBN - 1) / kBN;
   p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
   p.group_m = c.group_m;
+  p.unsigned_ab = c.unsigned_ab; p.out_shift = c.out_shift;
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0)) ? 1 : 0;
   p.tma_store = (p.vec_ok && (ctx->tma_store == 2 || (ctx->tma_store == 1 && kEpi != EPI_I8_SRS))) ? 1 : 0;
   CUtensorMap mc = ma;  // unused unless tma_store

@@ -83,6 +83,9 @@ struct GemmParams {
   // The other form of tail balancing: tiles >= nt_first_tile are cut into nt_parts column ranges
   // (narrower MMAs, no exchange between the ranges).  nt_parts == 1: off.  Never together with sk_parts > 1.
   int nt_first_tile, nt_parts;
+  // int32 products on the int8 tensor cores (see launch_mm_i32_tensor): operands are unsigned bytes and
+  // the int32 result is shifted left (wrapping) before it is stored or added.
+  int unsigned_ab, out_shift;
   long long* trace;        // measurement aid: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
   int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling);
                            // test aid: 3 = the producer neither loads nor signals, so every consumer wait
@@ -259,6 +262,10 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
                                             StoreCtx& sc) {
   const int ncols = min(32, p.N - col0);
   if constexpr (kEpi == EPI_I32 || kEpi == EPI_I32_ACC) {
+    if (p.out_shift) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] <<= p.out_shift;
+    }
     if (kEpi == EPI_I32_ACC && p.num_shards > 0 && p.shard_maps == nullptr) {
       shard_add_chunk(p, sc, r, col0);
       return;
@@ -496,7 +503,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc<kKind>(kBlockM, kBN);
+      // bits 7 and 10: A and B are signed bytes (cleared: unsigned)
+      const uint32_t idesc = make_idesc<kKind>(kBlockM, kBN) & ~(p.unsigned_ab ? ((1u << 7) | (1u << 10)) : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;

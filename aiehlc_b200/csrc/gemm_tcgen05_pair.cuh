@@ -239,7 +239,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tc_fence_after();
         if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        const uint32_t idesc = make_idesc<kKind>(kPairM, kBN / w.n_parts);
+        const uint32_t idesc = make_idesc<kKind>(kPairM, kBN / w.n_parts) &
+                               ~(p.unsigned_ab ? ((1u << 7) | (1u << 10)) : 0u);  // bits 7, 10: signed A, B
         const uint32_t b_block = S::kBBlock / w.n_parts;  // the K blocks of a box lie back to back
         for (int kb = w.kb0; kb < w.kb1; kb += kKPer) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);

@@ -38,6 +38,28 @@ def test_mm_i32_wraparound(ctx, shape):
     assert np.array_equal(ctx.mm_i32_host(inp, M, N, K), O.mm_i32(inp, M, N, K))
 
 
+@pytest.mark.parametrize("shape", [(512, 384, 1000), (300, 200, 4100), (1024, 1024, 1024), (130, 70, 8256), (256, 64, 64)])
+def test_mm_i32_on_the_tensor_cores(ctx, shape):
+    """Large int32 products run as int8 limb GEMMs on the tensor cores: full-range random words, and the
+    all-ones words that make every limb product as large as it can get (K = 8256 is the limit up to which
+    no partial sum can reach 2^31), against the oracle and against the CUDA-core kernel."""
+    M, N, K = shape
+    rng = np.random.default_rng(11)
+    inp = rng.integers(-2**31, 2**31 - 1, size=(M + N) * K, dtype=np.int64).astype(np.int32)
+    d_in = _dev(inp)
+    got = ctx.mm_i32(d_in, M, N, K)
+    assert np.array_equal(got.cpu().numpy(), O.mm_i32(inp, M, N, K))
+    ones = _dev(np.full((M + N) * K, -1, dtype=np.int32))                 # 0xFFFFFFFF everywhere
+    got_ones = ctx.mm_i32(ones, M, N, K)
+    assert bool((got_ones == K).all())                                    # (-1) * (-1) summed K times
+    ctx.set_mm_i32_tensor(False)
+    try:
+        assert torch.equal(ctx.mm_i32(d_in, M, N, K), got)
+    finally:
+        ctx.set_mm_i32_tensor(True)
+    assert ctx.sync() == 0
+
+
 # ---------------------------------------------------------------- int8 -> int32
 SHAPES = [(64, 64, 64),            # the single-tile configuration
           (128, 256, 128), (256, 512, 1024), (1024, 1024, 1024),
