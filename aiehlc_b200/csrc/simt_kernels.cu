@@ -132,18 +132,19 @@ int launch_mm_i32(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N
 //   a * b mod 2^32 = sum_{s=0..3} 2^(8s) * sum_{t=0..s} a_t * b_(s-t)        (terms with t + u > 3 vanish).
 // For every s the inner sums over t AND over k are one int8 GEMM with K' = (s+1) * K: the operand of group
 // s holds, side by side, limbs 0..s of A (for B: limbs s..0).  A group's sums stay below 2^31 while
-// (s+1) * K * 255^2 < 2^31, i.e. K <= 8256, so nothing depends on how the accumulator overflows.  Four
-// launches: group 0 stores, groups 1..3 add their result shifted left by 8 s (wrapping), which is exactly
-// the reference kernel's uint32 arithmetic (example/perf/aieml_perf.cc:74-82).
+// (s+1) * K * 255^2 < 2^31, i.e. K <= 8256, so nothing depends on how the accumulator overflows; longer K
+// goes in ranges of 8192 columns.  Four launches per range: group 0 stores (adds, after the first range),
+// groups 1..3 add their result shifted left by 8 s (wrapping), which is exactly the reference kernel's
+// uint32 arithmetic (example/perf/aieml_perf.cc:74-82).
 // K-blocks of Kp bytes before group s in a row set: 0, 1, 3, 6
 __host__ __device__ constexpr int limb_group_blocks(int s) { return s * (s + 1) / 2; }
-constexpr int kMmI32TensorMaxK = 8256;
 
 // src: rows x K int32.  dst: for s = 0..3 a matrix [rows][(s+1) * Kp] of bytes at offset
 // rows * Kp * limb_group_blocks(s); block t of group s holds limb t (reversed: limb s - t).  Kp = K rounded
 // up to 16; the padding columns are written as zero.
+// `src` rows have a pitch of `ld` words; the K columns start at the pointer given.
 __global__ void limb_split_kernel(const uint32_t* __restrict__ src, uint8_t* __restrict__ dst, long long rows, int K,
-                                  int Kp, int reversed) {
+                                  long long ld, int Kp, int reversed) {
   const long long total = rows * (Kp / 4);
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -151,7 +152,7 @@ __global__ void limb_split_kernel(const uint32_t* __restrict__ src, uint8_t* __r
     const int k = static_cast<int>(i - row * (Kp / 4)) * 4;
     uint32_t v[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) v[e] = (k + e < K) ? src[row * K + k + e] : 0u;
+    for (int e = 0; e < 4; ++e) v[e] = (k + e < K) ? src[row * ld + k + e] : 0u;
 #pragma unroll
     for (int limb = 0; limb < 4; ++limb) {
       const uint32_t word = ((v[0] >> (8 * limb)) & 0xFFu) | (((v[1] >> (8 * limb)) & 0xFFu) << 8) |
@@ -167,35 +168,41 @@ __global__ void limb_split_kernel(const uint32_t* __restrict__ src, uint8_t* __r
 }
 
 bool mm_i32_tensor_ok(const aiehlc_ctx* ctx, int M, int N, int K) {
-  return ctx->mm_i32_tensor && K >= 64 && K <= kMmI32TensorMaxK && M >= 128 && N >= 64 &&
-         static_cast<long long>(M) * N * K >= (1LL << 24);
+  return ctx->mm_i32_tensor && K >= 64 && M >= 128 && N >= 64 && static_cast<long long>(M) * N * K >= (1LL << 24);
 }
 
 int launch_mm_i32_tensor(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N, int K, cudaStream_t st) {
-  const int Kp = (K + 15) / 16 * 16;
-  if (ctx->limb_a.reserve(static_cast<size_t>(M) * Kp * 10) || ctx->limb_b.reserve(static_cast<size_t>(N) * Kp * 10))
+  // K ranges of at most 8192 columns (a multiple of 16 below the 8256 limit), one after the other: the first
+  // range's group 0 stores, everything else adds
+  const int kc_max = 8192;
+  const int kp_max = ((K < kc_max ? K : kc_max) + 15) / 16 * 16;
+  if (ctx->limb_a.reserve(static_cast<size_t>(M) * kp_max * 10) || ctx->limb_b.reserve(static_cast<size_t>(N) * kp_max * 10))
     return AIEHLC_ERR_NOMEM;
   const uint32_t* A = reinterpret_cast<const uint32_t*>(in);
   const uint32_t* B = A + static_cast<size_t>(M) * K;
   uint8_t* la = static_cast<uint8_t*>(ctx->limb_a.ptr);
   uint8_t* lb = static_cast<uint8_t*>(ctx->limb_b.ptr);
-  limb_split_kernel<<<grid_for(ctx, static_cast<long long>(M) * (Kp / 4), 256), 256, 0, st>>>(A, la, M, K, Kp, 0);
-  AIEHLC_CUDA(cudaGetLastError());
-  limb_split_kernel<<<grid_for(ctx, static_cast<long long>(N) * (Kp / 4), 256), 256, 0, st>>>(B, lb, N, K, Kp, 1);
-  AIEHLC_CUDA(cudaGetLastError());
-  ctx->launches += 2;
-  for (int s = 0; s < 4; ++s) {
-    GemmCall c{};
-    c.kind = 0;                      // int8 operands
-    c.epi = s == 0 ? 0 : 1;          // store, then add
-    c.A = la + static_cast<size_t>(M) * Kp * limb_group_blocks(s);
-    c.B = lb + static_cast<size_t>(N) * Kp * limb_group_blocks(s);
-    c.C = out;
-    c.M = M; c.N = N; c.K = (s + 1) * Kp;
-    c.lda = c.K; c.ldb = c.K; c.ldc = N;
-    c.unsigned_ab = 1;
-    c.out_shift = 8 * s;
-    if (int rc = launch_gemm(ctx, c, st)) return rc;
+  for (int k0 = 0; k0 < K; k0 += kc_max) {
+    const int kc = K - k0 < kc_max ? K - k0 : kc_max;
+    const int Kp = (kc + 15) / 16 * 16;
+    limb_split_kernel<<<grid_for(ctx, static_cast<long long>(M) * (Kp / 4), 256), 256, 0, st>>>(A + k0, la, M, kc, K, Kp, 0);
+    AIEHLC_CUDA(cudaGetLastError());
+    limb_split_kernel<<<grid_for(ctx, static_cast<long long>(N) * (Kp / 4), 256), 256, 0, st>>>(B + k0, lb, N, kc, K, Kp, 1);
+    AIEHLC_CUDA(cudaGetLastError());
+    ctx->launches += 2;
+    for (int s = 0; s < 4; ++s) {
+      GemmCall c{};
+      c.kind = 0;                                  // int8 operands
+      c.epi = (s == 0 && k0 == 0) ? 0 : 1;         // store once, then add
+      c.A = la + static_cast<size_t>(M) * Kp * limb_group_blocks(s);
+      c.B = lb + static_cast<size_t>(N) * Kp * limb_group_blocks(s);
+      c.C = out;
+      c.M = M; c.N = N; c.K = (s + 1) * Kp;
+      c.lda = c.K; c.ldb = c.K; c.ldc = N;
+      c.unsigned_ab = 1;
+      c.out_shift = 8 * s;
+      if (int rc = launch_gemm(ctx, c, st)) return rc;
+    }
   }
   return AIEHLC_OK;
 }

@@ -249,10 +249,11 @@ int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks);
  * activation box and one weight box per tap.  Filters whose taps do not fit in shared memory take the
  * second form whatever the setting. */
 int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on);
-/* Tuning knob for aiehlc_mm_i32_*: 1 (default) = products of at least 2^24 multiply-adds with 64 <= K <= 8256
- * run on the int8 tensor cores: the int32 operands are cut into unsigned bytes, four int8 GEMMs (one per
- * power of 256, operands of K, 2K, 3K and 4K bytes) add their shifted results, which is the reference
- * kernel's uint32 wrap-around arithmetic bit for bit; 0 = always the CUDA-core kernel. */
+/* Tuning knob for aiehlc_mm_i32_*: 1 (default) = products of at least 2^24 multiply-adds (K >= 64) run on the
+ * int8 tensor cores: the int32 operands are cut into unsigned bytes, four int8 GEMMs (one per power of
+ * 256, operands of K, 2K, 3K and 4K bytes; K in ranges of 8192 so that no partial sum can reach 2^31) add
+ * their shifted results, which is the reference kernel's uint32 wrap-around arithmetic bit for bit;
+ * 0 = always the CUDA-core kernel. */
 int aiehlc_set_mm_i32_tensor(aiehlc_ctx* ctx, int on);
 /* Tuning knob for aiehlc_conv2d_i8_srs_dev / _host: 1 (default) = where the patch form applies and the
  * output-channel tile is 32, 64 or 128 wide, the HWIO weights are fetched as they are (rows of output

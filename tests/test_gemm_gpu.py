@@ -38,11 +38,12 @@ def test_mm_i32_wraparound(ctx, shape):
     assert np.array_equal(ctx.mm_i32_host(inp, M, N, K), O.mm_i32(inp, M, N, K))
 
 
-@pytest.mark.parametrize("shape", [(512, 384, 1000), (300, 200, 4100), (1024, 1024, 1024), (130, 70, 8256), (256, 64, 64)])
+@pytest.mark.parametrize("shape", [(512, 384, 1000), (300, 200, 4100), (1024, 1024, 1024), (130, 70, 8256), (256, 64, 64),
+                                   (128, 64, 20000)])
 def test_mm_i32_on_the_tensor_cores(ctx, shape):
     """Large int32 products run as int8 limb GEMMs on the tensor cores: full-range random words, and the
-    all-ones words that make every limb product as large as it can get (K = 8256 is the limit up to which
-    no partial sum can reach 2^31), against the oracle and against the CUDA-core kernel."""
+    all-ones words that make every limb product as large as it can get (K goes in ranges of 8192 columns: up to
+    8256 no partial sum can reach 2^31), against the oracle and against the CUDA-core kernel."""
     M, N, K = shape
     rng = np.random.default_rng(11)
     inp = rng.integers(-2**31, 2**31 - 1, size=(M + N) * K, dtype=np.int64).astype(np.int32)
