@@ -109,6 +109,28 @@ def test_tile_visiting_order_needs_no_gpu():
         plan_tile_order(1000, 520, 272, num_shards=4, rows_per_shard=100)
 
 
+def test_int32_product_as_byte_limb_products():
+    """The arithmetic behind the tensor-core form of the reference's int32 kernel, in numpy: with unsigned
+    bytes a_t, b_u of the operands, sum_k a*b mod 2^32 == sum_s 2^(8s) * sum_k sum_(t<=s) a_t * b_(s-t)  mod 2^32,
+    and up to K = 8256 no group sum reaches 2^31 (so the int32 accumulator never overflows)."""
+    import numpy as np
+    from oracle import oracle as O
+    rng = np.random.default_rng(5)
+    M, N, K = 7, 5, 300
+    inp = rng.integers(-2**31, 2**31 - 1, size=(M + N) * K, dtype=np.int64).astype(np.int32)
+    A = inp[:M * K].reshape(M, K).view(np.uint32).astype(np.uint64)
+    B = inp[M * K:].reshape(N, K).view(np.uint32).astype(np.uint64)
+    limb = lambda x, t: (x >> np.uint64(8 * t)) & np.uint64(0xFF)
+    total = np.zeros((M, N), dtype=np.uint64)
+    for s in range(4):
+        group = sum(limb(A, t) @ limb(B, s - t).T for t in range(s + 1))          # one int8 GEMM of depth (s+1) K
+        assert int(group.max()) < 2**31
+        total += (group << np.uint64(8 * s)) & np.uint64(0xFFFFFFFF)
+    got = (total & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.int32)
+    assert np.array_equal(got, O.mm_i32(inp, M, N, K))
+    assert 4 * 8256 * 255 * 255 < 2**31 <= 4 * 8257 * 255 * 255                   # the K limit of one range
+
+
 def test_conv_planner_needs_no_gpu():
     """Which form a convolution takes and how it is tiled is host logic."""
     from aiehlc_b200.ops import plan_conv2d

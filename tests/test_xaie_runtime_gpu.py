@@ -49,6 +49,7 @@ def test_cpp_examples():
     res = subprocess.run([str(exes["kernel_call"])], capture_output=True, text=True, timeout=120)
     assert res.returncode == 0 and "CPU result matches device output." in res.stdout, res.stdout + res.stderr
     assert "perf: C[0]=36312 C[255]=2006232, 0 mismatches" in res.stdout
+    assert "perf 384x256x512: 0 mismatches" in res.stdout          # the same kernel on the tensor cores
     # the short host API of example/other/aieoob.c:88-95 on its own 8x8 fixture (h_a[i] = i)
     res = subprocess.run([str(exes["oob_host"])], capture_output=True, text=True, timeout=120)
     assert res.returncode == 0 and "CPU result matches vmem_out." in res.stdout, res.stdout + res.stderr
