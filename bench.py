@@ -253,7 +253,10 @@ def main() -> int:
 
     # launch-bound workloads: the K steps are recorded once and replayed as one CUDA graph, so the timed
     # region measures the GPU and not the interpreter issuing 5 us calls
-    use_graph = args.graph == "on" or (args.graph == "auto" and args.workload in ("cfg1", "cfg4") and world == 1)
+    # ... and with several ranks, where one rank's interpreter falling behind would set the job's time
+    use_graph = args.graph == "on" or (args.graph == "auto" and (
+        (args.workload in ("cfg1", "cfg4") and world == 1) or
+        (world > 1 and wl["kind"] in ("i8_srs", "i8_i32", "bf16"))))
     if use_graph:
         side = torch.cuda.Stream()
         torch.cuda.set_stream(side)        # calls are bound to the stream current at bind time
@@ -395,14 +398,22 @@ def main() -> int:
     graph, graph_launches = None, 0
     if use_graph:
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        c0 = ctx.launch_count
-        with torch.cuda.graph(graph, stream=side):
-            for i in range(K_steps):
-                step(i)
-        graph_launches = ctx.launch_count - c0
-        graph.replay()
-        torch.cuda.synchronize()
+        try:
+            graph = torch.cuda.CUDAGraph()
+            c0 = ctx.launch_count
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                for i in range(K_steps):
+                    step(i)
+            graph_launches = ctx.launch_count - c0
+            if args.workload in ("cfg1", "cfg4"):
+                graph.replay()           # microsecond kernels: a trial replay costs nothing
+            # (the long-running workloads are not replayed beforehand: a whole extra pass would start the timed
+            # one under the power cap, unlike the call-by-call form the single-GPU run uses)
+            torch.cuda.synchronize()
+        except Exception as exc:  # noqa: BLE001  -- recording failed: issue the steps one by one instead
+            graph, use_graph = None, False
+            extra["graph_fallback"] = f"{type(exc).__name__}: {exc}"[:160]
+            torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(local_rank).start()
     launches0 = ctx.launch_count
@@ -499,7 +510,7 @@ def main() -> int:
             ctx.conv2d_i8_srs_packed(xs[j], packed[j], (3, 3), sv, pad=1, out=ys[j])
         torch.cuda.synchronize()
         g2 = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g2, stream=side):
+        with torch.cuda.graph(g2, stream=side, capture_error_mode="thread_local"):
             for i in range(K_steps):
                 ctx.conv2d_i8_srs_packed(xs[i % nsets], packed[i % nsets], (3, 3), sv, pad=1, out=ys[i % nsets])
         g2.replay()
