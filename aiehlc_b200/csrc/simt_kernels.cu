@@ -131,18 +131,15 @@ int launch_mm_i32(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M, int N
 // a = sum_t a_t 2^(8t) with unsigned bytes a_t, likewise b, so
 //   a * b mod 2^32 = sum_{s=0..3} 2^(8s) * sum_{t=0..s} a_t * b_(s-t)        (terms with t + u > 3 vanish).
 // For every s the inner sums over t AND over k are one int8 GEMM with K' = (s+1) * K: the operand of group
-// s holds, side by side, limbs 0..s of A (for B: limbs s..0).  A group's sums stay below 2^31 while
+// s is, side by side, limbs 0..s of A (for B: limbs s..0).  A group's sums stay below 2^31 while
 // (s+1) * K * 255^2 < 2^31, i.e. K <= 8256, so nothing depends on how the accumulator overflows; longer K
 // goes in ranges of 8192 columns.  Four launches per range: group 0 stores (adds, after the first range),
 // groups 1..3 add their result shifted left by 8 s (wrapping), which is exactly the reference kernel's
 // uint32 arithmetic (example/perf/aieml_perf.cc:74-82).
-// K-blocks of Kp bytes before group s in a row set: 0, 1, 3, 6
-__host__ __device__ constexpr int limb_group_blocks(int s) { return s * (s + 1) / 2; }
-
-// src: rows x K int32.  dst: for s = 0..3 a matrix [rows][(s+1) * Kp] of bytes at offset
-// rows * Kp * limb_group_blocks(s); block t of group s holds limb t (reversed: limb s - t).  Kp = K rounded
-// up to 16; the padding columns are written as zero.
-// `src` rows have a pitch of `ld` words; the K columns start at the pointer given.
+// src: rows x K int32 (row pitch ld words).  dst: [rows][4 * Kp] bytes, block t of a row holding limb t of
+// its K words (reversed: limb 3 - t).  Kp = K rounded up to 16; the padding columns are written as zero.
+// Group s of A is then the first (s+1) blocks of every row, group s of B the last (s+1) blocks: the same
+// buffer serves all four GEMMs through the row pitch.
 __global__ void limb_split_kernel(const uint32_t* __restrict__ src, uint8_t* __restrict__ dst, long long rows, int K,
                                   long long ld, int Kp, int reversed) {
   const long long total = rows * (Kp / 4);
@@ -157,12 +154,8 @@ __global__ void limb_split_kernel(const uint32_t* __restrict__ src, uint8_t* __r
     for (int limb = 0; limb < 4; ++limb) {
       const uint32_t word = ((v[0] >> (8 * limb)) & 0xFFu) | (((v[1] >> (8 * limb)) & 0xFFu) << 8) |
                             (((v[2] >> (8 * limb)) & 0xFFu) << 16) | (((v[3] >> (8 * limb)) & 0xFFu) << 24);
-#pragma unroll
-      for (int s = limb; s < 4; ++s) {
-        const int block = reversed ? s - limb : limb;
-        uint8_t* g = dst + rows * Kp * limb_group_blocks(s);
-        *reinterpret_cast<uint32_t*>(g + row * (static_cast<long long>(s + 1) * Kp) + static_cast<long long>(block) * Kp + k) = word;
-      }
+      const int block = reversed ? 3 - limb : limb;
+      *reinterpret_cast<uint32_t*>(dst + row * (4LL * Kp) + static_cast<long long>(block) * Kp + k) = word;
     }
   }
 }
@@ -176,7 +169,7 @@ int launch_mm_i32_tensor(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M
   // range's group 0 stores, everything else adds
   const int kc_max = 8192;
   const int kp_max = ((K < kc_max ? K : kc_max) + 15) / 16 * 16;
-  if (ctx->limb_a.reserve(static_cast<size_t>(M) * kp_max * 10) || ctx->limb_b.reserve(static_cast<size_t>(N) * kp_max * 10))
+  if (ctx->limb_a.reserve(static_cast<size_t>(M) * kp_max * 4) || ctx->limb_b.reserve(static_cast<size_t>(N) * kp_max * 4))
     return AIEHLC_ERR_NOMEM;
   const uint32_t* A = reinterpret_cast<const uint32_t*>(in);
   const uint32_t* B = A + static_cast<size_t>(M) * K;
@@ -194,11 +187,11 @@ int launch_mm_i32_tensor(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M
       GemmCall c{};
       c.kind = 0;                                  // int8 operands
       c.epi = (s == 0 && k0 == 0) ? 0 : 1;         // store once, then add
-      c.A = la + static_cast<size_t>(M) * Kp * limb_group_blocks(s);
-      c.B = lb + static_cast<size_t>(N) * Kp * limb_group_blocks(s);
+      c.A = la;                                          // limbs 0..s: the first s+1 blocks of a row
+      c.B = lb + static_cast<size_t>(3 - s) * Kp;        // limbs s..0: the last s+1 blocks of a row
       c.C = out;
       c.M = M; c.N = N; c.K = (s + 1) * Kp;
-      c.lda = c.K; c.ldb = c.K; c.ldc = N;
+      c.lda = 4LL * Kp; c.ldb = 4LL * Kp; c.ldc = N;
       c.unsigned_ab = 1;
       c.out_shift = 8 * s;
       if (int rc = launch_gemm(ctx, c, st)) return rc;
