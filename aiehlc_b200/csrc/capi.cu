@@ -208,7 +208,8 @@ int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks) {
 
 int aiehlc_set_mm_i32_tensor(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
-  ctx->mm_i32_tensor = on ? 1 : 0;
+  if (on < 0 || on > 2) return fail(AIEHLC_ERR_INVALID, "mm_i32_tensor: 0 (never), 1 (large products) or 2 (always)");
+  ctx->mm_i32_tensor = on;
   return AIEHLC_OK;
 }
 

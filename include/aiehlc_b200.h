@@ -253,7 +253,8 @@ int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on);
  * int8 tensor cores: the int32 operands are cut into unsigned bytes, four int8 GEMMs (one per power of
  * 256, operands of K, 2K, 3K and 4K bytes; K in ranges of 8192 so that no partial sum can reach 2^31) add
  * their shifted results, which is the reference kernel's uint32 wrap-around arithmetic bit for bit;
- * 0 = always the CUDA-core kernel. */
+ * 0 = always the CUDA-core kernel; 2 = always the tensor cores, whatever the size (for tests: the reference's
+ * 16 x 16 x 16 fixture through this form). */
 int aiehlc_set_mm_i32_tensor(aiehlc_ctx* ctx, int on);
 /* Tuning knob for aiehlc_conv2d_i8_srs_dev / _host: 1 (default) = where the patch form applies and the
  * output-channel tile is 32, 64 or 128 wide, the HWIO weights are fetched as they are (rows of output

@@ -23,6 +23,25 @@ def test_perf_fixture_matches_reference_output(ctx, golden):
     assert np.array_equal(ctx.mm_i32_host(packed, 16, 16, 16), got)
 
 
+def test_reference_fixtures_through_the_tensor_core_form(ctx, golden):
+    """The reference's own 16 x 16 x 16 program output (and the 8 x 8 fixture) reproduced by the byte-limb
+    GEMMs on the tensor cores, forced for these tiny sizes."""
+    ctx.set_mm_i32_tensor(2)
+    try:
+        packed = np.arange(1, 513, dtype=np.int32)                      # example/perf/aieml_perf.cc:141-144
+        got = ctx.mm_i32(_dev(packed), 16, 16, 16).cpu().numpy()
+        assert np.array_equal(got.ravel(), np.array(golden["aieml_perf"]["words_read_back"][:256], dtype=np.int32))
+        c8 = ctx.mm_i32_host(np.arange(0, 128, dtype=np.int32), 8, 8, 8)  # aieoob.c:83-86
+        assert np.array_equal(c8, O.mm_i32(np.arange(0, 128, dtype=np.int32), 8, 8, 8))
+        rng = np.random.default_rng(12)
+        for (M, N, K) in [(1, 1, 1), (33, 17, 7), (100, 70, 33)]:
+            inp = rng.integers(-2**31, 2**31 - 1, size=(M + N) * K, dtype=np.int64).astype(np.int32)
+            assert np.array_equal(ctx.mm_i32_host(inp, M, N, K), O.mm_i32(inp, M, N, K))
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_mm_i32_tensor(1)
+
+
 def test_mm_fixtures_known_answers(ctx):
     c = ctx.mm_i32_host(np.arange(0, 512, dtype=np.int32), 16, 16, 16)    # aieml_mm.cc:137-140
     assert (c[0, 0], c[0, 15], c[15, 0], c[15, 15], int(c.sum(dtype=np.int64))) == (31960, 60760, 1043800, 1994200, 200366080)
