@@ -54,6 +54,7 @@ SIGNATURES = {
     "aiehlc_set_k_per_load": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_shard_tile_stores": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_conv_halo": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_set_conv_wide_n": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_mm_i32_tensor": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_conv_hwio_direct": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_host_blocks": (C.c_int, [_vp, C.c_int]),

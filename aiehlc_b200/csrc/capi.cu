@@ -213,6 +213,12 @@ int aiehlc_set_mm_i32_tensor(aiehlc_ctx* ctx, int on) {
   return AIEHLC_OK;
 }
 
+int aiehlc_set_conv_wide_n(aiehlc_ctx* ctx, int on) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->conv_wide_n = on ? 1 : 0;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_conv_hwio_direct(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   ctx->conv_hwio_direct = on ? 1 : 0;

@@ -74,6 +74,7 @@ struct aiehlc_ctx {
   int split_tail = 2;           // thin last wave: 1 = cut its tiles along K across idle CTA pairs, 2 = into two column ranges
   int group_m = 0;              // row-blocks per rasterisation group (0 = default for the kernel family)
   int host_blocks = 0;           // row blocks the *_host GEMM entry points pipeline over (0 = default)
+  int conv_wide_n = 0;          // patch form: the kw taps of a filter row in one MMA (N = kw * cout_tile)
   int conv_split_weights = 1;   // patch form: one weight box per filter row, each on its own barrier
   int conv_hwio_direct = 1;     // conv consumes HWIO weights as an N-major operand where it can (no re-layout launch)
   int conv_halo = 1;            // conv kernel fetches a tile's whole input patch and all taps' weights in two boxes

@@ -52,6 +52,13 @@ struct ConvParams {
   // needs about 4 cycles per box row; the weight rows are most of a CTA's load time).
   int w_split;
   uint32_t w_row_bytes;            // bytes of one filter row's box: kw taps
+  // Patch form, wide N: the kw taps of a filter row become ONE MMA with N = kw * cout_tile (the taps' weight
+  // blocks lie side by side in shared memory), so a CTA issues kh * cin / 32 instructions instead of
+  // kh * kw * cin / 32 -- small MMAs cost about 200 cycles each whatever their N.  Tap fw's product of patch
+  // row m belongs to output row m - fw: the epilogue adds column block fw of row m + fw to block 0 of row m
+  // (neighbouring lanes by shuffle, the first rows of the next warp through shared memory).
+  int wide_n;
+  uint32_t b_lbo_bytes;            // N-major weights: distance between the taps' column blocks
   uint32_t swizzle_code, sbo_bytes;
   uint32_t tmem_cols;
   int8_t* y;
@@ -74,6 +81,8 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(w_row_bar + kConvMaxStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   uint8_t* shift_smem = reinterpret_cast<uint8_t*>(tmem_base_slot + 2);  // this CTA's cout_tile shift bytes (<= 256)
+  // wide N: rows 0 .. kw-2 of every warp's column blocks 1 .. kw-1, for the warp before it (behind the barriers' 1 KB)
+  uint32_t* xchg = reinterpret_cast<uint32_t*>(bar_mem + 1024);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -174,7 +183,8 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   } else if (warp == 1) {
     if (lane == 0) {
       // bit 16: B is N-major (rows of output channels, one per input channel) instead of K-major
-      const uint32_t idesc = make_idesc<KIND_I8>(kBlockM, p.cout_tile) | (p.w_n_major ? (1u << 16) : 0u);
+      const uint32_t idesc = make_idesc<KIND_I8>(kBlockM, p.wide_n ? p.kw * p.cout_tile : p.cout_tile) |
+                             (p.w_n_major ? (1u << 16) : 0u);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -211,6 +221,20 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
               tc_fence_after();
             }
             uint64_t ad = a0 + fh * row_step;
+            if (p.wide_n) {
+              // all kw taps of this filter row at once: B = their kw column blocks (K-major weights: kw * cout_tile
+              // consecutive rows; N-major weights: blocks b_lbo_bytes apart, which the descriptor's
+              // leading-dimension field states)
+              uint64_t bw = bd;
+              if (p.w_n_major) bw = (bw & ~(0x3FFFull << 16)) | (static_cast<uint64_t>(p.b_lbo_bytes >> 4) << 16);
+#pragma unroll 4
+              for (int k = 0; k < ksteps; ++k) {
+                umma_ss<KIND_I8, 1>(tmem_base, ad + 2 * k, bw + k * p.b_kstep, idesc, accum);
+                accum = 1u;
+              }
+              bd += w_step * p.kw;
+              continue;
+            }
             for (int fw = 0; fw < p.kw; ++fw) {
 #pragma unroll 4
               for (int k = 0; k < ksteps; ++k) {
@@ -253,6 +277,29 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c, r);
         tmem_ld_wait();
+        if (p.wide_n) {
+          // out[m] = sum_fw D_fw[m + fw]: column block fw of the row fw lanes further on
+          for (int fw = 1; fw < p.kw; ++fw) {
+            uint32_t t[32];
+            tmem_ld_32x32b_x32(taddr + fw * p.cout_tile + c, t);
+            tmem_ld_wait();
+            // the first fw rows of this warp are what the last fw lanes of the warp before need
+            if (lane < fw && quad > 0) {
+              uint32_t* dst = xchg + ((quad * 4 + fw) * 4 + lane) * 32;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) dst[j] = t[j];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const bool from_next = lane + fw >= 32;
+            const uint32_t* src = xchg + (((quad + 1) * 4 + fw) * 4 + (lane + fw - 32)) * 32;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const uint32_t v = __shfl_down_sync(0xFFFFFFFFu, t[j], fw);
+              r[j] += (from_next && quad < 3) ? src[j] : (from_next ? 0u : v);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // before the next round overwrites the exchange rows
+          }
+        }
         const int col0 = co0 + c;
         if (!pix_ok || col0 >= p.cout) continue;
         const int ncols = min(32, min(p.cout_tile - c, p.cout - col0));
@@ -488,7 +535,7 @@ int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, 
   pl.tma_boxes_per_cta = p.halo ? 2 * p.chunks_per_tap : 2 * taps * p.chunks_per_tap;
   pl.mmas_per_cta = taps * p.chunks_per_tap * (p.chunk / kUmmaKBytes);
   pl.stages = p.stages;
-  pl.smem_bytes = p.stages * p.stage_bytes + 1024 + 1024;
+  pl.smem_bytes = p.stages * p.stage_bytes + 1024 + 8192 + 1024;
   pl.m_rows_used = p.rows_per_tile * p.row_w;
   pl.launches = (ctx->conv_hwio_direct && p.halo && (p.cout_tile == 32 || p.cout_tile == 64 || p.cout_tile == 128) &&
                  cout % p.cout_tile == 0) ? 1 : 2;
@@ -525,6 +572,8 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
   configure_conv(ctx, p, &n_tiles);
   p.w_split = (p.halo && p.chunks_per_tap == 1 && kh <= kConvMaxStages && kh > 1 && ctx->conv_split_weights) ? 1 : 0;
   p.w_row_bytes = static_cast<uint32_t>(kw) * p.w_block_bytes;
+  p.wide_n = (p.halo && ctx->conv_wide_n && kw > 1 && kw <= 4 && kw * p.cout_tile <= 256) ? 1 : 0;
+  p.b_lbo_bytes = p.w_block_bytes;
   p.w_n_major = hwio ? 1 : 0;
   p.b_swizzle_code = p.swizzle_code;
   p.b_sbo_bytes = p.sbo_bytes;
@@ -535,7 +584,9 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
     p.b_kstep = static_cast<uint32_t>(kUmmaKBytes * p.cout_tile) >> 4;  // 32 input channels further on
   }
   uint32_t cols = 32;
-  while (cols < static_cast<uint32_t>(p.cout_tile)) cols <<= 1;
+  const uint32_t acc_cols = p.wide_n ? static_cast<uint32_t>((kw - 1) * p.cout_tile + (p.cout_tile + 31) / 32 * 32)
+                                     : static_cast<uint32_t>(p.cout_tile);
+  while (cols < acc_cols) cols <<= 1;
   p.tmem_cols = cols;
   p.y = y; p.shift_vec = shift_vec; p.status = ctx->d_status;
   p.trace = ctx->trace;
@@ -589,7 +640,7 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
     if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
   }
 
-  const int smem_bytes = p.stages * p.stage_bytes + 1024 + 1024;
+  const int smem_bytes = p.stages * p.stage_bytes + 1024 + 8192 + 1024;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(conv2d_i8_kernel)];
   if (ks.smem_attr < smem_bytes) {
     AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
@@ -742,7 +793,7 @@ int launch_conv2d_static(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
 
-  const int smem_bytes = p.stages * p.stage_bytes + 1024 + 1024;
+  const int smem_bytes = p.stages * p.stage_bytes + 1024 + 8192 + 1024;
   AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid(n * p.tiles_h * p.tiles_w, n_tiles);
   cudaLaunchConfig_t cfg{};

@@ -107,6 +107,9 @@ class Context:
         """0/False: CUDA cores only, 1/True: tensor cores for large products (default), 2: tensor cores always."""
         _capi.check(self._lib.aiehlc_set_mm_i32_tensor(self._h, int(mode)))
 
+    def set_conv_wide_n(self, on: bool) -> None:
+        _capi.check(self._lib.aiehlc_set_conv_wide_n(self._h, 1 if on else 0))
+
     def set_conv_halo(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_conv_halo(self._h, 1 if on else 0))
 

@@ -261,6 +261,12 @@ int aiehlc_set_mm_i32_tensor(aiehlc_ctx* ctx, int on);
  * channels: the tensor core's N-major operand layout) and the convolution is one launch; 0 = weights
  * are always re-laid to [tap][cout][cin] by a pre-pass launch first. */
 int aiehlc_set_conv_hwio_direct(aiehlc_ctx* ctx, int on);
+/* Tuning knob for the convolution's patch form: 1 = the kw taps of a filter row are ONE MMA with
+ * N = kw * (output-channel tile) and the epilogue adds the taps' column blocks of neighbouring rows (filters up
+ * to 4 wide, kw * tile <= 256); 0 (default) = one MMA per tap and 32-byte K step.  Same bits either way;
+ * measured slower on the 56 x 56 x 64 benchmark (5.7 us against 4.9 us: the wider MMAs wait for the same
+ * weight boxes and the epilogue has three accumulator blocks to add). */
+int aiehlc_set_conv_wide_n(aiehlc_ctx* ctx, int on);
 /* Tuning knob for aiehlc_gemm_i8_i32_scatter_dev: 1 (default) = results leave as add-reducing TMA tile
  * stores (32 rows x 128 bytes per store; needs N a multiple of 4 and 16-byte aligned shards, else the
  * other form is used), 0 = as per-row reduction instructions issued by the epilogue warps.  Measured

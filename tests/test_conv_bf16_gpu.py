@@ -21,9 +21,10 @@ CONV_SHAPES = [(1, 56, 56, 64, 64),      # the benchmark configuration
                (1, 8, 8, 24, 16), (2, 5, 5, 3, 8), (1, 4, 4, 64, 10)]   # the last three take the direct kernel
 
 
-@pytest.mark.parametrize("halo,direct", [(True, True), (True, False), (False, False)])
+@pytest.mark.parametrize("halo,direct,wide", [(True, True, True), (True, False, True), (True, True, False),
+                                              (True, False, False), (False, False, False)])
 @pytest.mark.parametrize("shape", CONV_SHAPES)
-def test_conv2d_matches_oracle(ctx, shape, halo, direct):
+def test_conv2d_matches_oracle(ctx, shape, halo, direct, wide):
     """The forms of the tensor-core kernel: the tile's input patch fetched once with all taps as views
     into it, with the HWIO weights consumed as they are (one launch) or re-laid first (two), and one
     activation box per tap."""
@@ -34,12 +35,14 @@ def test_conv2d_matches_oracle(ctx, shape, halo, direct):
     exp = O.conv2d_i8_srs(x, wt, sv, pad=1)
     ctx.set_conv_halo(halo)
     ctx.set_conv_hwio_direct(direct)
+    ctx.set_conv_wide_n(wide)
     try:
         got = ctx.conv2d_i8_srs(_dev(x), _dev(wt), _dev(sv), pad=1).cpu().numpy()
         assert ctx.sync() == 0
     finally:
         ctx.set_conv_halo(True)
         ctx.set_conv_hwio_direct(True)
+        ctx.set_conv_wide_n(True)
     assert np.array_equal(got, exp)
 
 
