@@ -48,6 +48,7 @@ SIGNATURES = {
     "aiehlc_set_group_m": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_split_tail": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_tma_store": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_set_epilogue_groups": (C.c_int, [_vp, C.c_int]),
     "aiehlc_plan_conv2d": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "aiehlc_plan_tile_order": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp,
                                          C.c_int, _vp]),

@@ -192,6 +192,13 @@ int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on) {
   return AIEHLC_OK;
 }
 
+int aiehlc_set_epilogue_groups(aiehlc_ctx* ctx, int groups) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (groups < 0 || groups > 2) return fail(AIEHLC_ERR_INVALID, "epilogue groups must be 0, 1 or 2");
+  ctx->epi_groups = groups;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   if (on < 0 || on > 2) return fail(AIEHLC_ERR_INVALID, "split_tail: 0 (off), 1 (K ranges) or 2 (column ranges)");
@@ -258,7 +265,7 @@ int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer) {
 
 int aiehlc_set_debug(aiehlc_ctx* ctx, int mode) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
-  if (mode < 0 || mode > 3) return fail(AIEHLC_ERR_INVALID, "debug mode must be 0, 1, 2 or 3");
+  if (mode < 0 || mode > 5) return fail(AIEHLC_ERR_INVALID, "debug mode must be 0..5");
   ctx->debug_mode = mode;
   return AIEHLC_OK;
 }

@@ -70,6 +70,7 @@ struct aiehlc_ctx {
   int force_tile_n = 0;
   int pair_mode = -1;           // -1: choose per shape, 0: single-CTA tiles only, 1: CTA pairs wherever M > 128
   int k_per_load = 0;           // 0: choose, 1: one 128-byte K block per tile load, 2: two where K allows
+  int epi_groups = 0;           // groups of four epilogue warps in the CTA-pair kernel (1 or 2; 0 = by K)
   int tma_store = 1;            // epilogue results leave through shared memory + TMA tile stores when C allows
   int split_tail = 2;           // thin last wave: 1 = cut its tiles along K across idle CTA pairs, 2 = into two column ranges
   int group_m = 0;              // row-blocks per rasterisation group (0 = default for the kernel family)

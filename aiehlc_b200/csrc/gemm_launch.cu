@@ -284,7 +284,7 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
 
 
 // CTA-pair kernel: a 1-D grid of 2-CTA clusters, one cluster per 256 x kBN tile in flight.
-template <int kKind, int kBN, int kEpi, int kKPer>
+template <int kKind, int kBN, int kEpi, int kKPer, int kEpiGroups>
 int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   using S = PairSmem<kBN, kKPer>;
   CUtensorMap ma, mb, mb_narrow;
@@ -330,7 +330,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.debug = ctx->debug_mode;
   p.trace = ctx->trace;
 
-  auto kern = gemm_tn_pair_kernel<kKind, kBN, kEpi, kKPer>;
+  auto kern = gemm_tn_pair_kernel<kKind, kBN, kEpi, kKPer, kEpiGroups>;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
   if (ks.smem_attr < S::kTotal) {
     AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
@@ -346,7 +346,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   attr[0].val.clusterDim.z = 1;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.blockDim = dim3(kGemmThreads);
+  cfg.blockDim = dim3(pair_threads(kEpiGroups));
   cfg.dynamicSmemBytes = S::kTotal;
   cfg.stream = st;
   cfg.attrs = attr;
@@ -412,8 +412,16 @@ int dispatch_bn(aiehlc_ctx* ctx, const GemmCall& c, int bn, bool pair, cudaStrea
   if (pair) {
     // two K blocks per tile load when K is a whole number of 128-byte blocks (and there are enough of them)
     const bool wide = wide_k_loads(ctx, kKind == KIND_I8 ? 1 : 2, c.K);
-    if (bn == 256) return wide ? launch_pair<kKind, 256, kEpi, 2>(ctx, c, st) : launch_pair<kKind, 256, kEpi, 1>(ctx, c, st);
-    return wide ? launch_pair<kKind, 128, kEpi, 2>(ctx, c, st) : launch_pair<kKind, 128, kEpi, 1>(ctx, c, st);
+    // Two groups of epilogue warps pay where the output stage, not the MMAs, sets a tile's pace: up to
+    // 16 K blocks (measured: 10-18 % faster at K <= 1024 bytes, equal at 2048, 1-2 % slower beyond).
+    const long long k_bytes = static_cast<long long>(c.K) * (kKind == KIND_I8 ? 1 : 2);
+    const int groups = ctx->epi_groups ? ctx->epi_groups : (k_bytes <= 16 * kBlockKBytes ? 2 : 1);
+    if (groups == 1) {
+      if (bn == 256) return wide ? launch_pair<kKind, 256, kEpi, 2, 1>(ctx, c, st) : launch_pair<kKind, 256, kEpi, 1, 1>(ctx, c, st);
+      return wide ? launch_pair<kKind, 128, kEpi, 2, 1>(ctx, c, st) : launch_pair<kKind, 128, kEpi, 1, 1>(ctx, c, st);
+    }
+    if (bn == 256) return wide ? launch_pair<kKind, 256, kEpi, 2, 2>(ctx, c, st) : launch_pair<kKind, 256, kEpi, 1, 2>(ctx, c, st);
+    return wide ? launch_pair<kKind, 128, kEpi, 2, 2>(ctx, c, st) : launch_pair<kKind, 128, kEpi, 1, 2>(ctx, c, st);
   }
   switch (bn) {
     case 256: return launch_one<kKind, 256, kEpi>(ctx, c, st);

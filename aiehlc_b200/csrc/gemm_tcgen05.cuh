@@ -87,7 +87,8 @@ struct GemmParams {
   // the int32 result is shifted left (wrapping) before it is stored or added.
   int unsigned_ab, out_shift;
   long long* trace;        // measurement aid: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
-  int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling);
+  int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling),
+                           // 4 = int32 results staged but their tile stores not issued, 5 = no output stage;
                            // test aid: 3 = the producer neither loads nor signals, so every consumer wait
                            // runs out and the kernel leaves through its bounded-wait exit
 };
@@ -215,13 +216,17 @@ __device__ __forceinline__ void shard_add_chunk(const GemmParams& p, StoreCtx& s
 // XOR-swizzled with the row number exactly as the tensor map's swizzle mode expects, which also
 // spreads the rows over the shared-memory banks.  The hardware clips rows >= M and columns >= N.
 template <int kGroupBytes, int kPieceBytes, bool kReduceAdd>
-__device__ __forceinline__ void tma_emit(StoreCtx& sc, const uint32_t* words, int col0) {
+__device__ __forceinline__ void tma_emit(StoreCtx& sc, const uint32_t* words, int col0, bool issue = true) {
   constexpr int kPerGroup = kGroupBytes / kPieceBytes;
   constexpr int kPieces = kPieceBytes / 16;
   const int k = sc.chunk_in_group;
   uint8_t* buf = sc.buf[sc.which];
   if (k == 0) {
-    if (sc.lane == 0) tma_store_wait_read<1>();  // the store issued from this buffer two groups ago has read it
+    // the store issued from this buffer (two groups ago, or the last one where the warp has one buffer) has read it
+    if (sc.lane == 0) {
+      if (sc.buf[0] == sc.buf[1]) tma_store_wait_read<0>();
+      else tma_store_wait_read<1>();
+    }
     __syncwarp();
   }
   const int swz = kGroupBytes == 128 ? (sc.lane & 7) : kGroupBytes == 64 ? ((sc.lane >> 1) & 3) : ((sc.lane >> 2) & 1);
@@ -232,7 +237,7 @@ __device__ __forceinline__ void tma_emit(StoreCtx& sc, const uint32_t* words, in
   if (k == kPerGroup - 1) {
     fence_proxy_async_smem();
     __syncwarp();
-    if (sc.lane == 0) {
+    if (sc.lane == 0 && issue) {
       const int group_col0 = col0 - k * 32;
       if constexpr (kReduceAdd) tma_reduce_add_2d(sc.tmap, smem_u32(buf), group_col0, sc.warp_row0);
       else tma_store_2d(sc.tmap, smem_u32(buf), group_col0, sc.warp_row0);
@@ -261,6 +266,7 @@ template <int kEpi, int kBN, bool kForceDirect = false>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[32], int row, int col0, bool row_ok,
                                             StoreCtx& sc) {
   const int ncols = min(32, p.N - col0);
+  if (p.debug == 5) return;
   if constexpr (kEpi == EPI_I32 || kEpi == EPI_I32_ACC) {
     if (p.out_shift) {
 #pragma unroll
@@ -271,7 +277,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
       return;
     }
     if (!kForceDirect && p.tma_store) {
-      tma_emit<128, 128, kEpi == EPI_I32_ACC>(sc, r, col0);
+      tma_emit<128, 128, kEpi == EPI_I32_ACC>(sc, r, col0, p.debug != 4);
       return;
     }
     int32_t* dst = static_cast<int32_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;

@@ -10,8 +10,9 @@
 //               credited to the leader's "full" barrier
 //   leader    : warp 1 issues tcgen05.mma.cta_group::2 (M = 256); each CTA's TMEM receives its
 //               128 rows of the accumulator; completion is signalled to both CTAs' barriers
-//   both CTAs : warps 2-5 drain their 128 accumulator rows through the fused output stage and
-//               tell the leader when the accumulator buffer is free
+//   both CTAs : warps 2-5 (and 6-9 where the kernel is built with two epilogue groups) drain their
+//               128 accumulator rows through the fused output stage and tell the leader when the
+//               accumulator buffer is free
 //
 // The reference's formulation is unchanged: C = A . B^T with A[M][K], B[N][K], all K slices
 // accumulated in TMEM before one flush (example/perf/aieml_perf.cc:199-231; tiling.py:299-333).
@@ -109,8 +110,15 @@ __device__ __forceinline__ void add_deposited_chunk(uint32_t (&r)[32], const int
   }
 }
 
-template <int kKind, int kBN, int kEpi, int kKPer>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// Warps of a CTA of the pair kernel: producer, MMA issuer and two groups of four epilogue warps.  A
+// warp reads the 32 TMEM lanes its number modulo 4 selects, so the two warps of a lane quarter share
+// a tile's rows and each takes half of its columns: twice as many accumulator reads, proxy fences and
+// tile stores are in flight as with one group.
+// With one group (kEpiGroups = 1) every warp drains whole rows of the tile and has two staging buffers.
+constexpr int pair_threads(int epi_groups) { return 64 + epi_groups * 128; }
+
+template <int kKind, int kBN, int kEpi, int kKPer, int kEpiGroups>
+__global__ void __launch_bounds__(pair_threads(kEpiGroups), 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_b_narrow, const __grid_constant__ CUtensorMap tmap_c,
                     const GemmParams p) {
@@ -122,6 +130,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   constexpr int kElemBytes = kKind == KIND_I8 ? 1 : 2;
   constexpr int kBlockKElems = kBlockKBytes / kElemBytes;
   static_assert(kBN == 128 || kBN == 256, "pair tile N");
+  static_assert(kEpiGroups == 1 || kEpiGroups == 2, "epilogue warp groups");
+  static_assert(kEpiGroups * 4 * kStoreBufBytes <= kStoreStagingBytes, "at least one staging buffer per epilogue warp");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -152,7 +162,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[a]), 8);  // 4 epilogue warps in each of the two CTAs
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 8 * kEpiGroups);  // every epilogue warp of the two CTAs
     }
     *abort_flag = 0;
     *sk_warps_done = 0;
@@ -270,8 +280,10 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs)
     const int quad = warp & 3;
-    StoreCtx sc{&tmap_c, {store_staging + (quad * 2) * kStoreBufBytes, store_staging + (quad * 2 + 1) * kStoreBufBytes},
-                0, 0, lane, 0, nullptr, 0};
+    const int group = (warp - 2) >> 2;
+    // one staging buffer per warp with two groups (the tile stores of the other group overlap the refill)
+    uint8_t* stage0 = store_staging + (kEpiGroups == 1 ? quad * 2 : warp - 2) * kStoreBufBytes;
+    StoreCtx sc{&tmap_c, {stage0, kEpiGroups == 1 ? stage0 + kStoreBufBytes : stage0}, 0, 0, lane, 0, nullptr, 0};
     int it = 0;
     bool ok = true;
     WorkUnit w;
@@ -295,8 +307,15 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       select_shard(p, mb * kPairM + static_cast<int>(rank) * kBlockM, sc);
       if (w.parts == 1) {
         const int ncols = kBN / w.n_parts;
-        drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, nb * kBN + w.n_part * ncols, sc, ncols);
-      } else {
+        const int n0 = nb * kBN + w.n_part * ncols;
+        // each group takes half of the columns where a half is whole 64-column drain steps and whole store groups
+        constexpr int kGran = StoreGroup<kEpi, kBN>::kCols > 64 ? StoreGroup<kEpi, kBN>::kCols : 64;
+        const int share = ncols / kEpiGroups;
+        if (share % kGran == 0)
+          drain_accumulator<kBN, kEpi>(p, taddr + group * share, row, row_ok, n0 + group * share, sc, share);
+        else if (group == 0)
+          drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, n0, sc, ncols);
+      } else if (group == 0) {
         // tail tile cut along K; scratch is [tail tile][depositing range][CTA rank][chunk]
         constexpr int kChunks = kBN / 32;
         constexpr long long kCtaInts = static_cast<long long>(kChunks) * kSkChunkInts;

@@ -123,6 +123,10 @@ class Context:
         """0: per-thread stores, 1: tile stores for int32/bf16 results (default), 2: for int8 results too."""
         _capi.check(self._lib.aiehlc_set_tma_store(self._h, int(mode)))
 
+    def set_epilogue_groups(self, groups: int) -> None:
+        """CTA-pair kernel: 1 or 2 groups of four epilogue warps; 0 (default) chooses by K."""
+        _capi.check(self._lib.aiehlc_set_epilogue_groups(self._h, int(groups)))
+
     def set_split_tail(self, mode) -> None:
         """Thin last wave: 0/False = tiles whole, 1/True = cut along K, 2 = cut into two column ranges."""
         _capi.check(self._lib.aiehlc_set_split_tail(self._h, int(mode)))

@@ -231,6 +231,12 @@ int aiehlc_set_k_per_load(aiehlc_ctx* ctx, int k_blocks);
  * its per-thread 32-byte stores); 0 = every thread stores its own row directly.  Tile stores need C
  * 16-byte aligned with a 16-byte row pitch; otherwise the direct path is taken whatever the setting. */
 int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on);
+/* Tuning knob for the CTA-pair kernel: groups of four epilogue warps per CTA.  2 = the two warps of a
+ * TMEM lane quarter each drain half of a tile's columns (one staging buffer per warp; more accumulator
+ * reads, proxy fences and tile stores in flight: where the output stage sets the pace, K <= 1024 bytes,
+ * results leave 10-18 % faster); 1 = four warps with two staging buffers each (1-2 % faster where K is
+ * deep); 0 (default) = 2 up to 16 K blocks of 128 bytes, else 1. */
+int aiehlc_set_epilogue_groups(aiehlc_ctx* ctx, int groups);
 /* Tuning knob for a thin last wave (at most half of the CTA pairs busy) of a CTA-pair launch:
  *   1 = (int8 only) its tiles are cut along K into up to 4 ranges run by otherwise idle pairs; the ranges
  *       exchange int32 partial sums through a context workspace and each runs the output stage on its
@@ -284,7 +290,8 @@ int aiehlc_set_group_m(aiehlc_ctx* ctx, int group_m);
 int aiehlc_set_pdl(aiehlc_ctx* ctx, int on);
 /* Measurement aid for the GEMM kernels (results are then meaningless): 1 = skip the TMA loads and
  * run the MMAs on whatever shared memory holds (tensor-pipe ceiling), 2 = skip the MMAs and only
- * stream the operands (operand-feed ceiling), 0 = normal.
+ * stream the operands (operand-feed ceiling), 4 = int32 results are staged in shared memory but their
+ * tile stores are not issued, 5 = the output stage is skipped after the accumulator reads, 0 = normal.
  * Test aid: 3 = the producer warp neither loads nor signals.  Every other warp's wait then runs out
  * (about one second), the kernel records which wait gave up in the status word, frees its TMEM and
  * returns; aiehlc_sync reports AIEHLC_ERR_DEVICE with the code (102 = the MMA issuer waited for

@@ -262,6 +262,41 @@ def test_both_store_paths(ctx, tma_store):
         ctx.set_tma_store(1)
 
 
+@pytest.mark.parametrize("tma_store", [1, 2])
+@pytest.mark.parametrize("groups", [1, 2])
+@pytest.mark.parametrize("shape", [(512, 512, 512), (520, 336, 640), (300, 260, 192), (2304, 2304, 512), (2560, 2000, 272)])
+def test_epilogue_warp_groups(ctx, shape, groups, tma_store):
+    """CTA-pair kernel with one or two groups of epilogue warps (two: the warps of a TMEM lane quarter
+    each drain half of a tile's columns, also of the 128-column ranges of a thin last wave), results
+    leaving through tile stores or, for int8, per-thread stores: the oracle's bytes in every case."""
+    M, N, K = shape
+    A = synth.int8_uniform(13, (M, K))
+    B = synth.int8_uniform(1013, (N, K))
+    ctx.set_epilogue_groups(groups)
+    ctx.set_tma_store(tma_store)
+    ctx.set_cta_pair(1)
+    try:
+        dA, dB = _dev(A), _dev(B)
+        exp32 = O.gemm_i8_i32(A, B)
+        acc = ctx.gemm_i8_i32(dA, dB)
+        assert np.array_equal(acc.cpu().numpy(), exp32)
+        ctx.gemm_i8_i32(dA, dB, out=acc, accumulate=True)
+        assert np.array_equal(acc.cpu().numpy(), exp32 * 2)
+        assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift=8).cpu().numpy(), O.gemm_i8_srs(A, B, shift=8))
+        Kb = K // 2
+        Ab = synth.normal_bf16_bits(14, (M, Kb))
+        Bb = synth.normal_bf16_bits(1014, (N, Kb))
+        got = ctx.gemm_bf16(_dev(Ab.view(np.int16)).view(torch.bfloat16), _dev(Bb.view(np.int16)).view(torch.bfloat16))
+        ref = O.gemm_bf16(Ab, Bb).astype(np.float64)
+        gf = got.float().cpu().numpy().astype(np.float64)
+        assert float(np.max(np.abs(gf - ref) / np.maximum(np.abs(ref), 1.0))) <= 1e-2      # the bf16 tolerance
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_epilogue_groups(0)
+        ctx.set_tma_store(1)
+        ctx.set_cta_pair(-1)
+
+
 @pytest.mark.parametrize("k_per_load", [1, 2])
 @pytest.mark.parametrize("shape", [(512, 512, 512), (520, 336, 640), (300, 520, 1152), (256, 256, 384), (1024, 384, 2176)])
 def test_k_blocks_per_tile_load(ctx, shape, k_per_load):
@@ -312,18 +347,24 @@ def test_row_sharded_add_reduction_output(ctx, M, N, K, rows_per_shard, group_m,
     try:
         half = K // 2 // 16 * 16
         dA, dB = _dev(A), _dev(B)
-        ctx.gemm_i8_i32_scatter(dA[:, :half].contiguous(), dB[:, :half].contiguous(), shards, rows_per_shard, first_shard)
-        ctx.gemm_i8_i32_scatter(dA[:, half:].contiguous(), dB[:, half:].contiguous(), shards, rows_per_shard, first_shard + 1)
-        assert ctx.sync() == 0
-        got = torch.cat(shards).cpu().numpy()
         exp = O.gemm_i8_i32(A, B)
         exp[(n_shards - 1) * rows_per_shard:] += 77
-        assert np.array_equal(got[:M], exp)
-        assert np.all(got[M:] == 77)
+        for groups in ((1, 2) if pair else (0,)):                      # epilogue warp groups of the pair kernel
+            ctx.set_epilogue_groups(groups)
+            for sh in shards[:-1]:
+                sh.zero_()
+            shards[-1].fill_(77)
+            ctx.gemm_i8_i32_scatter(dA[:, :half].contiguous(), dB[:, :half].contiguous(), shards, rows_per_shard, first_shard)
+            ctx.gemm_i8_i32_scatter(dA[:, half:].contiguous(), dB[:, half:].contiguous(), shards, rows_per_shard, first_shard + 1)
+            assert ctx.sync() == 0
+            got = torch.cat(shards).cpu().numpy()
+            assert np.array_equal(got[:M], exp)
+            assert np.all(got[M:] == 77)
     finally:
         ctx.set_cta_pair(-1)
         ctx.set_group_m(0)
         ctx.set_shard_tile_stores(True)
+        ctx.set_epilogue_groups(0)
     with pytest.raises(_capi.AiehlcError):
         ctx.gemm_i8_i32_scatter(dA, dB, shards, 100)                   # not a multiple of 128
     with pytest.raises(_capi.AiehlcError):
