@@ -60,6 +60,7 @@ SIGNATURES = {
     "aiehlc_set_conv_hwio_direct": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_host_blocks": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_trace": (C.c_int, [_vp, _vp]),
+    "aiehlc_set_cta_times": (C.c_int, [_vp, _vp]),
     "aiehlc_launch_count": (C.c_longlong, [_vp]),
 }
 

@@ -257,6 +257,12 @@ int aiehlc_set_pdl(aiehlc_ctx* ctx, int on) {
   return AIEHLC_OK;
 }
 
+int aiehlc_set_cta_times(aiehlc_ctx* ctx, long long* device_buffer) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->cta_times = device_buffer;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   ctx->trace = device_buffer;

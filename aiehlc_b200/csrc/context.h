@@ -81,6 +81,7 @@ struct aiehlc_ctx {
   int conv_halo = 1;            // conv kernel fetches a tile's whole input patch and all taps' weights in two boxes
   int pdl = 1;                  // launch the tensor-core kernels with programmatic stream serialization
   int debug_mode = 0;           // see GemmParams::debug
+  long long* cta_times = nullptr;  // see GemmParams::cta_times (device pointer owned by the caller)
   long long* trace = nullptr;   // see GemmParams::trace (device pointer owned by the caller)
   long long launches = 0;
   std::unordered_map<const void*, aiehlc::KernelSetup> kernel_setup;

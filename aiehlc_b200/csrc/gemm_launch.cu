@@ -257,6 +257,7 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.status = ctx->d_status;
   p.debug = ctx->debug_mode;
   p.trace = ctx->trace;
+  p.cta_times = ctx->cta_times;
 
   auto kern = gemm_tn_kernel<kKind, kBN, kEpi>;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
@@ -329,6 +330,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.status = ctx->d_status;
   p.debug = ctx->debug_mode;
   p.trace = ctx->trace;
+  p.cta_times = ctx->cta_times;
 
   auto kern = gemm_tn_pair_kernel<kKind, kBN, kEpi, kKPer, kEpiGroups>;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];

@@ -86,6 +86,7 @@ struct GemmParams {
   // int32 products on the int8 tensor cores (see launch_mm_i32_tensor): operands are unsigned bytes and
   // the int32 result is shifted left (wrapping) before it is stored or added.
   int unsigned_ab, out_shift;
+  long long* cta_times;    // measurement aid (pair kernel): global nanosecond timer at entry / exit of every CTA, or null
   long long* trace;        // measurement aid: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
   int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling),
                            // 4 = int32 results staged but their tile stores not issued, 5 = no output stage;

@@ -411,6 +411,10 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     p.trace[6] = clock64();
     p.trace[15] = static_cast<long long>(globaltimer_ns());
   }
+  if (p.cta_times && threadIdx.x == 0) {
+    p.cta_times[2 * blockIdx.x] = static_cast<long long>(entry_ns);
+    p.cta_times[2 * blockIdx.x + 1] = static_cast<long long>(globaltimer_ns());
+  }
 }
 
 }  // namespace aiehlc

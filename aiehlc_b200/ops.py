@@ -146,6 +146,12 @@ class Context:
         ptr = C.c_void_p(None) if buf is None else self._dev(buf, torch.int64, "trace")
         _capi.check(self._lib.aiehlc_set_trace(self._h, ptr))
 
+    def set_cta_times(self, buf) -> None:
+        """buf: int64 CUDA tensor of 2 * 148 words (entry / exit nanoseconds of every CTA of a pair launch) or None."""
+        import torch
+        ptr = C.c_void_p(None) if buf is None else self._dev(buf, torch.int64, "cta_times")
+        _capi.check(self._lib.aiehlc_set_cta_times(self._h, ptr))
+
     def sync(self, on_torch_stream: bool = True) -> int:
         """Waits for the stream and returns the device status word (raises if it is non-zero)."""
         st = C.c_int32(0)

@@ -304,6 +304,10 @@ int aiehlc_set_debug(aiehlc_ctx* ctx, int mode);
  * tile 0 also holds [5] kernel entry, [6] kernel exit (clock64) and [7] / word 15 the global
  * nanosecond timer at entry / exit.  The buffer must hold 8 * max(2, tiles per CTA) words.  NULL switches the stamps off. */
 int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer);
+/* Measurement aid: while `device_buffer` is non-NULL, every CTA of a CTA-pair GEMM launch writes the
+ * global nanosecond timer at its entry and exit into words [2 * CTA] and [2 * CTA + 1] (the buffer
+ * must hold 2 * 148 words): shows which pairs finish last.  NULL switches it off. */
+int aiehlc_set_cta_times(aiehlc_ctx* ctx, long long* device_buffer);
 /* Number of kernel launches this context has enqueued since creation. */
 long long aiehlc_launch_count(const aiehlc_ctx* ctx);
 
