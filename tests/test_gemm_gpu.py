@@ -441,6 +441,36 @@ def test_cfg2_full_size_properties_and_sampled_rows(ctx):
     assert torch.equal(ctx.gemm_i8_srs_cascade(dA, dB, 4, shift=8), c8)
 
 
+@pytest.mark.parametrize("shape", [(16384, 4096, 512), (8192, 8192, 1024)])
+def test_shallow_k_large_outputs_sampled_rows_and_checksums(ctx, shape):
+    """Large outputs over a shallow K (the output stage sets the pace; two groups of epilogue warps by
+    default): sampled rows bit-exact against the oracle, every row through the checksum of checksums,
+    srs consistent with the int32 result everywhere, one and two groups identical."""
+    M, N, K = shape
+    dA = synth.int8_uniform_torch(6, (M, K), DEV)
+    dB = synth.int8_uniform_torch(1006, (N, K), DEV)
+    c32 = ctx.gemm_i8_i32(dA, dB)
+    c8 = ctx.gemm_i8_srs(dA, dB, shift=7)
+    assert ctx.sync() == 0
+    rows = np.r_[0:8, M // 2 - 4:M // 2 + 4, M - 8:M]
+    B = synth.int8_uniform(1006, (N, K))
+    A_rows = np.concatenate([synth.int8_uniform(6, (1, K), start=int(r) * K) for r in rows])
+    sel = torch.from_numpy(rows).to(DEV)
+    assert np.array_equal(c32[sel].cpu().numpy(), O.gemm_i8_i32(A_rows, B))
+    assert np.array_equal(c8[sel].cpu().numpy(), O.gemm_i8_srs(A_rows, B, shift=7))
+    colsum = dB.to(torch.float64).sum(dim=0)
+    assert torch.equal(c32.to(torch.float64).sum(dim=1), dA.to(torch.float64) @ colsum)
+    assert torch.equal(ctx.srs_i32_i8(c32, shift=7), c8)
+    try:
+        for groups in (1, 2):
+            ctx.set_epilogue_groups(groups)
+            assert torch.equal(ctx.gemm_i8_i32(dA, dB), c32), groups
+            assert torch.equal(ctx.gemm_i8_srs(dA, dB, shift=7), c8), groups
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_epilogue_groups(0)
+
+
 def test_cfg5_full_size_sampled_rows_and_checksums(ctx):
     """int8 65536 x 8192 x 8192 -> int32 (2.1 GB of results) at full size: sampled rows bit-exact against the
     oracle, every row through the checksum of checksums, and the row-sharded form (8 shards of 8192 rows,
