@@ -99,14 +99,45 @@ __global__ void fill_i32_kernel(int32_t* out, long long n, int value) {
     out[i] = value;
 }
 
-template <typename T>
-__global__ void repack_kernel(const T* __restrict__ src, T* __restrict__ dst, long long rows,
-                              long long cols, long long ld_src, long long ld_dst) {
-  const long long n = rows * cols;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / cols, c = i - r * cols;
-    dst[r * ld_dst + c] = src[r * ld_src + c];
+// Copies a matrix whose base or row pitch is not 16-byte aligned into a pitched workspace, 16 output
+// bytes per thread.  The source bytes of a vector start at any address: they are fetched as five aligned
+// 32-bit words and shifted into place; vectors at the very ends of the source (where an aligned word
+// would reach outside it) and the ragged end of a row go byte by byte.  Bytes of the workspace past the
+// row's true extent are zeroed.
+__global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, long long rows,
+                              long long row_bytes, long long ld_src_bytes, long long ld_dst_bytes) {
+  const long long vecs_per_row = ld_dst_bytes / 16;
+  const uint8_t* const src_end = src + (rows - 1) * ld_src_bytes + row_bytes;
+  for (long long row = blockIdx.y; row < rows; row += gridDim.y) {
+    const uint8_t* srow = src + row * ld_src_bytes;
+    uint4* drow = reinterpret_cast<uint4*>(dst + row * ld_dst_bytes);
+    for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < vecs_per_row;
+         v += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long b = v * 16;
+      const uint8_t* s = srow + b;
+      const long long left = row_bytes - b;
+      const uintptr_t addr = reinterpret_cast<uintptr_t>(s);
+      const unsigned a = static_cast<unsigned>(addr & 3);
+      const uint8_t* w0 = s - a;
+      uint4 out;
+      if (left >= 16 && w0 >= src && w0 + 20 <= src_end) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(w0);
+        const uint32_t x0 = w[0], x1 = w[1], x2 = w[2], x3 = w[3];
+        const uint32_t x4 = a ? w[4] : 0u;
+        const unsigned sh = a * 8;
+        out.x = __funnelshift_r(x0, x1, sh);
+        out.y = __funnelshift_r(x1, x2, sh);
+        out.z = __funnelshift_r(x2, x3, sh);
+        out.w = __funnelshift_r(x3, x4, sh);
+      } else {
+        uint32_t o[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (j < left) o[j >> 2] |= static_cast<uint32_t>(s[j]) << (8 * (j & 3));
+        out = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      drow[v] = out;
+    }
   }
 }
 
@@ -219,13 +250,13 @@ int launch_fill_i32(aiehlc_ctx* ctx, int32_t* out, long long n, int value, cudaS
 
 int launch_repack(aiehlc_ctx* ctx, const void* src, void* dst, long long rows, long long cols,
                   long long ld_src, long long ld_dst, int esize, cudaStream_t st) {
-  const int g = grid_for(ctx, rows * cols, 256);
-  if (esize == 1)
-    repack_kernel<uint8_t><<<g, 256, 0, st>>>(static_cast<const uint8_t*>(src),
-                                             static_cast<uint8_t*>(dst), rows, cols, ld_src, ld_dst);
-  else
-    repack_kernel<uint16_t><<<g, 256, 0, st>>>(static_cast<const uint16_t*>(src),
-                                              static_cast<uint16_t*>(dst), rows, cols, ld_src, ld_dst);
+  // ld_dst * esize is a multiple of 16 and dst 16-byte aligned (a workspace of this library)
+  const long long vecs = ld_dst * esize / 16;
+  const unsigned gx = static_cast<unsigned>(vecs > 256 * 4 ? 4 : (vecs + 255) / 256);
+  const long long cap = static_cast<long long>(ctx->sm_count) * 16 / gx;
+  const unsigned gy = static_cast<unsigned>(rows < cap ? rows : cap);
+  repack_kernel<<<dim3(gx ? gx : 1, gy ? gy : 1), 256, 0, st>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst),
+                                                           rows, cols * esize, ld_src * esize, ld_dst * esize);
   AIEHLC_CUDA(cudaGetLastError());
   ctx->launches++;
   return AIEHLC_OK;

@@ -107,6 +107,34 @@ def test_gemm_i8_i32_matches_oracle(ctx, shape, tile_n, pair):
     assert np.array_equal(got, O.gemm_i8_i32(A, B))
 
 
+@pytest.mark.parametrize("offset", [0, 1, 2, 3, 8])
+@pytest.mark.parametrize("K", [17, 19, 50, 333, 1001, 3000])
+def test_operands_with_unaligned_rows_or_base(ctx, K, offset):
+    """Row pitches and base addresses TMA cannot take (not multiples of 16 bytes): the operands are first
+    copied to a pitched workspace, 16 bytes per thread from any byte alignment; same bytes as the oracle
+    for int8 (int32 and srs results) and within the bf16 tolerance for bf16 (2-byte alignment)."""
+    M, N = 150, 70
+    A = synth.int8_uniform(21, (M, K))
+    B = synth.int8_uniform(1021, (N, K))
+    flat_a = torch.zeros(M * K + 64, dtype=torch.int8, device=DEV)
+    flat_b = torch.zeros(N * K + 64, dtype=torch.int8, device=DEV)
+    dA = flat_a[offset:offset + M * K].view(M, K)
+    dB = flat_b[offset + 1:offset + 1 + N * K].view(N, K)
+    dA.copy_(_dev(A)); dB.copy_(_dev(B))
+    assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), O.gemm_i8_i32(A, B))
+    assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift=6).cpu().numpy(), O.gemm_i8_srs(A, B, shift=6))
+    Ab = synth.normal_bf16_bits(22, (M, K))
+    Bb = synth.normal_bf16_bits(1022, (N, K))
+    flat = torch.zeros((M + N) * K + 64, dtype=torch.bfloat16, device=DEV)
+    dAb = flat[offset:offset + M * K].view(M, K)
+    dBb = flat[offset + M * K + 1:offset + M * K + 1 + N * K].view(N, K)
+    dAb.copy_(_dev(Ab.view(np.int16)).view(torch.bfloat16)); dBb.copy_(_dev(Bb.view(np.int16)).view(torch.bfloat16))
+    ref = O.gemm_bf16(Ab, Bb).astype(np.float64)
+    gf = ctx.gemm_bf16(dAb, dBb).float().cpu().numpy().astype(np.float64)
+    assert float(np.max(np.abs(gf - ref) / np.maximum(np.abs(ref), 1.0))) <= 1e-2      # the bf16 tolerance
+    assert ctx.sync() == 0
+
+
 def test_extreme_values_and_host_entry_point(ctx):
     M, N, K = 192, 160, 8192                                            # |acc| reaches 2^27
     A = np.full((M, K), -128, np.int8)
