@@ -421,7 +421,8 @@ int dispatch_bn(aiehlc_ctx* ctx, const GemmCall& c, int bn, bool pair, cudaStrea
     // Two groups of epilogue warps pay where the output stage, not the MMAs, sets a tile's pace: up to
     // 16 K blocks (measured: 10-18 % faster at K <= 1024 bytes, equal at 2048, 1-2 % slower beyond).
     const long long k_bytes = static_cast<long long>(c.K) * (kKind == KIND_I8 ? 1 : 2);
-    const int groups = ctx->epi_groups ? ctx->epi_groups : (k_bytes <= 16 * kBlockKBytes ? 2 : 1);
+    // (a row-sharded output is bound by the wire to the other GPUs, not by the output stage: one group, as measured)
+    const int groups = ctx->epi_groups ? ctx->epi_groups : (k_bytes <= 16 * kBlockKBytes && c.num_shards == 0 ? 2 : 1);
     if (groups == 1) {
       if (bn == 256) return wide ? launch_pair<kKind, 256, kEpi, 2, 1>(ctx, c, st) : launch_pair<kKind, 256, kEpi, 1, 1>(ctx, c, st);
       return wide ? launch_pair<kKind, 128, kEpi, 2, 1>(ctx, c, st) : launch_pair<kKind, 128, kEpi, 1, 1>(ctx, c, st);
