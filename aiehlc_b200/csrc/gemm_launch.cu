@@ -418,11 +418,13 @@ int dispatch_bn(aiehlc_ctx* ctx, const GemmCall& c, int bn, bool pair, cudaStrea
   if (pair) {
     // two K blocks per tile load when K is a whole number of 128-byte blocks (and there are enough of them)
     const bool wide = wide_k_loads(ctx, kKind == KIND_I8 ? 1 : 2, c.K);
-    // Two groups of epilogue warps pay where the output stage, not the MMAs, sets a tile's pace: up to
-    // 16 K blocks (measured: 10-18 % faster at K <= 1024 bytes, equal at 2048, 1-2 % slower beyond).
+    // Two groups of epilogue warps pay where the output stage, not the MMAs, sets a tile's pace: measured
+    // 10-18 % faster up to 8 K blocks for int8 (int32 or srs results) and up to 4 for bf16 (half the result
+    // bytes per tile), equal to 5 % slower from twice that depth on.  A row-sharded output is bound by the
+    // wire to the other GPUs, not by the output stage: one group, as measured.
     const long long k_bytes = static_cast<long long>(c.K) * (kKind == KIND_I8 ? 1 : 2);
-    // (a row-sharded output is bound by the wire to the other GPUs, not by the output stage: one group, as measured)
-    const int groups = ctx->epi_groups ? ctx->epi_groups : (k_bytes <= 16 * kBlockKBytes && c.num_shards == 0 ? 2 : 1);
+    const long long two_groups_up_to = (kKind == KIND_I8 ? 8 : 4) * kBlockKBytes;
+    const int groups = ctx->epi_groups ? ctx->epi_groups : (k_bytes <= two_groups_up_to && c.num_shards == 0 ? 2 : 1);
     if (groups == 1) {
       if (bn == 256) return wide ? launch_pair<kKind, 256, kEpi, 2, 1>(ctx, c, st) : launch_pair<kKind, 256, kEpi, 1, 1>(ctx, c, st);
       return wide ? launch_pair<kKind, 128, kEpi, 2, 1>(ctx, c, st) : launch_pair<kKind, 128, kEpi, 1, 1>(ctx, c, st);

@@ -235,7 +235,8 @@ int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on);
  * TMEM lane quarter each drain half of a tile's columns (one staging buffer per warp; more accumulator
  * reads, proxy fences and tile stores in flight: where the output stage sets the pace, K <= 1024 bytes,
  * results leave 10-18 % faster); 1 = four warps with two staging buffers each (1-2 % faster where K is
- * deep); 0 (default) = 2 up to 16 K blocks of 128 bytes, else 1. */
+ * deep); 0 (default) = 2 up to 8 K blocks of 128 bytes for int8 operands and 4 for bf16 (and never for a
+ * row-sharded output, which the wire bounds), else 1. */
 int aiehlc_set_epilogue_groups(aiehlc_ctx* ctx, int groups);
 /* Tuning knob for a thin last wave (at most half of the CTA pairs busy) of a CTA-pair launch:
  *   1 = (int8 only) its tiles are cut along K into up to 4 ranges run by otherwise idle pairs; the ranges
