@@ -201,6 +201,35 @@ def reference_arm(args, wl: dict) -> dict:
 
 
 # --------------------------------------------------------------------------- GPU arm
+GATE_HEAD = 128   # calls queued before the gate opens: far below the depth of a stream's launch queue
+
+
+class StreamGate:
+    """Holds a stream at a wait on a word of pinned host memory (a stream memory operation, no kernel spins)
+    until the host writes it: work queued behind it starts when the host says so."""
+
+    def __init__(self):
+        import torch
+        from cuda.bindings import driver as drv
+        self._drv = drv
+        self._flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+        err, dptr = drv.cuMemHostGetDevicePointer(self._flag.data_ptr(), 0)
+        if err != drv.CUresult.CUDA_SUCCESS:
+            raise RuntimeError(f"cuMemHostGetDevicePointer: {err}")
+        self._dptr = dptr
+
+    def close(self, stream):
+        drv = self._drv
+        self._flag[0] = 0
+        (err,) = drv.cuStreamWaitValue32(stream.cuda_stream, self._dptr, 1,
+                                         drv.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_EQ)
+        if err != drv.CUresult.CUDA_SUCCESS:
+            raise RuntimeError(f"cuStreamWaitValue32: {err}")
+
+    def open(self):
+        self._flag[0] = 1
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -213,8 +242,10 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-lib", action="store_true", help="skip the library int8 GEMM timing")
     ap.add_argument("--sets", type=int, default=0, help="number of rotating input sets (0 = enough to exceed L2)")
-    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
-                    help="replay the timed steps from one CUDA graph (auto: for the launch-bound workloads cfg1 and cfg4)")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off", "gate"],
+                    help="on: replay the timed steps from one CUDA graph (auto: for the launch-bound workloads cfg1 and "
+                         "cfg4 on one GPU); gate: one call per step, the first ones queued behind a stream gate before "
+                         "the clock starts (auto: GEMM workloads on several GPUs)")
     ap.add_argument("--splitk-exchange", default="fused", choices=["fused", "nccl"],
                     help="cfg5_splitk: partial sums added into the owners' shards by the GEMM epilogue over peer "
                          "memory (fused), or a full partial matrix followed by NCCL reduce-scatter (nccl)")
@@ -254,15 +285,26 @@ def main() -> int:
     # launch-bound workloads: the K steps are recorded once and replayed as one CUDA graph, so the timed
     # region measures the GPU and not the interpreter issuing 5 us calls
     # ... and with several ranks, where one rank's interpreter falling behind would set the job's time
-    use_graph = args.graph == "on" or (args.graph == "auto" and (
-        (args.workload in ("cfg1", "cfg4") and world == 1) or
-        (world > 1 and wl["kind"] in ("i8_srs", "i8_i32", "bf16"))))
-    if use_graph:
+    # Several ranks run call by call as one GPU does (a graph replay loses the overlap of consecutive launches:
+    # 50.3 against 48.0 us per step), but the stream is held at a gate until the first calls are queued, so that
+    # the interpreter is ahead of the GPU when the clock starts; if the gate cannot be set up, a graph is used.
+    use_gate = args.graph == "gate" or (args.graph == "auto" and world > 1 and wl["kind"] in ("i8_srs", "i8_i32", "bf16"))
+    use_graph = args.graph == "on" or (args.graph == "auto" and args.workload in ("cfg1", "cfg4") and world == 1)
+    gate, gate_fallback = None, None
+    if use_gate:
+        try:
+            gate = StreamGate()
+        except Exception as exc:  # noqa: BLE001
+            use_gate, use_graph = False, True
+            gate_fallback = f"{type(exc).__name__}: {exc}"[:160]
+    if use_graph or use_gate:
         side = torch.cuda.Stream()
         torch.cuda.set_stream(side)        # calls are bound to the stream current at bind time
 
     # ---------------------------------------------------------------- build the per-rank workload
     extra = {}
+    if gate_fallback:
+        extra["gate_fallback"] = gate_fallback
     if kind == "conv":
         n, h, w, cin, cout = wl["n"], wl["h"], wl["w"], wl["cin"], wl["cout"]
         nsets = 8
@@ -419,12 +461,29 @@ def main() -> int:
     launches0 = ctx.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    e0.record()
-    if graph is not None:
-        graph.replay()
+    if gate is not None:
+        try:
+            gate.close(side)             # everything queued from here on waits for gate.open()
+        except Exception as exc:  # noqa: BLE001  -- no gate on this system: plain call-by-call run
+            extra["gate_fallback"] = f"{type(exc).__name__}: {exc}"[:160]
+            gate = None
+    if gate is not None:
+        try:
+            e0.record()
+            head = min(K_steps, GATE_HEAD)
+            for i in range(K_steps):
+                if i == head:
+                    gate.open()
+                step(i)
+        finally:
+            gate.open()
     else:
-        for i in range(K_steps):
-            step(i)
+        e0.record()
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(K_steps):
+                step(i)
     e1.record()
     barrier()
     elapsed_ms = e0.elapsed_time(e1)
@@ -488,7 +547,9 @@ def main() -> int:
         "higher_is_better": True, "scaling": wl["scaling"], "vs_baseline": None, "dtype": dtype, "data": "synthetic",
         "config": {"workload": wl["desc"], "per_gpu": f"M={m_local} N={n_dim} K={k_dim}", "parallelism": f"row-shard x{world}",
                    "l2": l2_note, "tile_n": args.tile_n or "auto",
-                   "launch": "the K steps replayed from one CUDA graph" if use_graph else "one C-ABI call per step"},
+                   "launch": "the K steps replayed from one CUDA graph" if use_graph else
+                             (f"one C-ABI call per step, the first {min(K_steps, GATE_HEAD)} queued behind a stream gate before the clock starts"
+                              if gate is not None else "one C-ABI call per step")},
         "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches), "device_status": int(status),
     }
     if e2e is not None:
