@@ -46,6 +46,9 @@ WORKLOADS = {
                  desc="int8 conv2d NHWC 1x56x56x64, 3x3x64x64 HWIO, stride 1 pad 1, per-channel srs 6"),
     "cfg5": dict(M=65536, N=8192, K=8192, kind="i8_i32", scaling="strong",
                  desc="int8 GEMM 65536x8192x8192 -> int32, rows of A/C sharded over the GPUs"),
+    "shallow_k": dict(M=16384, N=4096, K=512, kind="i8_i32", scaling="weak", bound="hbm",
+                      desc="int8 GEMM 16384x4096x512 -> int32: 268 MB of results over 4 K blocks, the output stage "
+                           "sets the pace (two groups of epilogue warps)"),
     "cfg5_splitk": dict(M=65536, N=8192, K=8192, kind="i8_i32_splitk", splitk=8, scaling="strong",
                         desc="int8 GEMM 65536x8192x8192 -> int32, split-K 8 over the GPUs, int32 partial sums "
                              "exchanged between the GPUs (how: splitk_exchange)"),
@@ -517,6 +520,13 @@ def main() -> int:
                     "note": (f"peak = 2 x measured bf16 {which} (kind::i8 has twice the K per instruction)"
                              if dtype != "bf16" else f"peak = measured bf16 {which}") +
                             f", of {peaks['source']}; timed region {elapsed_ms:.0f} ms"}
+    if wl.get("bound") == "hbm" and kind != "conv":
+        # a product over a shallow K: the result bytes, not the MMAs, bound the launch
+        gemm_bytes = wl["M"] * wl["K"] + wl["N"] * wl["K"] + wl["M"] * wl["N"] * 4
+        gbs = gemm_bytes / (per_launch_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                    "note": f"algorithmic bytes A + B + C(int32) = {gemm_bytes / 1e6:.1f} MB per launch; peak {peaks['source']}"}
     if kind == "mm_i32":
         # one int32 product costs ten int8 limb products (K + 2K + 3K + 4K bytes of depth)
         roofline["achieved"] = achieved * 10.0
