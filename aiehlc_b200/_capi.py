@@ -17,7 +17,7 @@ ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE, ERR_NOMEM = -1, -2, -3, -4, 
 _i32p = C.POINTER(C.c_int32)
 _vp = C.c_void_p
 
-# name -> (restype, argtypes); every symbol include/aiehlc_b200.h declares
+# name -> (restype, argtypes); every symbol include/aiehlc_b200.h and include/aiehlc_b200_tuning.h declare
 SIGNATURES = {
     "aiehlc_create": (C.c_int, [C.c_int, C.POINTER(_vp)]),
     "aiehlc_destroy": (C.c_int, [_vp]),
@@ -45,6 +45,7 @@ SIGNATURES = {
     "aiehlc_set_cta_pair": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_debug": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_pdl": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_set_cta_limit": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_group_m": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_split_tail": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_tma_store": (C.c_int, [_vp, C.c_int]),
@@ -62,6 +63,7 @@ SIGNATURES = {
     "aiehlc_set_trace": (C.c_int, [_vp, _vp]),
     "aiehlc_set_cta_times": (C.c_int, [_vp, _vp]),
     "aiehlc_launch_count": (C.c_longlong, [_vp]),
+    "aiehlc_workspace_generation": (C.c_longlong, [_vp]),
 }
 
 

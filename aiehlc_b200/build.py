@@ -2,6 +2,8 @@
 
     python -m aiehlc_b200.build            # build if sources are newer than the library
     python -m aiehlc_b200.build --force
+    AIEHLC_MEASURE=1 python -m aiehlc_b200.build   # libaiehlc_b200_measure.so: kernels with clock stamps and
+                                                   # the debug modes that skip part of a kernel (-DAIEHLC_MEASURE)
 
 nvcc cross-compiles without a GPU, so this also runs on a CPU-only machine.
 """
@@ -17,9 +19,10 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
-OBJ_DIR = PKG / "_obj"
+MEASURE = os.environ.get("AIEHLC_MEASURE", "0") not in ("", "0")
+OBJ_DIR = PKG / ("_obj_measure" if MEASURE else "_obj")
 LIB_DIR = PKG / "lib"
-LIB_PATH = LIB_DIR / "libaiehlc_b200.so"
+LIB_PATH = LIB_DIR / ("libaiehlc_b200_measure.so" if MEASURE else "libaiehlc_b200.so")
 
 CUDA_SOURCES = ["capi.cu", "gemm_launch.cu", "simt_kernels.cu", "conv_tcgen05.cu"]
 CXX_SOURCES = ["xaie_runtime.cpp"]
@@ -55,7 +58,8 @@ def needs_build() -> bool:
 
 def _compile(src: Path, verbose: bool) -> Path:
     obj = OBJ_DIR / (src.name + ".o")
-    cmd = [nvcc_path(), *NVCC_FLAGS, "-I", str(INCLUDE), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc_path(), *NVCC_FLAGS, *(["-DAIEHLC_MEASURE"] if MEASURE else []),
+           "-I", str(INCLUDE), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -104,14 +108,6 @@ def build_examples() -> list[Path]:
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"example {src.name} failed to build:\n{res.stderr}")
-        outs.append(out)
-    for src in sorted(EXAMPLES_DIR.glob("*.cu")):     # stand-alone CUDA measurement programs
-        out = EXAMPLES_BIN / src.stem
-        if not (out.exists() and out.stat().st_mtime > src.stat().st_mtime):
-            cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", str(src), "-o", str(out)]
-            res = subprocess.run(cmd, capture_output=True, text=True)
-            if res.returncode != 0:
-                raise RuntimeError(f"example {src.name} failed to build:\n{res.stderr}")
         outs.append(out)
     return outs
 

@@ -1,8 +1,11 @@
 // extern "C" entry points declared in include/aiehlc_b200.h.
 #include <cstdio>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
 
+#include "../../include/aiehlc_b200_tuning.h"
 #include "context.h"
 #include "gemm_tcgen05.cuh"
 
@@ -22,7 +25,10 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 int DevBuf::reserve(size_t need) {
   if (need <= bytes) return 0;
-  if (ptr) cudaFree(ptr);
+  if (ptr) {
+    cudaFree(ptr);
+    if (generation) ++*generation;  // whoever recorded the old address must not use it again
+  }
   ptr = nullptr;
   bytes = 0;
   const size_t want = (need + (1u << 20) - 1) & ~static_cast<size_t>((1u << 20) - 1);
@@ -39,6 +45,20 @@ void DevBuf::release() {
   if (ptr) cudaFree(ptr);
   ptr = nullptr;
   bytes = 0;
+}
+
+int ensure_dynamic_smem(int device, const void* func, int bytes, int* cached) {
+  if (cached && *cached >= bytes) return AIEHLC_OK;
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, int> limit;  // (device, kernel) -> bytes already granted
+  std::lock_guard<std::mutex> lk(mu);
+  int& have = limit[{device, func}];
+  if (have < bytes) {
+    AIEHLC_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    have = bytes;
+  }
+  if (cached) *cached = have;
+  return AIEHLC_OK;
 }
 
 static int check_ctx(aiehlc_ctx* ctx) {
@@ -80,6 +100,9 @@ int aiehlc_create(int device, aiehlc_ctx** out) {
   aiehlc_ctx* ctx = new aiehlc_ctx();
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
+  for (DevBuf* b : {&ctx->buf_a, &ctx->buf_b, &ctx->buf_c, &ctx->buf_aux, &ctx->pack_a, &ctx->pack_b, &ctx->limb_a,
+                    &ctx->limb_b, &ctx->sk_scratch, &ctx->sk_flags, &ctx->shard_maps})
+    b->generation = &ctx->workspace_generation;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
   e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -134,6 +157,9 @@ int aiehlc_destroy(aiehlc_ctx* ctx) {
 
 int aiehlc_sm_count(const aiehlc_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 long long aiehlc_launch_count(const aiehlc_ctx* ctx) { return ctx ? ctx->launches : 0; }
+long long aiehlc_workspace_generation(const aiehlc_ctx* ctx) {
+  return ctx ? static_cast<long long>(ctx->workspace_generation) : 0;
+}
 
 int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
@@ -251,20 +277,34 @@ int aiehlc_set_group_m(aiehlc_ctx* ctx, int group_m) {
   return AIEHLC_OK;
 }
 
+int aiehlc_set_cta_limit(aiehlc_ctx* ctx, int sms) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (sms < 0) return fail(AIEHLC_ERR_INVALID, "cta_limit must be >= 0");
+  ctx->cta_limit = sms;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_pdl(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   ctx->pdl = on ? 1 : 0;
   return AIEHLC_OK;
 }
 
+static int need_measure_build(const char* what) {
+  if (kMeasure) return AIEHLC_OK;
+  return fail(AIEHLC_ERR_UNSUPPORTED, std::string(what) + ": this library was built without AIEHLC_MEASURE");
+}
+
 int aiehlc_set_cta_times(aiehlc_ctx* ctx, long long* device_buffer) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (device_buffer) if (int rc = need_measure_build("aiehlc_set_cta_times")) return rc;
   ctx->cta_times = device_buffer;
   return AIEHLC_OK;
 }
 
 int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (device_buffer) if (int rc = need_measure_build("aiehlc_set_trace")) return rc;
   ctx->trace = device_buffer;
   return AIEHLC_OK;
 }
@@ -272,6 +312,7 @@ int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer) {
 int aiehlc_set_debug(aiehlc_ctx* ctx, int mode) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   if (mode < 0 || mode > 5) return fail(AIEHLC_ERR_INVALID, "debug mode must be 0..5");
+  if (mode != 0 && mode != 3) if (int rc = need_measure_build("aiehlc_set_debug (modes 1, 2, 4, 5)")) return rc;
   ctx->debug_mode = mode;
   return AIEHLC_OK;
 }

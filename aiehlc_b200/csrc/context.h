@@ -27,9 +27,16 @@ int cuda_fail(cudaError_t e, const char* what);
 struct DevBuf {
   void* ptr = nullptr;
   size_t bytes = 0;
+  unsigned long long* generation = nullptr;  // bumped whenever the buffer moves (see aiehlc_ctx::workspace_generation)
   int reserve(size_t need);
   void release();
 };
+
+// Raises the dynamic shared-memory limit of kernel `func` on `device` to at least `bytes`.  The limit
+// belongs to the device and the function, not to a context, and a launch that needs more than the
+// current value fails: it is therefore kept in one process-wide table and only ever raised.
+// `cached` is the caller's own copy of the value (fast path: no lock once it is large enough).
+int ensure_dynamic_smem(int device, const void* func, int bytes, int* cached);
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -79,11 +86,16 @@ struct aiehlc_ctx {
   int conv_split_weights = 1;   // patch form: one weight box per filter row, each on its own barrier
   int conv_hwio_direct = 1;     // conv consumes HWIO weights as an N-major operand where it can (no re-layout launch)
   int conv_halo = 1;            // conv kernel fetches a tile's whole input patch and all taps' weights in two boxes
+  int cta_limit = 0;            // persistent GEMM kernels occupy at most this many SMs (0 = all of them)
+  int usable_sms() const { return cta_limit > 0 && cta_limit < sm_count ? cta_limit : sm_count; }
   int pdl = 1;                  // launch the tensor-core kernels with programmatic stream serialization
   int debug_mode = 0;           // see GemmParams::debug
   long long* cta_times = nullptr;  // see GemmParams::cta_times (device pointer owned by the caller)
   long long* trace = nullptr;   // see GemmParams::trace (device pointer owned by the caller)
   long long launches = 0;
+  // counts re-allocations of the context's device workspaces: a recorded CUDA graph that holds pointers
+  // into them is stale once this has moved on
+  unsigned long long workspace_generation = 0;
   std::unordered_map<const void*, aiehlc::KernelSetup> kernel_setup;
   // staging for *_host entry points and for operands that TMA cannot address directly
   aiehlc::DevBuf buf_a, buf_b, buf_c, buf_aux, pack_a, pack_b;
@@ -139,8 +151,11 @@ int launch_repack(aiehlc_ctx* ctx, const void* src, void* dst, long long rows, l
                   long long ld_src, long long ld_dst, int esize, cudaStream_t st);
 
 // implicit-GEMM conv (conv_tcgen05.cu)
+// `weight_scratch`: where re-laid weights ([tap][cout][cin], kh*kw*cin*cout bytes) are kept when the
+// shape needs them; null = the context's growing workspace.
 int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
-                  int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st);
+                  int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st,
+                  int8_t* weight_scratch = nullptr);
 
 bool conv_tensor_path(const int8_t* x, int cin, int cout);
 int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, int kh, int kw, int pad,

@@ -64,7 +64,7 @@ struct ConvParams {
   int8_t* y;
   const uint8_t* shift_vec;
   int* status;
-  long long* trace;   // measurement aid: clock64 stamps of CTA 0, or null
+  long long* trace;   // kMeasure: clock64 stamps of CTA 0, or null
 };
 
 __global__ void __launch_bounds__(kConvThreads, 1)
@@ -87,7 +87,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long entry_clock = clock64();
-  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+  const bool tracing = kMeasure && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -402,7 +402,8 @@ bool conv_hwio_direct(const aiehlc_ctx* ctx, const int8_t* w, int n, int h, int 
                       int pad);
 
 int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
-                  int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
+                  int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st,
+                  int8_t* weight_scratch) {
   const bool tensor_ok = conv_tensor_path(x, cin, cout);
   if (!tensor_ok) {
     const long long total = static_cast<long long>(n) * h * wd * cout;
@@ -420,10 +421,15 @@ int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, 
     return launch_conv_tensor(ctx, x, w, true, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec, st);
   const int taps = kh * kw;
   const size_t wbytes = static_cast<size_t>(taps) * cin * cout;
-  if (ctx->pack_b.reserve(wbytes)) return AIEHLC_ERR_NOMEM;
-  if (int rc = launch_conv_pack_weights(ctx, w, static_cast<int8_t*>(ctx->pack_b.ptr), taps, cin, cout, st)) return rc;
-  return launch_conv2d_packed(ctx, x, static_cast<const int8_t*>(ctx->pack_b.ptr), y, n, h, wd, cin, cout, kh, kw, pad,
-                              shift_vec, st);
+  int8_t* packed = weight_scratch;
+  if (packed == nullptr) {
+    if (ctx->pack_b.reserve(wbytes)) return AIEHLC_ERR_NOMEM;
+    packed = static_cast<int8_t*>(ctx->pack_b.ptr);
+  }
+  // every byte the convolution kernel reads ([0, wbytes)) is rewritten here: nothing an earlier call
+  // left in the scratch can reach this one
+  if (int rc = launch_conv_pack_weights(ctx, w, packed, taps, cin, cout, st)) return rc;
+  return launch_conv2d_packed(ctx, x, packed, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec, st);
 }
 
 // Tiling of the tensor-core kernel for the problem already written into p (n .. pad): fills the tile,
@@ -642,10 +648,8 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
 
   const int smem_bytes = p.stages * p.stage_bytes + 1024 + 8192 + 1024;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(conv2d_i8_kernel)];
-  if (ks.smem_attr < smem_bytes) {
-    AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    ks.smem_attr = smem_bytes;
-  }
+  if (int rc = ensure_dynamic_smem(ctx->device, reinterpret_cast<const void*>(conv2d_i8_kernel), smem_bytes, &ks.smem_attr))
+    return rc;
   dim3 grid(n * p.tiles_h * p.tiles_w, n_tiles);
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];
@@ -703,112 +707,18 @@ int static_weights_address(int device, int8_t** out) {
 }
 }  // namespace
 
-// Same two kernels as launch_conv2d, with the packed weights in the static array.
+// The regular launcher -- same forms, same tiling (configure_conv), same kernels -- with the re-laid
+// weights, where the shape needs them, in the static array instead of the context's workspace.
 int launch_conv2d_static(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
                          int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st) {
-  const int taps = kh * kw;
-  const size_t wbytes = static_cast<size_t>(taps) * cin * cout;
+  const size_t wbytes = static_cast<size_t>(kh) * kw * cin * cout;
   if (wbytes > kConvStaticScratchBytes)
     return fail(AIEHLC_ERR_UNSUPPORTED,
                 "conv2d (static scratch): kh*kw*cin*cout = " + std::to_string(wbytes) + " bytes of weights exceed the " +
                     std::to_string(kConvStaticScratchBytes) + "-byte static scratch; use aiehlc_conv2d_i8_srs_dev");
-  const bool tensor_ok = (cin % 32 == 0) && (cin == 32 || cin == 64 || cin % 128 == 0) && (cout % 16 == 0) &&
-                         (reinterpret_cast<uintptr_t>(x) % 16 == 0);
-  if (!tensor_ok) {
-    // the direct kernel needs no scratch at all
-    const long long total = static_cast<long long>(n) * h * wd * cout;
-    long long g = (total + 255) / 256;
-    if (g > ctx->sm_count * 16LL) g = ctx->sm_count * 16LL;
-    conv2d_i8_direct_kernel<<<static_cast<int>(g), 256, 0, st>>>(x, w, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec);
-    AIEHLC_CUDA(cudaGetLastError());
-    ctx->launches++;
-    return AIEHLC_OK;
-  }
   int8_t* packed = nullptr;
-  int rc = static_weights_address(ctx->device, &packed);
-  if (rc) return rc;
-  {
-    // Every byte the second kernel reads ([0, wbytes)) is rewritten here, so nothing left by an
-    // earlier call can leak into this one and nothing has to be cleared.
-    long long g = (static_cast<long long>(wbytes) + 255) / 256;
-    if (g > ctx->sm_count * 8LL) g = ctx->sm_count * 8LL;
-    conv_weight_prepack_kernel<<<static_cast<int>(g), 256, 0, st>>>(w, packed, taps, cin, cout);
-    AIEHLC_CUDA(cudaGetLastError());
-    ctx->launches++;
-  }
-
-  ConvParams p{};
-  p.n = n; p.h = h; p.w = wd; p.cin = cin; p.cout = cout; p.kh = kh; p.kw = kw; p.pad = pad;
-  p.wt = wd <= kBlockM ? wd : kBlockM;
-  p.rows_per_tile = wd <= kBlockM ? kBlockM / wd : 1;
-  if (p.rows_per_tile > h) p.rows_per_tile = h;
-  p.tiles_w = (wd + p.wt - 1) / p.wt;
-  p.tiles_h = (h + p.rows_per_tile - 1) / p.rows_per_tile;
-  p.chunk = cin >= 128 ? 128 : cin;
-  p.chunks_per_tap = cin / p.chunk;
-  p.cout_tile = cout <= 256 ? cout : 256;
-  if (cout > 256 && cout % 256 != 0) {
-    int ct = 256;
-    while (ct > 16 && cout % ct != 0) ct -= 16;
-    p.cout_tile = ct;
-  }
-  const int n_tiles = (cout + p.cout_tile - 1) / p.cout_tile;
-  p.swizzle_code = p.chunk == 128 ? 2u : (p.chunk == 64 ? 4u : 6u);
-  p.sbo_bytes = 8u * p.chunk;
-  p.a_bytes = kBlockM * p.chunk;
-  const int b_bytes = (p.cout_tile * p.chunk + 1023) / 1024 * 1024;
-  p.stage_bytes = p.a_bytes + b_bytes;
-  p.tx_bytes = static_cast<uint32_t>(p.chunk) * (p.wt * p.rows_per_tile + p.cout_tile);
-  p.row_w = p.wt;  // one K block per tap and channel chunk (the form this entry point was written for)
-  p.b_swizzle_code = p.swizzle_code; p.b_sbo_bytes = p.sbo_bytes; p.b_kstep = kUmmaKBytes >> 4;
-  int stages = (200 * 1024) / p.stage_bytes;
-  if (stages > kConvMaxStages) stages = kConvMaxStages;
-  if (stages > taps * p.chunks_per_tap) stages = taps * p.chunks_per_tap;
-  p.stages = stages;
-  uint32_t cols = 32;
-  while (cols < static_cast<uint32_t>(p.cout_tile)) cols <<= 1;
-  p.tmem_cols = cols;
-  p.y = y; p.shift_vec = shift_vec; p.status = ctx->d_status;
-  p.trace = ctx->trace;
-
-  CUtensorMap mx, mw;
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUtensorMapSwizzle sw = p.chunk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                : p.chunk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
-  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(wd), static_cast<cuuint64_t>(h),
-                              static_cast<cuuint64_t>(n)};
-  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(cin) * wd,
-                                 static_cast<cuuint64_t>(cin) * wd * h};
-  const cuuint32_t box[4] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.wt),
-                             static_cast<cuuint32_t>(p.rows_per_tile), 1};
-  CUresult r = ctx->encode(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(x), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv input");
-  const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(cin), static_cast<cuuint64_t>(taps) * cout};
-  const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(cin)};
-  const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(p.chunk), static_cast<cuuint32_t>(p.cout_tile)};
-  r = ctx->encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, packed, wdims, wstrides, wbox, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
-
-  const int smem_bytes = p.stages * p.stage_bytes + 1024 + 8192 + 1024;
-  AIEHLC_CUDA(cudaFuncSetAttribute(conv2d_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-  dim3 grid(n * p.tiles_h * p.tiles_w, n_tiles);
-  cudaLaunchConfig_t cfg{};
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(kConvThreads);
-  cfg.dynamicSmemBytes = smem_bytes;
-  cfg.stream = st;
-  cfg.attrs = attr;
-  cfg.numAttrs = ctx->pdl ? 1 : 0;
-  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, conv2d_i8_kernel, mx, mw, p));
-  ctx->launches++;
-  return AIEHLC_OK;
+  if (int rc = static_weights_address(ctx->device, &packed)) return rc;
+  return launch_conv2d(ctx, x, w, y, n, h, wd, cin, cout, kh, kw, pad, shift_vec, st, packed);
 }
 
 }  // namespace aiehlc

@@ -127,7 +127,7 @@ void narrow_tail(int tiles, int slots, int tile_n, int enabled, int* first, int*
 int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* out) {
   const int cand[3] = {256, 128, 64};
   const double eff[3] = {1.0, 0.60, 0.35};
-  const int sms = ctx->sm_count;
+  const int sms = ctx->usable_sms();
   const int esize = kind == KIND_I8 ? 1 : 2;
   aiehlc_gemm_plan best{};
   double best_cost = -1;
@@ -138,7 +138,7 @@ int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_
     for (int i = 0; i < 3; ++i) {
       const int bn = cand[i];
       if (ctx->force_tile_n && bn != ctx->force_tile_n) continue;
-      if (pr == 1 && bn == 64) continue;
+      if (pr == 1 && (bn == 64 || sms < 2)) continue;
       const int tm = pr ? kPairM : kBlockM;
       aiehlc_gemm_plan pl{};
       pl.tile_m = tm;
@@ -265,12 +265,9 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
 
   auto kern = gemm_tn_kernel<kKind, kBN, kEpi>;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
-  if (ks.smem_attr < S::kTotal) {
-    AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-    ks.smem_attr = S::kTotal;
-  }
+  if (int rc2 = ensure_dynamic_smem(ctx->device, reinterpret_cast<const void*>(kern), S::kTotal, &ks.smem_attr)) return rc2;
   const int tiles = p.num_m_blocks * p.num_n_blocks;
-  int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  int grid = tiles < ctx->usable_sms() ? tiles : ctx->usable_sms();
   if (p.rot_shards > 0) grid = coprime_slots(grid, p.rot_shards);
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];
@@ -338,12 +335,10 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
 
   auto kern = gemm_tn_pair_kernel<kKind, kBN, kEpi, kKPer, kEpiGroups>;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
-  if (ks.smem_attr < S::kTotal) {
-    AIEHLC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-    ks.smem_attr = S::kTotal;
-  }
+  if (int rc2 = ensure_dynamic_smem(ctx->device, reinterpret_cast<const void*>(kern), S::kTotal, &ks.smem_attr)) return rc2;
   const int tiles = p.num_m_blocks * p.num_n_blocks;
   int max_pairs = ctx->sm_count / 2;
+  const int pair_limit = ctx->usable_sms() / 2 > 0 ? ctx->usable_sms() / 2 : 1;
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -371,7 +366,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
     }
     cfg.numAttrs = na;
   }
-  max_pairs = ks.max_clusters;
+  max_pairs = ks.max_clusters < pair_limit ? ks.max_clusters : pair_limit;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
   // Tail balancing (int32 accumulation only: sums of partial sums are exact; fp32 would change rounding)
   p.sk_first_tile = tiles;

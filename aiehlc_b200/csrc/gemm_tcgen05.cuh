@@ -43,6 +43,14 @@ constexpr int kStoreStagingBytes = 4 * 2 * kStoreBufBytes;
 
 constexpr int kMaxShards = 16;
 
+// Clock stamps and the debug modes that skip part of a kernel exist only in libraries built with
+// -DAIEHLC_MEASURE; in the regular build kMeasure is a constant false and those branches are gone.
+#ifdef AIEHLC_MEASURE
+constexpr bool kMeasure = true;
+#else
+constexpr bool kMeasure = false;
+#endif
+
 struct GemmParams {
   int M, N, K;
   void* C;                 // int32 / int8 / bf16, row-major, leading dimension ldc (elements)
@@ -86,12 +94,12 @@ struct GemmParams {
   // int32 products on the int8 tensor cores (see launch_mm_i32_tensor): operands are unsigned bytes and
   // the int32 result is shifted left (wrapping) before it is stored or added.
   int unsigned_ab, out_shift;
-  long long* cta_times;    // measurement aid (pair kernel): global nanosecond timer at entry / exit of every CTA, or null
-  long long* trace;        // measurement aid: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
-  int debug;               // measurement aid: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling),
-                           // 4 = int32 results staged but their tile stores not issued, 5 = no output stage;
-                           // test aid: 3 = the producer neither loads nor signals, so every consumer wait
-                           // runs out and the kernel leaves through its bounded-wait exit
+  long long* cta_times;    // kMeasure (pair kernel): global nanosecond timer at entry / exit of every CTA, or null
+  long long* trace;        // kMeasure: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
+  int debug;               // test aid: 3 = the producer neither loads nor signals, so every consumer wait
+                           // runs out and the kernel leaves through its bounded-wait exit;
+                           // kMeasure: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling),
+                           // 4 = int32 results staged but their tile stores not issued, 5 = no output stage
 };
 
 // Shift-round-saturate, pure integer: round half to even on the dropped bits, saturate to int8.
@@ -267,7 +275,7 @@ template <int kEpi, int kBN, bool kForceDirect = false>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[32], int row, int col0, bool row_ok,
                                             StoreCtx& sc) {
   const int ncols = min(32, p.N - col0);
-  if (p.debug == 5) return;
+  if (kMeasure && p.debug == 5) return;
   if constexpr (kEpi == EPI_I32 || kEpi == EPI_I32_ACC) {
     if (p.out_shift) {
 #pragma unroll
@@ -278,7 +286,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
       return;
     }
     if (!kForceDirect && p.tma_store) {
-      tma_emit<128, 128, kEpi == EPI_I32_ACC>(sc, r, col0, p.debug != 4);
+      tma_emit<128, 128, kEpi == EPI_I32_ACC>(sc, r, col0, !(kMeasure && p.debug == 4));
       return;
     }
     int32_t* dst = static_cast<int32_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
@@ -465,7 +473,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const uint32_t tmem_base = *tmem_base_slot;
   pdl_launch_dependents();
   pdl_wait();  // from here on global memory may be read and written
-  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (kMeasure && p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
     p.trace[5] = entry_clock;
     p.trace[7] = static_cast<long long>(entry_ns);
   }
@@ -486,8 +494,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                          ST_TIMEOUT_EMPTY);
           if (!ok) break;
           const uint32_t fb = smem_u32(&full_bar[stage]);
-          if (p.debug == 1 || p.debug == 3) {
-            if (p.debug == 1) mbar_arrive(fb);
+          if ((kMeasure && p.debug == 1) || p.debug == 3) {
+            if (kMeasure && p.debug == 1) mbar_arrive(fb);
             if (++stage == kStages) { stage = 0; phase ^= 1; }
             continue;
           }
@@ -523,7 +531,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                        ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
-        if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
+        if (kMeasure && p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
@@ -533,7 +541,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t sb = sa + S::kABytes;
           const uint64_t adesc = make_kmajor_desc(sa, 1024, 2);
           const uint64_t bdesc = make_kmajor_desc(sb, 1024, 2);
-          if (p.debug != 2) {
+          if (!(kMeasure && p.debug == 2)) {
 #pragma unroll
             for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
               // K-step inside the swizzle span: advance the start-address field by 32 B (>>4 = 2).
@@ -545,7 +553,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));
-        if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 1] = clock64();
+        if (kMeasure && p.trace && blockIdx.x == 0) p.trace[it * 8 + 1] = clock64();
       }
     }
   } else {
@@ -560,7 +568,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tile_coords(t, p, mb, nb);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const bool tracer = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0;
+      const bool tracer = kMeasure && p.trace && blockIdx.x == 0 && warp == 2 && lane == 0;
       if (tracer) p.trace[it * 8 + 2] = clock64();
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status,
                      ST_TIMEOUT_TMEM_FULL);
@@ -589,7 +597,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, kTmemCols);
   }
-  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (kMeasure && p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
     p.trace[6] = clock64();
     p.trace[15] = static_cast<long long>(globaltimer_ns());
   }

@@ -183,7 +183,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const uint32_t tmem_base = *tmem_base_slot;
   pdl_launch_dependents();
   pdl_wait();  // from here on global memory may be read and written
-  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (kMeasure && p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
     p.trace[5] = entry_clock;
     p.trace[7] = static_cast<long long>(entry_ns);
   }
@@ -204,8 +204,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
           if (!ok) break;
           const uint32_t fb_local = smem_u32(&full_bar[stage]);
-          if (p.debug == 1 || p.debug == 3) {
-            if (p.debug == 1 && leader) mbar_arrive(fb_local);
+          if ((kMeasure && p.debug == 1) || p.debug == 3) {
+            if (kMeasure && p.debug == 1 && leader) mbar_arrive(fb_local);
             if (++stage == kStages) { stage = 0; phase ^= 1; }
             continue;
           }
@@ -247,7 +247,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                        ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
-        if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
+        if (kMeasure && p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         const uint32_t idesc = make_idesc<kKind>(kPairM, kBN / w.n_parts) &
                                ~(p.unsigned_ab ? ((1u << 7) | (1u << 10)) : 0u);  // bits 7, 10: signed A, B
@@ -258,7 +258,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
           const uint32_t sb = sa + S::kABytes;
-          if (p.debug != 2) {
+          if (!(kMeasure && p.debug == 2)) {
 #pragma unroll
             for (int kk = 0; kk < kKPer; ++kk) {
               if (kb + kk >= w.kb1) break;  // K blocks of this stage beyond the range: loaded, not multiplied
@@ -274,7 +274,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit_pair_mask(smem_u32(&tmem_full_bar[acc]), 3);
-        if (p.trace && blockIdx.x == 0) p.trace[it * 8 + 1] = clock64();
+        if (kMeasure && p.trace && blockIdx.x == 0) p.trace[it * 8 + 1] = clock64();
       }
     }
   } else {
@@ -292,7 +292,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tile_coords(w.tile, p, mb, nb);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const bool tracer = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0;
+      const bool tracer = kMeasure && p.trace && blockIdx.x == 0 && warp == 2 && lane == 0;
       if (tracer) p.trace[it * 8 + 2] = clock64();
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xFFFFFFFFu, ok);
@@ -407,11 +407,11 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after();
     tmem_dealloc<2>(tmem_base, kTmemCols);
   }
-  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (kMeasure && p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
     p.trace[6] = clock64();
     p.trace[15] = static_cast<long long>(globaltimer_ns());
   }
-  if (p.cta_times && threadIdx.x == 0) {
+  if (kMeasure && p.cta_times && threadIdx.x == 0) {
     p.cta_times[2 * blockIdx.x] = static_cast<long long>(entry_ns);
     p.cta_times[2 * blockIdx.x + 1] = static_cast<long long>(globaltimer_ns());
   }

@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "../../include/aiehlc_b200.h"
+#include "../../include/aiehlc_b200_tuning.h"
 #include "../../include/aiehlc_kernels.h"
 #include "../../include/xaie_placeholder.h"
 #include "../../include/xaiengine.h"
@@ -88,6 +89,7 @@ struct Tile {
   bool launched = false;
   bool armed = false;
   u64 in_bytes = 0;
+  u64 out_bytes = 0;     // bytes the kernel's last launch produced in its output window
   bool enabled = true;
 };
 
@@ -113,6 +115,9 @@ struct XAie_Graph {
   cudaGraphExec_t exec = nullptr;
   cudaEvent_t done = nullptr;
   bool launched = false;
+  // what the recorded device addresses depended on: see Runtime::generation
+  u64 rt_generation = 0;
+  long long ctx_generation = 0;
 };
 
 namespace {
@@ -126,10 +131,15 @@ struct Runtime {
   cudaStream_t stream = nullptr;
   std::map<u16, Tile> tiles;
   std::vector<XAie_MemInst*> mems;
+  std::mutex mems_mu;       // the list is also read by kernel calls of other threads looking for a buffer's owner
   std::vector<XAie_RoutingInstance*> routes;
   u64 launches = 0;
   u32 inject_status = 0, inject_count = 0;
   bool capturing = false;   // between XAie_GraphBeginCapture and XAie_GraphEndCapture
+  // Counts the times a tile window moved to a larger allocation.  A recorded graph holds raw device
+  // addresses of windows (and of the context's workspaces, which have their own counter); replaying it
+  // after either moved would touch freed memory, so XAie_GraphLaunch compares both counters first.
+  u64 generation = 0;
 
   bool is_shim(XAie_LocType l) const { return l.Row == dev->Cfg.ShimRowNum; }
   bool valid_loc(XAie_LocType l) const {
@@ -182,10 +192,13 @@ struct Runtime {
         cudaError_t e = cudaMalloc(&p, need);
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(tile window)");
         XCUDA(cudaMemcpyAsync(p, r->dptr, r->cap, cudaMemcpyDeviceToDevice, stream));
+        // like tile data memory, bytes nothing has written read as zero
+        XCUDA(cudaMemsetAsync(static_cast<uint8_t*>(p) + r->cap, 0, need - r->cap, stream));
         XCUDA(cudaStreamSynchronize(stream));
         cudaFree(r->dptr);
         r->dptr = p;
         r->cap = need;
+        ++generation;
       }
       *dptr = static_cast<uint8_t*>(r->dptr) + (addr - start);
       return XAIE_OK;
@@ -195,16 +208,24 @@ struct Runtime {
     r.cap = need;
     cudaError_t e = cudaMalloc(&r.dptr, need);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(tile window)");
-    if (start != addr) XCUDA(cudaMemsetAsync(r.dptr, 0, need, stream));
+    if (capturing) {
+      cudaFree(r.dptr);
+      return fail(XAIE_ERR, "a tile window would have to be created while a graph is being recorded; run the sequence once before recording it");
+    }
+    XCUDA(cudaMemsetAsync(r.dptr, 0, need, stream));  // unwritten bytes read as zero
     t.regions.push_back(r);
     *dptr = static_cast<uint8_t*>(r.dptr) + (addr - start);
     return XAIE_OK;
   }
 };
 
-// The device instance that kernel-call expressions (which carry no instance argument) run on:
-// the one initialised last.
-Runtime* g_current_rt = nullptr;
+// Kernel-call expressions carry no instance argument.  They run on the instance that owns the GMIO
+// buffer their input address lies in; the short host API, which names no instance either, uses the one
+// the CALLING THREAD initialised last.  Nothing here is shared between host threads except the list
+// below (under its mutex), so one device instance per thread needs no further locking.
+thread_local Runtime* g_current_rt = nullptr;
+std::mutex g_runtimes_mu;
+std::vector<Runtime*> g_runtimes;
 
 Runtime* rt_of(XAie_DevInst* d) { return d ? static_cast<Runtime*>(d->Priv) : nullptr; }
 
@@ -287,6 +308,7 @@ AieRC launch_tile(Runtime* rt, Tile& t, u32 count) {
   if (rc != XAIE_OK) return rc;
   info.out = op;
   info.out_bytes = ob;
+  t.out_bytes = ob;
   if (t.kernel.acc_addr) {
     if (Region* r = rt->find_region(t, t.kernel.acc_addr, 1)) {
       info.acc = static_cast<uint8_t*>(r->dptr) + (t.kernel.acc_addr - r->addr);
@@ -361,8 +383,20 @@ AieRC XAie_CfgInitialize(XAie_DevInst* DevInst, XAie_Config* ConfigPtr) {
   DevInst->Cfg = *ConfigPtr;
   DevInst->Backend = &DevInst->BackendStorage;
   DevInst->BackendStorage.Type = XAIE_IO_BACKEND_CUDA;
+  // Which GPU: XAie_SetCudaDevice if it was called; else the environment variable AIEHLC_DEVICE; else,
+  // when a partition was configured, the array's columns are dealt evenly over the visible GPUs and
+  // the partition runs on the GPU that owns its start column; else GPU 0.
   int device = 0;
-  if (const char* e = getenv("AIEHLC_DEVICE")) device = atoi(e);
+  if (DevInst->CudaDevicePlus1 > 0) {
+    device = DevInst->CudaDevicePlus1 - 1;
+  } else if (const char* e = getenv("AIEHLC_DEVICE")) {
+    device = atoi(e);
+  } else if (DevInst->PartNumCols > 0) {
+    int gpus = 0;
+    if (cudaGetDeviceCount(&gpus) != cudaSuccess) { cudaGetLastError(); gpus = 0; }
+    if (gpus > 1) device = static_cast<int>(DevInst->StartCol) * gpus / ConfigPtr->NumCols;
+    if (device >= gpus && gpus > 0) device = gpus - 1;
+  }
   aiehlc_ctx* ctx = nullptr;
   if (aiehlc_create(device, &ctx) != AIEHLC_OK) return fail(XAIE_INVALID_DEVICE, aiehlc_last_error());
   Runtime* rt = new Runtime();
@@ -378,7 +412,24 @@ AieRC XAie_CfgInitialize(XAie_DevInst* DevInst, XAie_Config* ConfigPtr) {
   DevInst->Priv = rt;
   DevInst->IsReady = 1;
   g_current_rt = rt;
+  {
+    std::lock_guard<std::mutex> lk(g_runtimes_mu);
+    g_runtimes.push_back(rt);
+  }
   return XAIE_OK;
+}
+
+AieRC XAie_SetCudaDevice(XAie_DevInst* DevInst, int Device) {
+  if (!DevInst) return fail(XAIE_INVALID_ARGS, "null device instance");
+  if (DevInst->IsReady && DevInst->Priv) return fail(XAIE_ERR, "XAie_SetCudaDevice: call it before XAie_CfgInitialize");
+  if (Device < 0) return fail(XAIE_INVALID_ARGS, "XAie_SetCudaDevice: negative device");
+  DevInst->CudaDevicePlus1 = Device + 1;
+  return XAIE_OK;
+}
+
+int XAie_GetCudaDevice(XAie_DevInst* DevInst) {
+  Runtime* rt = rt_of(DevInst);
+  return rt ? rt->device : -1;
 }
 
 AieRC XAie_SetIOBackend(XAie_DevInst* DevInst, XAie_BackendType Backend) {
@@ -403,6 +454,14 @@ AieRC XAie_PmRequestTiles(XAie_DevInst* DevInst, XAie_LocType*, u32) {
 AieRC XAie_PartitionTeardown(XAie_DevInst* DevInst) {
   if (!DevInst) return fail(XAIE_INVALID_ARGS, "null device instance");
   if (g_current_rt == rt_of(DevInst)) g_current_rt = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_runtimes_mu);
+    for (size_t i = 0; i < g_runtimes.size(); ++i)
+      if (g_runtimes[i] == rt_of(DevInst)) {
+        g_runtimes.erase(g_runtimes.begin() + i);
+        break;
+      }
+  }
   free_runtime(rt_of(DevInst));
   DevInst->Priv = nullptr;
   DevInst->IsReady = 0;
@@ -565,7 +624,10 @@ XAie_MemInst* XAie_MemAllocate(XAie_DevInst* DevInst, u64 Size, XAie_MemCachePro
       return nullptr;
     }
   }
-  rt->mems.push_back(m);
+  {
+    std::lock_guard<std::mutex> lk(rt->mems_mu);
+    rt->mems.push_back(m);
+  }
   return m;
 }
 
@@ -573,11 +635,14 @@ AieRC XAie_MemFree(XAie_MemInst* m) {
   if (!m) return fail(XAIE_INVALID_ARGS, "null buffer");
   Runtime* rt = m->rt;
   cudaStreamSynchronize(rt->stream);
-  for (size_t i = 0; i < rt->mems.size(); ++i)
-    if (rt->mems[i] == m) {
-      rt->mems.erase(rt->mems.begin() + i);
-      break;
-    }
+  {
+    std::lock_guard<std::mutex> lk(rt->mems_mu);
+    for (size_t i = 0; i < rt->mems.size(); ++i)
+      if (rt->mems[i] == m) {
+        rt->mems.erase(rt->mems.begin() + i);
+        break;
+      }
+  }
   if (m->mmapped) {
     cudaHostUnregister(m->host);
     munmap(m->host, m->map_bytes);
@@ -776,6 +841,8 @@ AieRC XAie_GraphEndCapture(XAie_DevInst* DevInst, XAie_Graph** Out) {
   XAie_Graph* gr = new XAie_Graph();
   gr->rt = rt;
   gr->graph = g;
+  gr->rt_generation = rt->generation;
+  gr->ctx_generation = aiehlc_workspace_generation(rt->ctx);
   e = cudaGraphInstantiate(&gr->exec, g, 0);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&gr->done, cudaEventDisableTiming);
   if (e != cudaSuccess) {
@@ -794,6 +861,9 @@ AieRC XAie_GraphLaunch(XAie_Graph* Graph) {
   Runtime* rt = Graph->rt;
   XCUDA(cudaSetDevice(rt->device));
   if (rt->capturing) return fail(XAIE_ERR, "cannot launch a graph while another one is being recorded");
+  if (Graph->rt_generation != rt->generation || Graph->ctx_generation != aiehlc_workspace_generation(rt->ctx))
+    return fail(XAIE_ERR, "graph is stale: a tile window or a workspace it recorded has since moved to a larger "
+                          "allocation; record it again");
   XCUDA(cudaGraphLaunch(Graph->exec, rt->stream));
   XCUDA(cudaEventRecord(Graph->done, rt->stream));
   Graph->launched = true;
@@ -836,6 +906,7 @@ AieRC XAie_GraphDestroy(XAie_Graph* Graph) {
 // call is the whole load / move-in / run / wait / move-out sequence on tile (colstart,rowstart):
 // `in` and `out` are addresses inside GMIO buffers (what XAie_MemGetDevAddr returns).
 static XAie_MemInst* find_mem(Runtime* rt, u64 addr, u64* offset) {
+  std::lock_guard<std::mutex> lk(rt->mems_mu);
   for (XAie_MemInst* m : rt->mems) {
     const u64 base = reinterpret_cast<u64>(m->host);
     if (addr >= base && addr < base + m->bytes) {
@@ -848,8 +919,21 @@ static XAie_MemInst* find_mem(Runtime* rt, u64 addr, u64* offset) {
 
 AieRC XAie_KernelCall(const void* kernel_key, const void* args, u32 args_bytes, int Col, int Row, int colstart,
                       int rowstart, u64 in_addr, u64 out_addr) {
-  Runtime* rt = g_current_rt;
-  if (!rt) return fail(XAIE_INVALID_DEVICE, "kernel call before XAie_CfgInitialize");
+  // the instance that owns the input buffer; the calling thread's own instance is tried first
+  Runtime* rt = nullptr;
+  {
+    u64 off0 = 0;
+    if (g_current_rt && find_mem(g_current_rt, in_addr, &off0)) rt = g_current_rt;
+    if (!rt) {
+      std::lock_guard<std::mutex> lk(g_runtimes_mu);
+      for (Runtime* r : g_runtimes)
+        if (find_mem(r, in_addr, &off0)) { rt = r; break; }
+    }
+  }
+  if (!rt) {
+    if (!g_current_rt) return fail(XAIE_INVALID_DEVICE, "kernel call before XAie_CfgInitialize");
+    return fail(XAIE_INVALID_ADDRESS, "kernel call: input address is not inside a GMIO buffer");
+  }
   XCUDA(cudaSetDevice(rt->device));
   if (Col < 1 || Row < 1) return fail(XAIE_INVALID_ARGS, "kernel call: Col and Row must be at least 1");
   const XAie_LocType loc = XAie_TileLoc(static_cast<u8>(colstart), static_cast<u8>(rowstart));
@@ -870,11 +954,16 @@ AieRC XAie_KernelCall(const void* kernel_key, const void* args, u32 args_bytes, 
   XAie_MemInst* mout = find_mem(rt, out_addr, &off);
   if (!mout) return fail(XAIE_INVALID_ADDRESS, "kernel call: output address is not inside a GMIO buffer");
   g_err.clear();
+  // Col x Row tiles of the array become Col x Row SMs: the persistent GEMM kernels plan their tile
+  // shape and waves for that many and occupy no more (a grid larger than the GPU means all of it)
+  const long long grid_sms = static_cast<long long>(Col) * Row;
+  aiehlc_set_cta_limit(rt->ctx, grid_sms > 0x7FFFFFFF ? 0 : static_cast<int>(grid_sms));
   rc = launch_tile(rt, t, 1);
+  aiehlc_set_cta_limit(rt->ctx, 0);
   if (rc != XAIE_OK) return rc;
   Region* r = rt->find_region(t, t.kernel.out_addr, 1);
   if (!r) return fail(XAIE_INVALID_ADDRESS, "kernel call: kernel produced no output window");
-  u64 n = r->cap;
+  u64 n = t.out_bytes;   // what this launch produced, not the window's capacity
   if (n > mout->bytes - off) n = mout->bytes - off;
   rc = t2h(rt, loc, t.kernel.out_addr, static_cast<uint8_t*>(mout->host) + off, n);  // waits for the stream
   if (rc != XAIE_OK) return rc;
@@ -897,7 +986,7 @@ struct XAie_Kernel_Inst {
 namespace {
 // The device instance behind XAie_LoadKernel when the program has not initialised one itself:
 // the array of example/other/aieoob.c:8-19.
-XAie_DevInst g_implicit_dev;
+thread_local XAie_DevInst g_implicit_dev;
 bool lookup_kernel_by_name(const char* name, const void** key) {
   seed_library_kernels();
   Registry& r = registry();

@@ -134,6 +134,10 @@ class Context:
     def set_group_m(self, group_m: int) -> None:
         _capi.check(self._lib.aiehlc_set_group_m(self._h, int(group_m)))
 
+    def set_cta_limit(self, sms: int) -> None:
+        """SMs the persistent GEMM kernels may occupy (0 = all)."""
+        _capi.check(self._lib.aiehlc_set_cta_limit(self._h, int(sms)))
+
     def set_pdl(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_pdl(self._h, 1 if on else 0))
 

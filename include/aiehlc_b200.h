@@ -201,11 +201,15 @@ int aiehlc_plan_conv2d(aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout,
  * the whole device to someone else.  Same arguments and bit-identical results as
  * aiehlc_conv2d_i8_srs_dev, but the re-laid weights live in a fixed array inside the library
  * (AIEHLC_CONV_STATIC_SCRATCH_BYTES, held by every GPU that loads the library until the process
- * ends) instead of a workspace that grows with cudaMalloc.  The call performs no cudaMalloc /
- * cudaFree and calls no allocating routine.
+ * ends) instead of a workspace that grows with cudaMalloc.  Form, tiling and kernels are those of the
+ * regular entry point (aiehlc_plan_conv2d describes both); shapes whose HWIO weights feed the tensor
+ * cores as they are do not touch the array at all.
  *   - kh*kw*cin*cout above AIEHLC_CONV_STATIC_SCRATCH_BYTES is refused with AIEHLC_ERR_UNSUPPORTED.
- *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress); make
- *     that first call before starting any stream capture.
+ *   - The FIRST call on a device is not allocation-free: it resolves the array's device address
+ *     (cudaGetSymbolAddress) and, with CUDA's lazy module loading, makes the driver load the kernels
+ *     and the array itself, which allocates device memory.  Make one warm-up call per device while
+ *     allocation is still allowed -- before the pool is frozen and before any stream capture.  Every
+ *     later call performs no cudaMalloc / cudaFree and calls no allocating routine.
  *   - All calls on a GPU share the one array and it keeps what the last call left there; each call
  *     rewrites every byte it later reads, so results never depend on earlier calls -- but two calls
  *     that overlap on the GPU (different streams, or different contexts on one device) race on it.
@@ -215,102 +219,16 @@ int aiehlc_conv2d_i8_srs_static_dev(aiehlc_ctx* ctx, const int8_t* x, const int8
                                     int h, int wd, int cin, int cout, int kh, int kw, int pad,
                                     const uint8_t* shift_vec, void* stream);
 
-/* Tuning knob for experiments: force the N extent of the GEMM tile (64, 128 or 256; 0 = choose). */
-int aiehlc_set_tile_n(aiehlc_ctx* ctx, int tile_n);
-/* Tuning knob: 1 = run the GEMM tiles on CTA pairs (tcgen05 cta_group::2, 256-row tiles, each CTA
- * fetching half of the B tile) wherever M > 128, 0 = one CTA per 128-row tile, -1 = choose per
- * shape (the default). */
-int aiehlc_set_cta_pair(aiehlc_ctx* ctx, int mode);
-/* Tuning knob for the CTA-pair kernel: 128-byte K blocks fetched by one TMA tile load (and held by one
- * pipeline stage).  2 needs K * element size to be a multiple of 128 bytes; 0 (default) = 2 where that
- * holds, else 1. */
-int aiehlc_set_k_per_load(aiehlc_ctx* ctx, int k_blocks);
-/* Tuning knob: 1 (default) = the int32 and bf16 GEMM epilogues stage 32 rows x 128 bytes of results in
- * shared memory and write them with a TMA tile store (whole 128-byte lines, clipped at the edges of C;
- * `accumulate` uses the add-reduction form); 2 = the int8 srs epilogue does so too (measured slower than
- * its per-thread 32-byte stores); 0 = every thread stores its own row directly.  Tile stores need C
- * 16-byte aligned with a 16-byte row pitch; otherwise the direct path is taken whatever the setting. */
-int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on);
-/* Tuning knob for the CTA-pair kernel: groups of four epilogue warps per CTA.  2 = the two warps of a
- * TMEM lane quarter each drain half of a tile's columns (one staging buffer per warp; more accumulator
- * reads, proxy fences and tile stores in flight: where the output stage sets the pace, K <= 1024 bytes,
- * results leave 10-18 % faster); 1 = four warps with two staging buffers each (1-2 % faster where K is
- * deep); 0 (default) = 2 up to 8 K blocks of 128 bytes for int8 operands and 4 for bf16 (and never for a
- * row-sharded output, which the wire bounds), else 1. */
-int aiehlc_set_epilogue_groups(aiehlc_ctx* ctx, int groups);
-/* Tuning knob for a thin last wave (at most half of the CTA pairs busy) of a CTA-pair launch:
- *   1 = (int8 only) its tiles are cut along K into up to 4 ranges run by otherwise idle pairs; the ranges
- *       exchange int32 partial sums through a context workspace and each runs the output stage on its
- *       share of the columns (integer sums: bit-identical results);
- *   2 = (default) its 256-column tiles are cut into two 128-column ranges run by different pairs (narrower
- *       MMAs, nothing to exchange; every output element is still one accumulation over K in the same
- *       order); measured 48.3 us against 49.7 us on the 4096^3 benchmark;
- *   0 = every tile computed whole. */
-int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on);
-/* Tuning knob for the *_host GEMM entry points: number of row blocks of A / C that upload, kernel and
- * download are pipelined over (0 = default 4; blocks are whole 256-row tiles). */
-int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks);
-/* Tuning knob for the convolution kernel: 1 (default) = a CTA fetches its tile's whole input patch
- * (rows + kh - 1 image rows of width + kw - 1 pixels, zero-filled outside the image) with ONE TMA box and
- * every tap's weights with another, and the kh * kw taps are kh * kw views into that one patch; 0 = one
- * activation box and one weight box per tap.  Filters whose taps do not fit in shared memory take the
- * second form whatever the setting. */
-int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on);
-/* Tuning knob for aiehlc_mm_i32_*: 1 (default) = products of at least 2^24 multiply-adds (K >= 64) run on the
- * int8 tensor cores: the int32 operands are cut into unsigned bytes, four int8 GEMMs (one per power of
- * 256, operands of K, 2K, 3K and 4K bytes; K in ranges of 8192 so that no partial sum can reach 2^31) add
- * their shifted results, which is the reference kernel's uint32 wrap-around arithmetic bit for bit;
- * 0 = always the CUDA-core kernel; 2 = always the tensor cores, whatever the size (for tests: the reference's
- * 16 x 16 x 16 fixture through this form). */
-int aiehlc_set_mm_i32_tensor(aiehlc_ctx* ctx, int on);
-/* Tuning knob for aiehlc_conv2d_i8_srs_dev / _host: 1 (default) = where the patch form applies and the
- * output-channel tile is 32, 64 or 128 wide, the HWIO weights are fetched as they are (rows of output
- * channels: the tensor core's N-major operand layout) and the convolution is one launch; 0 = weights
- * are always re-laid to [tap][cout][cin] by a pre-pass launch first. */
-int aiehlc_set_conv_hwio_direct(aiehlc_ctx* ctx, int on);
-/* Tuning knob for the convolution's patch form: 1 = the kw taps of a filter row are ONE MMA with
- * N = kw * (output-channel tile) and the epilogue adds the taps' column blocks of neighbouring rows (filters up
- * to 4 wide, kw * tile <= 256); 0 (default) = one MMA per tap and 32-byte K step.  Same bits either way;
- * measured slower on the 56 x 56 x 64 benchmark (5.7 us against 4.9 us: the wider MMAs wait for the same
- * weight boxes and the epilogue has three accumulator blocks to add). */
-int aiehlc_set_conv_wide_n(aiehlc_ctx* ctx, int on);
-/* Tuning knob for aiehlc_gemm_i8_i32_scatter_dev: 1 (default) = results leave as add-reducing TMA tile
- * stores (32 rows x 128 bytes per store; needs N a multiple of 4 and 16-byte aligned shards, else the
- * other form is used), 0 = as per-row reduction instructions issued by the epilogue warps.  Measured
- * between two B200 (65536 x 8192 x 4096 per GPU, half of the tiles remote): 2.04 ms against 2.10 ms,
- * all shards local 1.63 ms against 2.08 ms. */
-int aiehlc_set_shard_tile_stores(aiehlc_ctx* ctx, int on);
-/* Tuning knob: number of tile row-blocks the persistent scheduler walks before it moves to the next
- * tile column (the L2 footprint of one wave is group_m row-blocks of A plus slots/group_m column-blocks
- * of B).  0 = default: 8 for CTA-pair tiles, 16 for single-CTA tiles (about square wave footprints). */
-int aiehlc_set_group_m(aiehlc_ctx* ctx, int group_m);
-/* Tuning knob: 1 (default) = the tensor-core kernels are launched with programmatic stream
- * serialization, so their set-up (barriers, TMEM allocation) overlaps the tail of the kernel before
- * them in the stream; they still wait for that kernel to complete before touching global memory.
- * 0 = plain stream-ordered launches. */
-int aiehlc_set_pdl(aiehlc_ctx* ctx, int on);
-/* Measurement aid for the GEMM kernels (results are then meaningless): 1 = skip the TMA loads and
- * run the MMAs on whatever shared memory holds (tensor-pipe ceiling), 2 = skip the MMAs and only
- * stream the operands (operand-feed ceiling), 4 = int32 results are staged in shared memory but their
- * tile stores are not issued, 5 = the output stage is skipped after the accumulator reads, 0 = normal.
- * Test aid: 3 = the producer warp neither loads nor signals.  Every other warp's wait then runs out
- * (about one second), the kernel records which wait gave up in the status word, frees its TMEM and
- * returns; aiehlc_sync reports AIEHLC_ERR_DEVICE with the code (102 = the MMA issuer waited for
- * operands) and clears it, and the context stays usable.  This is how the bounded-wait exit is tested
- * without faulting or hanging the GPU. */
-int aiehlc_set_debug(aiehlc_ctx* ctx, int mode);
-/* Measurement aid: while `device_buffer` is non-NULL, the first CTA of every GEMM launch writes
- * clock64() stamps for each of its tiles into it, 8 int64 slots per tile: [0] MMA loop start,
- * [1] MMA loop issued, [2] epilogue starts waiting, [3] accumulator ready, [4] epilogue done;
- * tile 0 also holds [5] kernel entry, [6] kernel exit (clock64) and [7] / word 15 the global
- * nanosecond timer at entry / exit.  The buffer must hold 8 * max(2, tiles per CTA) words.  NULL switches the stamps off. */
-int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer);
-/* Measurement aid: while `device_buffer` is non-NULL, every CTA of a CTA-pair GEMM launch writes the
- * global nanosecond timer at its entry and exit into words [2 * CTA] and [2 * CTA + 1] (the buffer
- * must hold 2 * 148 words): shows which pairs finish last.  NULL switches it off. */
-int aiehlc_set_cta_times(aiehlc_ctx* ctx, long long* device_buffer);
 /* Number of kernel launches this context has enqueued since creation. */
 long long aiehlc_launch_count(const aiehlc_ctx* ctx);
+/* Number of times this context has moved one of its device workspaces (staging buffers of the _host
+ * entry points, re-pitched operands, re-laid convolution weights, ...) to a larger allocation.  A CUDA
+ * graph recorded over calls on this context holds the old addresses: it must be recorded again once
+ * this number has changed (XAie_GraphLaunch checks exactly that). */
+long long aiehlc_workspace_generation(const aiehlc_ctx* ctx);
+
+/* Tuning knobs and measurement aids are declared in aiehlc_b200_tuning.h; nothing a caller of the entry
+ * points above needs. */
 
 #ifdef __cplusplus
 }

@@ -99,11 +99,17 @@ AieRC XAie_KernelBind(const void* key, const char* name, const void* library_ker
 
 /* The kernel-call form k<Col,Row,colstart,rowstart,M,N,K>(in, out) of
  * example/nokernelload/aie_nokernelload.cc:130 as one blocking call: loads `kernel_key` on tile
- * (colstart,rowstart) of the device instance initialised last, sets its arguments, moves the GMIO
- * data at host address `in` to the kernel's input window, runs it, and moves the output window back
- * to host address `out` (both addresses must lie inside buffers from XAie_MemAllocate).  Col x Row
- * is the tile grid the caller asked for; the CUDA kernels choose their own grid, so it is validated
- * (>= 1) and otherwise unused. */
+ * (colstart,rowstart), sets its arguments, moves the GMIO data at host address `in` to the kernel's
+ * input window, runs it, and moves what the kernel produced back to host address `out` (both addresses
+ * must lie inside buffers from XAie_MemAllocate; the call runs on the device instance that owns the
+ * input buffer, so host threads with an instance each can call side by side).
+ * Col x Row is the tile grid the caller asks for.  On the AIE array it is the number of tiles the kernel
+ * is spread over; here it is the number of SMs: the persistent tensor-core GEMM kernels pick their tile
+ * shape and waves for Col x Row SMs (aiehlc_plan_gemm with that limit) and launch no more CTAs than
+ * that -- 8 x 16 = 128 of a B200's 148, 1 x 1 = a single CTA.  Kernels without a persistent grid (the
+ * int32 CUDA-core kernel, conv, srs) size their grid from the problem.
+ * Allocation: the tile's windows are created by the first call and reused; a later call whose operands
+ * and result fit in them allocates nothing. */
 AieRC XAie_KernelCall(const void* kernel_key, const void* args, u32 args_bytes, int Col, int Row, int colstart,
                       int rowstart, u64 in, u64 out);
 

@@ -87,6 +87,7 @@ typedef struct XAie_DevInst {
   const XAie_Backend* Backend;       /* examples read DevInst.Backend->Type (aieml_perf.cc:298) */
   XAie_Backend BackendStorage;
   void* Priv;                        /* run-time state: CUDA device, stream, tiles */
+  int CudaDevicePlus1;               /* XAie_SetCudaDevice: GPU index + 1; 0 = not chosen by the program */
 } XAie_DevInst;
 
 typedef struct XAie_MemInst XAie_MemInst;
@@ -102,7 +103,7 @@ typedef struct XAie_RoutingInstance XAie_RoutingInstance;
 
 /* XAie_InstDeclare(DevInst, &ConfigPtr)                                   -- aieml_perf.cc:273 */
 #define XAie_InstDeclare(Inst, ConfigPtr) \
-  XAie_DevInst Inst = {*(ConfigPtr), 0, 0, 0, 0, &(Inst).BackendStorage, {XAIE_IO_BACKEND_CUDA}, NULL}
+  XAie_DevInst Inst = {*(ConfigPtr), 0, 0, 0, 0, &(Inst).BackendStorage, {XAIE_IO_BACKEND_CUDA}, NULL, 0}
 
 static inline XAie_LocType XAie_TileLoc(u8 Col, u8 Row) {
   XAie_LocType l;
@@ -112,7 +113,18 @@ static inline XAie_LocType XAie_TileLoc(u8 Col, u8 Row) {
 }
 
 /* ---- bring-up / teardown (aieml_perf.cc:281-321) ------------------------------------------
- * The CUDA device is chosen by the environment variable AIEHLC_DEVICE (default 0). */
+ * One device instance drives one GPU.  Which one, in order of precedence:
+ *   1. XAie_SetCudaDevice(&DevInst, gpu), called before XAie_CfgInitialize (an addition; no counterpart);
+ *   2. the environment variable AIEHLC_DEVICE (one GPU for the whole process);
+ *   3. the partition: XAie_SetupPartitionConfig(&DevInst, base, startcol, ncols) (aieml_perf.cc:281) places the
+ *      instance on a range of array columns; the array's NumCols columns are dealt evenly over the visible
+ *      GPUs and the instance runs on GPU  startcol * gpus / NumCols  (one GPU: always GPU 0);
+ *   4. GPU 0.
+ * Instances are independent: a host thread per instance (per GPU) needs no locking, and the calls that
+ * name no instance (the kernel-call form, xaie_placeholder.h) resolve it from the GMIO buffer they are
+ * given or from the instance the calling thread initialised last. */
+AieRC XAie_SetCudaDevice(XAie_DevInst* DevInst, int Device);
+int XAie_GetCudaDevice(XAie_DevInst* DevInst);   /* the GPU an initialised instance runs on, else -1 */
 AieRC XAie_SetupPartitionConfig(XAie_DevInst* DevInst, u64 PartBaseAddr, u8 PartStartCol, u8 PartNumCols);
 AieRC XAie_CfgInitialize(XAie_DevInst* DevInst, XAie_Config* ConfigPtr);
 AieRC XAie_SetIOBackend(XAie_DevInst* DevInst, XAie_BackendType Backend);
@@ -193,7 +205,10 @@ AieRC XAie_DataMemBlockWrite(XAie_DevInst* DevInst, XAie_LocType Loc, u64 Addr, 
  * returns immediately; XAie_GraphWait polls for its completion like XAie_CoreWaitForDone (TimeOut in
  * microseconds, 0 = poll once).  GMIO buffers are read and written when the graph runs, so new input
  * is: fill the buffer, launch, wait, read the output buffer.  Run the sequence once normally before
- * recording it (tile windows must already have their size), and record again if a window grows. */
+ * recording it (tile windows must already exist with their size: a window that would have to be created
+ * or to grow during recording is refused).  A graph holds device addresses: once a tile window or one of
+ * the context's workspaces has moved to a larger allocation, XAie_GraphLaunch refuses the graph
+ * (XAIE_ERR, "graph is stale") before any work is issued; record it again. */
 typedef struct XAie_Graph XAie_Graph;
 AieRC XAie_GraphBeginCapture(XAie_DevInst* DevInst);
 AieRC XAie_GraphEndCapture(XAie_DevInst* DevInst, XAie_Graph** Graph);

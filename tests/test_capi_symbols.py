@@ -25,12 +25,31 @@ def test_library_loads():
 
 
 def test_every_declared_aiehlc_symbol_is_exported():
+    """Two symbol sets: the drop-in boundary (entry points, planners, counters) and, apart from it, the
+    tuning knobs and measurement aids."""
     lib = _capi.load()
-    names = _declared_functions(ROOT / "include" / "aiehlc_b200.h", "aiehlc_")
-    assert len(names) >= 18
-    for n in names:
-        assert hasattr(lib, n), f"{n} declared in aiehlc_b200.h but not exported"
-    assert set(_capi.SIGNATURES) <= set(names) | {"aiehlc_last_error"}
+    boundary = _declared_functions(ROOT / "include" / "aiehlc_b200.h", "aiehlc_")
+    tuning = _declared_functions(ROOT / "include" / "aiehlc_b200_tuning.h", "aiehlc_")
+    assert len(boundary) >= 24 and len(tuning) >= 17
+    assert not [n for n in boundary if n.startswith("aiehlc_set_")], "knobs belong in aiehlc_b200_tuning.h"
+    assert all(n.startswith("aiehlc_set_") for n in tuning)
+    assert not set(boundary) & set(tuning)
+    for n in boundary + tuning:
+        assert hasattr(lib, n), f"{n} declared in a header but not exported"
+    assert set(_capi.SIGNATURES) <= set(boundary) | set(tuning)
+    assert set(boundary) <= set(_capi.SIGNATURES), "every boundary entry point has a ctypes signature"
+
+
+def test_measurement_aids_are_compiled_out_of_the_regular_build():
+    """Clock stamps and the kernel-skipping debug modes exist only in AIEHLC_MEASURE builds; the
+    bounded-wait test aid (mode 3) is in every build."""
+    import os
+    if os.environ.get("AIEHLC_MEASURE", "0") not in ("", "0"):
+        pytest.skip("this is a measurement build")
+    lib = _capi.load()
+    assert lib.aiehlc_set_debug(None, 1) == _capi.ERR_INVALID          # null context comes first
+    fake = C.c_void_p(0)
+    assert lib.aiehlc_set_trace(fake, None) == _capi.ERR_INVALID
 
 
 def test_every_declared_xaie_symbol_is_exported():

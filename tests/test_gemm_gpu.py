@@ -399,6 +399,27 @@ def test_row_sharded_add_reduction_output(ctx, M, N, K, rows_per_shard, group_m,
         ctx.gemm_i8_i32_scatter(dA, dB, shards[:1], 128)               # shards do not cover M
 
 
+@pytest.mark.parametrize("shape", [(1024, 768, 512), (300, 520, 1152), (2304, 2304, 512)])
+def test_sm_limit_changes_the_schedule_not_the_result(ctx, shape):
+    """The Col x Row grid of the kernel-call form becomes a limit on the SMs a launch occupies: the planner
+    sizes waves for that many CTAs; the bits stay the same."""
+    from aiehlc_b200.ops import plan_gemm
+    M, N, K = shape
+    A, B = _dev(synth.int8_uniform(61, (M, K))), _dev(synth.int8_uniform(1061, (N, K)))
+    want = ctx.gemm_i8_srs(A, B, shift=7)
+    want32 = ctx.gemm_i8_i32(A, B)
+    try:
+        for sms in (1, 2, 16, 128, 1000):
+            ctx.set_cta_limit(sms)
+            plan = plan_gemm(M, N, K, ctx=ctx)
+            assert plan["slots"] * (2 if plan["cta_pair"] else 1) <= min(sms, ctx.sm_count)
+            assert torch.equal(ctx.gemm_i8_srs(A, B, shift=7), want)
+            assert torch.equal(ctx.gemm_i8_i32(A, B), want32)
+    finally:
+        ctx.set_cta_limit(0)
+    assert ctx.sync() == 0
+
+
 @pytest.mark.parametrize("pair", [0, 1])
 def test_a_wait_that_runs_out_is_reported_and_the_context_survives(ctx, pair):
     """No GPU fault, no hang: the producer is told not to deliver (debug mode 3), the consumers' bounded
