@@ -9,7 +9,8 @@
 # below with the kernel cut out) and
 # example/multi/vek385_verification.cpp (its kernel never terminates).
 set -u
-REF="${1:-/root/reference}"
+REF="${1:-${AIEHLC_REFERENCE:-}}"
+if [ -z "$REF" ]; then echo "usage: ref_build.sh /path/to/aiehlc   (or set AIEHLC_REFERENCE)"; exit 2; fi
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 INC="$HERE/../include"

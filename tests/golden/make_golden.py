@@ -33,7 +33,10 @@ PROGRAMS = {
 
 
 def main() -> int:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AIEHLC_REFERENCE")
+    if not ref:
+        print("usage: make_golden.py /path/to/aiehlc   (or set AIEHLC_REFERENCE)")
+        return 2
     subprocess.run(["bash", str(ROOT / "oracle" / "ref_build.sh"), ref], check=True)
     out = {"generator": "tests/golden/make_golden.py", "programs": {}}
     for name, (src, ok_line) in PROGRAMS.items():
