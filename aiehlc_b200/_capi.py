@@ -46,6 +46,7 @@ SIGNATURES = {
     "aiehlc_set_debug": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_pdl": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_cta_limit": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_set_operands_ready": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_group_m": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_split_tail": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_tma_store": (C.c_int, [_vp, C.c_int]),
@@ -75,7 +76,7 @@ class GemmPlan(C.Structure):
                 ("waves", C.c_int), ("wave_efficiency", C.c_double), ("group_m", C.c_int), ("stages", C.c_int),
                 ("smem_bytes", C.c_int), ("tmem_columns", C.c_int), ("k_blocks", C.c_int), ("a_shared_by", C.c_int),
                 ("b_shared_by", C.c_int), ("wave_footprint_bytes", C.c_longlong), ("cost_units", C.c_double),
-                ("split_tail_tiles", C.c_int), ("split_tail_parts", C.c_int),
+                ("split_k_tiles", C.c_int), ("split_k_at", C.c_int),
                 ("narrow_tail_tiles", C.c_int)]
 
     def as_dict(self):

@@ -227,7 +227,7 @@ int aiehlc_set_epilogue_groups(aiehlc_ctx* ctx, int groups) {
 
 int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
-  if (on < 0 || on > 2) return fail(AIEHLC_ERR_INVALID, "split_tail: 0 (off), 1 (K ranges) or 2 (column ranges)");
+  if (on < 0 || on > 3) return fail(AIEHLC_ERR_INVALID, "split_tail: 0 (off), 1 (K halves), 2 (column ranges) or 3 (choose)");
   ctx->split_tail = on;
   return AIEHLC_OK;
 }
@@ -281,6 +281,12 @@ int aiehlc_set_cta_limit(aiehlc_ctx* ctx, int sms) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   if (sms < 0) return fail(AIEHLC_ERR_INVALID, "cta_limit must be >= 0");
   ctx->cta_limit = sms;
+  return AIEHLC_OK;
+}
+
+int aiehlc_set_operands_ready(aiehlc_ctx* ctx, int on) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->operands_ready = on ? 1 : 0;
   return AIEHLC_OK;
 }
 
@@ -576,19 +582,19 @@ static int stage_ab(aiehlc_ctx* ctx, const void* A, const void* B, size_t a_byte
 
 }  // extern "C"
 
-// Host-buffer GEMM as a pipeline over row blocks of A and C on three streams:
-//   stream_up : B -> device, then the row blocks of A -> device, back to back
-//   stream    : per block, once its rows have arrived: the kernel
-//   stream2   : per block, once its kernel is done: C rows -> host
-// so the PCIe link never waits for a kernel in either direction, and what is left after the last
-// upload is one block's kernel and download.  Measured on the 4096^3 int8 case (50 MB per call): the
-// link carries 53 GB/s one way but only about 35 + 35 GB/s when both directions are busy, and every
-// extra block costs about 20 us, so four blocks are the best split (0.87 ms per call; 1.00 ms unsplit).  With pinned host buffers the
-// copies are truly asynchronous; with pageable ones the runtime stages them and the result is the
-// same, only slower.
-template <typename LaunchRows>
+// Host-buffer GEMM as a pipeline over blocks of A rows and of B rows (= C columns) on three streams:
+//   stream_up : A_0, B_0, B_1, A_1, B_2, A_2, ... -> device, back to back
+//   stream    : after each upload, ONE kernel for the part of C that has just become computable: the new
+//               row block against every B block present, or every A block present against the new B block
+//   stream2   : that rectangle of C -> host as soon as its kernel is done
+// so the first kernel starts after one block of each operand (not after all of B), the link never waits
+// for a kernel in either direction, and what is left after the last upload is one block's kernel and
+// download.  With pinned host buffers the copies are truly asynchronous; with pageable ones the runtime
+// stages them and the result is the same, only slower.
+//   launch_rect(A rows, B rows, C corner, rows, cols, first column): C[rows][cols] (pitch N) = A . B^T
+template <typename LaunchRect>
 static int host_gemm_pipelined(aiehlc_ctx* ctx, const void* A, const void* B, void* C, int M, int N, int K, int in_esize,
-                               int out_esize, LaunchRows launch_rows) {
+                               int out_esize, LaunchRect launch_rect) {
   const size_t a_bytes = static_cast<size_t>(M) * K * in_esize, b_bytes = static_cast<size_t>(N) * K * in_esize;
   const size_t c_bytes = static_cast<size_t>(M) * N * out_esize;
   if (ctx->buf_a.reserve(a_bytes ? a_bytes : 16) || ctx->buf_b.reserve(b_bytes ? b_bytes : 16) ||
@@ -597,32 +603,77 @@ static int host_gemm_pipelined(aiehlc_ctx* ctx, const void* A, const void* B, vo
   // whatever the caller queued on the context's stream before (shift bytes, ...) precedes the uploads
   AIEHLC_CUDA(cudaEventRecord(ctx->block_done, ctx->stream));
   AIEHLC_CUDA(cudaStreamWaitEvent(ctx->stream_up, ctx->block_done, 0));
-  if (b_bytes) AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_b.ptr, B, b_bytes, cudaMemcpyHostToDevice, ctx->stream_up));
-  // blocks of whole 256-row tiles; small problems go in one piece
+  // blocks of whole 256-row tiles; small problems (and empty contractions) go in one piece
   const int blocks = ctx->host_blocks > 0 ? ctx->host_blocks : 4;
-  int rows_per_block = ((M + blocks - 1) / blocks + 255) / 256 * 256;
-  if (static_cast<size_t>(rows_per_block) * K * in_esize < (1u << 20)) rows_per_block = M;
-  int b = 0;
-  for (int r0 = 0; r0 < M; r0 += rows_per_block, ++b) {
-    const int rows = M - r0 < rows_per_block ? M - r0 : rows_per_block;
-    uint8_t* da = static_cast<uint8_t*>(ctx->buf_a.ptr) + static_cast<size_t>(r0) * K * in_esize;
-    uint8_t* dc = static_cast<uint8_t*>(ctx->buf_c.ptr) + static_cast<size_t>(r0) * N * out_esize;
+  int a_rows = ((M + blocks - 1) / blocks + 255) / 256 * 256;
+  int b_rows = ((N + blocks - 1) / blocks + 255) / 256 * 256;
+  if (K == 0 || static_cast<size_t>(a_rows) * K * in_esize < (1u << 20)) a_rows = M;
+  if (K == 0 || static_cast<size_t>(b_rows) * K * in_esize < (1u << 20)) b_rows = N;
+  const int na = (M + a_rows - 1) / a_rows, nb = (N + b_rows - 1) / b_rows;
+  uint8_t* da = static_cast<uint8_t*>(ctx->buf_a.ptr);
+  uint8_t* db = static_cast<uint8_t*>(ctx->buf_b.ptr);
+  uint8_t* dc = static_cast<uint8_t*>(ctx->buf_c.ptr);
+  int ev = 0;
+  // the rectangle rows [r0, r1) x columns [c0, c1) of C: kernel once the upload just queued has landed, then download
+  auto rect = [&](int r0, int r1, int c0, int c1) -> int {
     cudaEvent_t up = nullptr, done = nullptr;
-    if (int rc = ctx->block_events(b, &up, &done)) return rc;
-    if (K > 0)
-      AIEHLC_CUDA(cudaMemcpyAsync(da, static_cast<const uint8_t*>(A) + static_cast<size_t>(r0) * K * in_esize,
-                                  static_cast<size_t>(rows) * K * in_esize, cudaMemcpyHostToDevice, ctx->stream_up));
+    if (int rc = ctx->block_events(ev++, &up, &done)) return rc;
     AIEHLC_CUDA(cudaEventRecord(up, ctx->stream_up));
     AIEHLC_CUDA(cudaStreamWaitEvent(ctx->stream, up, 0));
-    const int rc = launch_rows(da, dc, rows);
-    if (rc) return rc;
+    uint8_t* corner = dc + (static_cast<size_t>(r0) * N + c0) * out_esize;
+    if (int rc = launch_rect(da + static_cast<size_t>(r0) * K * in_esize, db + static_cast<size_t>(c0) * K * in_esize, corner,
+                             r1 - r0, c1 - c0, c0))
+      return rc;
     AIEHLC_CUDA(cudaEventRecord(done, ctx->stream));
     AIEHLC_CUDA(cudaStreamWaitEvent(ctx->stream2, done, 0));
-    AIEHLC_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(C) + static_cast<size_t>(r0) * N * out_esize, dc,
-                                static_cast<size_t>(rows) * N * out_esize, cudaMemcpyDeviceToHost, ctx->stream2));
+    uint8_t* host = static_cast<uint8_t*>(C) + (static_cast<size_t>(r0) * N + c0) * out_esize;
+    if (c0 == 0 && c1 == N)
+      AIEHLC_CUDA(cudaMemcpyAsync(host, corner, static_cast<size_t>(r1 - r0) * N * out_esize, cudaMemcpyDeviceToHost, ctx->stream2));
+    else
+      AIEHLC_CUDA(cudaMemcpy2DAsync(host, static_cast<size_t>(N) * out_esize, corner, static_cast<size_t>(N) * out_esize,
+                                    static_cast<size_t>(c1 - c0) * out_esize, r1 - r0, cudaMemcpyDeviceToHost, ctx->stream2));
+    return AIEHLC_OK;
+  };
+  auto upload = [&](uint8_t* dev, const void* host, int row0, int rows) -> int {
+    if (K > 0 && rows > 0)
+      AIEHLC_CUDA(cudaMemcpyAsync(dev + static_cast<size_t>(row0) * K * in_esize,
+                                  static_cast<const uint8_t*>(host) + static_cast<size_t>(row0) * K * in_esize,
+                                  static_cast<size_t>(rows) * K * in_esize, cudaMemcpyHostToDevice, ctx->stream_up));
+    return AIEHLC_OK;
+  };
+  auto a_end = [&](int i) { return (i + 1) * a_rows < M ? (i + 1) * a_rows : M; };
+  auto b_end = [&](int j) { return (j + 1) * b_rows < N ? (j + 1) * b_rows : N; };
+  int ia = 0, ib = 0;  // blocks of A and of B on the device so far
+  if (int rc = upload(da, A, 0, a_end(0))) return rc;
+  if (int rc = upload(db, B, 0, b_end(0))) return rc;
+  ia = ib = 1;
+  if (int rc = rect(0, a_end(0), 0, b_end(0))) return rc;
+  while (ia < na || ib < nb) {
+    // the operand that is further behind goes next; on a tie B, so that the last piece of C is whole rows
+    const bool take_b = ib < nb && (ia >= na || ib * na <= ia * nb);
+    if (take_b) {
+      if (int rc = upload(db, B, ib * b_rows, b_end(ib) - ib * b_rows)) return rc;
+      if (int rc = rect(0, a_end(ia - 1), ib * b_rows, b_end(ib))) return rc;
+      ++ib;
+    } else {
+      if (int rc = upload(da, A, ia * a_rows, a_end(ia) - ia * a_rows)) return rc;
+      if (int rc = rect(ia * a_rows, a_end(ia), 0, b_end(ib - 1))) return rc;
+      ++ia;
+    }
   }
   AIEHLC_CUDA(cudaStreamSynchronize(ctx->stream2));
   return finish_host(ctx);
+}
+
+// One rectangle of a host GEMM: the tile GEMM on device operands with C's pitch given (the public _dev entry
+// points fix it at N).
+static int gemm_rect(aiehlc_ctx* ctx, int kind, int epi, const void* A, const void* B, void* C, int M, int N, int K,
+                     long long ldc, int shift, const uint8_t* shift_vec) {
+  GemmCall c{};
+  c.kind = kind; c.epi = epi;
+  c.A = A; c.B = B; c.C = C; c.M = M; c.N = N; c.K = K; c.lda = K; c.ldb = K; c.ldc = ldc;
+  c.shift = shift; c.shift_vec = shift_vec;
+  return launch_gemm(ctx, c, ctx->stream);
 }
 
 extern "C" {
@@ -633,9 +684,9 @@ int aiehlc_gemm_i8_i32_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, i
   if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32: negative size");
   if (M == 0 || N == 0) return AIEHLC_OK;
   if (!C || (K > 0 && (!A || !B))) return fail(AIEHLC_ERR_INVALID, "gemm_i8_i32: null pointer");
-  return host_gemm_pipelined(ctx, A, B, C, M, N, K, 1, 4, [&](uint8_t* da, uint8_t* dc, int rows) {
-    return aiehlc_gemm_i8_i32_dev(ctx, reinterpret_cast<const int8_t*>(da), static_cast<const int8_t*>(ctx->buf_b.ptr),
-                                  reinterpret_cast<int32_t*>(dc), rows, N, K, 0, ctx->stream);
+  return host_gemm_pipelined(ctx, A, B, C, M, N, K, 1, 4, [&](uint8_t* da, uint8_t* db, uint8_t* dc, int rows, int cols, int) {
+    if (K == 0) return aiehlc_gemm_i8_i32_dev(ctx, nullptr, nullptr, reinterpret_cast<int32_t*>(dc), rows, cols, 0, 0, ctx->stream);
+    return gemm_rect(ctx, KIND_I8, EPI_I32, da, db, dc, rows, cols, K, N, 0, nullptr);
   });
 }
 
@@ -644,6 +695,9 @@ int aiehlc_gemm_i8_srs_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, i
   int rc = check_ctx(ctx);
   if (rc) return rc;
   if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: negative size");
+  if ((rc = check_shift(shift, shift_vec))) return rc;
+  if (splitk < 1 || (K > 0 && K % splitk != 0))
+    return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: splitk must be >= 1 and divide K");
   if (M == 0 || N == 0) return AIEHLC_OK;
   if (!C || (K > 0 && (!A || !B))) return fail(AIEHLC_ERR_INVALID, "gemm_i8_srs: null pointer");
   const uint8_t* dsv = nullptr;
@@ -654,9 +708,11 @@ int aiehlc_gemm_i8_srs_host(aiehlc_ctx* ctx, const int8_t* A, const int8_t* B, i
     AIEHLC_CUDA(cudaMemcpyAsync(ctx->buf_aux.ptr, shift_vec, N, cudaMemcpyHostToDevice, ctx->stream));
     dsv = static_cast<const uint8_t*>(ctx->buf_aux.ptr);
   }
-  return host_gemm_pipelined(ctx, A, B, C, M, N, K, 1, 1, [&](uint8_t* da, uint8_t* dc, int rows) {
-    return aiehlc_gemm_i8_srs_dev(ctx, reinterpret_cast<const int8_t*>(da), static_cast<const int8_t*>(ctx->buf_b.ptr),
-                                  reinterpret_cast<int8_t*>(dc), rows, N, K, shift, dsv, nullptr, splitk, ctx->stream);
+  return host_gemm_pipelined(ctx, A, B, C, M, N, K, 1, 1, [&](uint8_t* da, uint8_t* db, uint8_t* dc, int rows, int cols, int c0) {
+    if (K == 0)   // whole C in one piece: srs(0) = 0
+      return aiehlc_gemm_i8_srs_dev(ctx, nullptr, nullptr, reinterpret_cast<int8_t*>(dc), rows, cols, 0, shift, dsv, nullptr, 1,
+                                    ctx->stream);
+    return gemm_rect(ctx, KIND_I8, EPI_I8_SRS, da, db, dc, rows, cols, K, N, shift, dsv ? dsv + c0 : nullptr);
   });
 }
 
@@ -667,9 +723,9 @@ int aiehlc_gemm_bf16_host(aiehlc_ctx* ctx, const uint16_t* A, const uint16_t* B,
   if (M < 0 || N < 0 || K < 0) return fail(AIEHLC_ERR_INVALID, "gemm_bf16: negative size");
   if (M == 0 || N == 0) return AIEHLC_OK;
   if (!C || (K > 0 && (!A || !B))) return fail(AIEHLC_ERR_INVALID, "gemm_bf16: null pointer");
-  return host_gemm_pipelined(ctx, A, B, C, M, N, K, 2, 2, [&](uint8_t* da, uint8_t* dc, int rows) {
-    return aiehlc_gemm_bf16_dev(ctx, reinterpret_cast<const uint16_t*>(da), static_cast<const uint16_t*>(ctx->buf_b.ptr),
-                                reinterpret_cast<uint16_t*>(dc), rows, N, K, ctx->stream);
+  return host_gemm_pipelined(ctx, A, B, C, M, N, K, 2, 2, [&](uint8_t* da, uint8_t* db, uint8_t* dc, int rows, int cols, int) {
+    if (K == 0) return aiehlc_gemm_bf16_dev(ctx, nullptr, nullptr, reinterpret_cast<uint16_t*>(dc), rows, cols, 0, ctx->stream);
+    return gemm_rect(ctx, KIND_BF16, EPI_BF16, da, db, dc, rows, cols, K, N, 0, nullptr);
   });
 }
 

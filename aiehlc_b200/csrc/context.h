@@ -79,7 +79,8 @@ struct aiehlc_ctx {
   int k_per_load = 0;           // 0: choose, 1: one 128-byte K block per tile load, 2: two where K allows
   int epi_groups = 0;           // groups of four epilogue warps in the CTA-pair kernel (1 or 2; 0 = by K)
   int tma_store = 1;            // epilogue results leave through shared memory + TMA tile stores when C allows
-  int split_tail = 2;           // thin last wave: 1 = cut its tiles along K across idle CTA pairs, 2 = into two column ranges
+  int split_tail = 3;           // last wave at most half full: 1 = its tiles run as two K halves (int8), 2 = as two column
+                                // ranges, 3 = the faster of the two as measured (column ranges), 0 = whole tiles
   int group_m = 0;              // row-blocks per rasterisation group (0 = default for the kernel family)
   int host_blocks = 0;           // row blocks the *_host GEMM entry points pipeline over (0 = default)
   int conv_wide_n = 0;          // patch form: the kw taps of a filter row in one MMA (N = kw * cout_tile)
@@ -88,6 +89,7 @@ struct aiehlc_ctx {
   int conv_halo = 1;            // conv kernel fetches a tile's whole input patch and all taps' weights in two boxes
   int cta_limit = 0;            // persistent GEMM kernels occupy at most this many SMs (0 = all of them)
   int usable_sms() const { return cta_limit > 0 && cta_limit < sm_count ? cta_limit : sm_count; }
+  int operands_ready = 0;       // caller's promise: GEMM operands are never written by the kernel just before in the stream
   int pdl = 1;                  // launch the tensor-core kernels with programmatic stream serialization
   int debug_mode = 0;           // see GemmParams::debug
   long long* cta_times = nullptr;  // see GemmParams::cta_times (device pointer owned by the caller)
@@ -101,7 +103,7 @@ struct aiehlc_ctx {
   aiehlc::DevBuf buf_a, buf_b, buf_c, buf_aux, pack_a, pack_b;
   aiehlc::DevBuf limb_a, limb_b;        // byte planes of int32 operands (mm_i32 on the tensor cores)
   int mm_i32_tensor = 1;                // large int32 products run as int8 limb GEMMs on the tensor cores
-  aiehlc::DevBuf sk_scratch, sk_flags;  // partial sums and deposit counters of split tail tiles
+  aiehlc::DevBuf sk_scratch, sk_flags;  // partial sums and deposit counters of tail tiles cut along K
   int shard_tile_stores = 1;            // sharded output leaves as add-reducing TMA tile stores (else row reductions)
   aiehlc::DevBuf shard_maps;            // tensor maps of a row-sharded output, as the kernels read them
   std::vector<unsigned long long> shard_key;  // what those maps were made from
@@ -124,6 +126,7 @@ struct GemmCall {
   const uint8_t* shift_vec; int shift;
   int group_m;                  // filled in from the plan
   int unsigned_ab = 0, out_shift = 0;   // see GemmParams
+  int operands_from_kernel = 0;         // A or B was produced by a kernel this library launched just before (never early)
   // row-sharded add-reduction output (see GemmParams::shard); C is unused when num_shards > 0
   int32_t* const* shards = nullptr;
   const CUtensorMap* shard_maps = nullptr;   // optional: the shards as tensors for add-reducing tile stores
@@ -135,8 +138,8 @@ int encode_c_map(aiehlc_ctx* ctx, CUtensorMap* map, int epi, int bn, void* base,
 int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_plan* out);
 int tile_order(const aiehlc_ctx* ctx, int kind, int M, int N, int K, int num_shards, int rows_per_shard, int first_shard,
                int* row_block, int* col_block, int capacity, int* slots_out);
-// Tail balancing: tiles [first, tiles) are cut into `parts` K ranges (parts == 1: no cut).
-void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int* parts);
+// Tail tiles of a CTA-pair launch that run as two K halves (0: none) and where they are cut; see gemm_launch.cu.
+int split_k_tail(int tiles, int slots, int k_blocks, int mode, int* cut_at);
 void narrow_tail(int tiles, int slots, int tile_n, int enabled, int* first, int* parts);
 
 // SIMT helpers (simt_kernels.cu)

@@ -84,21 +84,22 @@ int encode_c_map(aiehlc_ctx* ctx, CUtensorMap* map, int epi, int bn, void* base,
   return AIEHLC_OK;
 }
 
-// When the last wave of a persistent launch is at most half full, its tiles are cut along K into as
-// many ranges as there are idle slots per tile (at most 4, at least 8 K-blocks each).
-void split_tail(int tiles, int slots, int k_blocks, int enabled, int* first, int* parts) {
-  *first = tiles;
-  *parts = 1;
-  if (enabled != 1 || slots <= 0) return;
-  const int rem = tiles % slots;
-  if (rem == 0 || rem * 2 > slots) return;
-  int s = slots / rem;
-  if (s > 4) s = 4;
-  while (s > 1 && k_blocks / s < 8) --s;
-  if (s > 1) {
-    *first = tiles - rem;
-    *parts = s;
-  }
+// Tail balancing of a CTA-pair launch along K (int8).  With `slots` pairs, tiles = full * slots + rem tiles
+// take full + 1 waves of which the last keeps only rem pairs busy.  When rem <= slots / 2 the rem tail tiles
+// are cut into two K halves that run side by side in the first round, on 2 rem pairs, while the other pairs
+// start on whole tiles; after that every pair has `full` whole tiles left, so no pair has more than
+// full + 1/2 tile times of work.  The upper half leaves its partial sums in a workspace; the lower half
+// owns the output stage and adds them while its pair is already multiplying its next tile.  Needs one full
+// wave (so that there is a next tile) and a K of at least 16 blocks (halves of >= 8).  Returns the number
+// of tail tiles cut (0: none) and the K block where they are cut.
+//   mode 1: wherever that applies;  else: never.
+int split_k_tail(int tiles, int slots, int k_blocks, int mode, int* cut_at) {
+  if (cut_at) *cut_at = 0;
+  if (mode != 1 || slots <= 0 || k_blocks < 16) return 0;
+  const int full = tiles / slots, rem = tiles % slots;
+  if (full < 1 || rem == 0 || rem * 2 > slots) return 0;
+  if (cut_at) *cut_at = (k_blocks / 2 + 1) & ~1;  // an even number of K blocks in the lower half
+  return rem;
 }
 
 // Whether the CTA-pair kernel fetches two 128-byte K blocks with one tile load: K must be a whole
@@ -113,7 +114,7 @@ static bool wide_k_loads(const aiehlc_ctx* ctx, int esize, int K) {
 void narrow_tail(int tiles, int slots, int tile_n, int enabled, int* first, int* parts) {
   *first = tiles;
   *parts = 1;
-  if (enabled != 2 || slots <= 0 || tile_n != 256) return;
+  if ((enabled != 2 && enabled != 3) || slots <= 0 || tile_n != 256) return;
   const int rem = tiles % slots;
   if (rem == 0 || rem * 2 > slots) return;
   *first = tiles - rem;
@@ -154,10 +155,17 @@ int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_
       // rows of the last row-block that fall outside M are computed all the same
       double waves = pl.waves;
       {
-        // a thin last wave of 256-column pair tiles runs as 128-column ranges: measured 0.87 of a whole tile's time
+        const int kb = static_cast<int>((static_cast<long long>(K) * esize + kBlockKBytes - 1) / kBlockKBytes);
+        const int mode = pr ? ctx->split_tail : 0;
         int first = 0, parts = 1;
-        narrow_tail(static_cast<int>(pl.tiles), pl.slots, bn, pr ? ctx->split_tail : 0, &first, &parts);
-        if (parts > 1) waves -= 0.13;
+        if (kind == KIND_I8 && split_k_tail(static_cast<int>(pl.tiles), pl.slots, kb, mode, nullptr) > 0) {
+          // the tail tiles run as K halves: half a wave (plus the meeting of the partial sums)
+          waves = pl.waves - 0.5 + 0.04;
+        } else {
+          // a thin last wave of 256-column pair tiles runs as 128-column ranges: measured 0.87 of a whole tile's time
+          narrow_tail(static_cast<int>(pl.tiles), pl.slots, bn, mode, &first, &parts);
+          if (parts > 1) waves -= 0.13;
+        }
       }
       // Pairs halve the B traffic per SM, which pays once tiles follow one another; a single wave of 256-column
       // tiles runs 5-14 % faster on single CTAs (measured: 2048^3 10.7 against 11.5 us, 1536 x 3072 x 4096 15.6
@@ -189,11 +197,13 @@ int plan_gemm(const aiehlc_ctx* ctx, int kind, int M, int N, int K, aiehlc_gemm_
                                (wave_cols < best.grid_n ? wave_cols : best.grid_n) * best.tile_n) *
                               static_cast<long long>(K) * esize;
   int first = 0, parts = 1;
-  split_tail(static_cast<int>(best.tiles), best.slots, best.k_blocks, best.cta_pair ? ctx->split_tail : 0, &first, &parts);
-  best.split_tail_tiles = parts > 1 ? static_cast<int>(best.tiles) - first : 0;
-  best.split_tail_parts = parts;
-  narrow_tail(static_cast<int>(best.tiles), best.slots, best.tile_n, best.cta_pair ? ctx->split_tail : 0, &first, &parts);
-  best.narrow_tail_tiles = parts > 1 ? static_cast<int>(best.tiles) - first : 0;
+  const int mode = best.cta_pair ? ctx->split_tail : 0;
+  best.split_k_tiles = kind == KIND_I8 ? split_k_tail(static_cast<int>(best.tiles), best.slots, best.k_blocks, mode, &best.split_k_at) : 0;
+  best.narrow_tail_tiles = 0;
+  if (best.split_k_tiles == 0) {
+    narrow_tail(static_cast<int>(best.tiles), best.slots, best.tile_n, mode, &first, &parts);
+    best.narrow_tail_tiles = parts > 1 ? static_cast<int>(best.tiles) - first : 0;
+  }
   *out = best;
   return AIEHLC_OK;
 }
@@ -244,6 +254,7 @@ int launch_one(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
   p.group_m = c.group_m;
   p.unsigned_ab = c.unsigned_ab; p.out_shift = c.out_shift;
+  p.early_operands = (ctx->operands_ready && ctx->pdl && !c.operands_from_kernel) ? 1 : 0;
   // 32 consecutive outputs per thread are written with 16-byte stores when every row start is aligned.
   bool vec = (reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0);
   p.vec_ok = vec ? 1 : 0;
@@ -318,6 +329,7 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.num_k_blocks = static_cast<int>((static_cast<long long>(c.K) * esize + kBlockKBytes - 1) / kBlockKBytes);
   p.group_m = c.group_m;
   p.unsigned_ab = c.unsigned_ab; p.out_shift = c.out_shift;
+  p.early_operands = (ctx->operands_ready && ctx->pdl && !c.operands_from_kernel) ? 1 : 0;
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c.C) % 16 == 0) && ((c.ldc * cesize) % 16 == 0)) ? 1 : 0;
   p.tma_store = (p.vec_ok && (ctx->tma_store == 2 || (ctx->tma_store == 1 && kEpi != EPI_I8_SRS))) ? 1 : 0;
   CUtensorMap mc = ma;  // unused unless tma_store
@@ -332,6 +344,9 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   p.debug = ctx->debug_mode;
   p.trace = ctx->trace;
   p.cta_times = ctx->cta_times;
+#ifdef AIEHLC_MEASURE
+  if (const char* e = getenv("AIEHLC_TRACE_CTA")) p.trace_cta = atoi(e);
+#endif
 
   auto kern = gemm_tn_pair_kernel<kKind, kBN, kEpi, kKPer, kEpiGroups>;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
@@ -368,16 +383,17 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
   }
   max_pairs = ks.max_clusters < pair_limit ? ks.max_clusters : pair_limit;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
-  // Tail balancing (int32 accumulation only: sums of partial sums are exact; fp32 would change rounding)
-  p.sk_first_tile = tiles;
-  p.sk_parts = 1;
-  if (kKind == KIND_I8 && c.num_shards == 0) {  // the K ranges store per thread: not into a sharded output
-    split_tail(tiles, tiles < max_pairs ? max_pairs : pairs, p.num_k_blocks, ctx->split_tail, &p.sk_first_tile, &p.sk_parts);
-    if (p.sk_parts > 1) {
-      const int tail = tiles - p.sk_first_tile;
+  // Tail tiles as K halves (int32 accumulation only: sums of partial sums are exact, fp32 would change
+  // rounding; the lower half runs the plain output stage: not into a sharded output)
+  p.sk_tiles = 0;
+  p.sk_cut = 0;
+  if (kKind == KIND_I8 && c.num_shards == 0 && tiles >= max_pairs) {
+    p.sk_tiles = split_k_tail(tiles, max_pairs, p.num_k_blocks, ctx->split_tail, &p.sk_cut);
+    if (p.sk_tiles > 0) {
+      // one slot and one counter per tail tile and CTA rank
       const size_t cta_ints = static_cast<size_t>(kBN / 32) * kSkChunkInts;
-      const size_t scratch_bytes = static_cast<size_t>(tail) * p.sk_parts * 2 * cta_ints * sizeof(int32_t);
-      const size_t flag_bytes = static_cast<size_t>(tail) * 2 * 4 * sizeof(int);
+      const size_t scratch_bytes = static_cast<size_t>(p.sk_tiles) * 2 * cta_ints * sizeof(int32_t);
+      const size_t flag_bytes = static_cast<size_t>(p.sk_tiles) * 2 * sizeof(int);
       if (ctx->sk_scratch.reserve(scratch_bytes)) return AIEHLC_ERR_NOMEM;
       if (flag_bytes > ctx->sk_flags.bytes) {
         if (ctx->sk_flags.reserve(flag_bytes)) return AIEHLC_ERR_NOMEM;
@@ -385,13 +401,12 @@ int launch_pair(aiehlc_ctx* ctx, const GemmCall& c, cudaStream_t st) {
       }
       p.sk_scratch = static_cast<int32_t*>(ctx->sk_scratch.ptr);
       p.sk_flags = static_cast<int*>(ctx->sk_flags.ptr);
-      const int units = p.sk_first_tile + tail * p.sk_parts;
-      pairs = units < max_pairs ? units : max_pairs;
+      pairs = max_pairs;  // at least one full wave: every pair has work
     }
   }
   p.nt_first_tile = tiles;
   p.nt_parts = 1;
-  if (p.sk_parts == 1) {
+  if (p.sk_tiles == 0) {
     narrow_tail(tiles, tiles < max_pairs ? max_pairs : pairs, kBN, ctx->split_tail, &p.nt_first_tile, &p.nt_parts);
     if (p.nt_parts > 1) {
       rc = kKPer == 1 ? encode_kmajor_map(ctx, &mb_narrow, kKind, c.B, c.N, c.K, c.ldb, kBN / 2 / p.nt_parts)
@@ -476,6 +491,7 @@ int launch_gemm(aiehlc_ctx* ctx, const GemmCall& call, cudaStream_t st) {
     int rc = launch_repack(ctx, c.A, ctx->pack_a.ptr, c.M, c.K, c.lda, ld, esize, st);
     if (rc) return rc;
     c.A = ctx->pack_a.ptr; c.lda = ld;
+    c.operands_from_kernel = 1;
   }
   if (needs_pack(c.B, c.ldb)) {
     const long long ld = (static_cast<long long>(c.K) * esize + 15) / 16 * 16 / esize;
@@ -483,6 +499,7 @@ int launch_gemm(aiehlc_ctx* ctx, const GemmCall& call, cudaStream_t st) {
     int rc = launch_repack(ctx, c.B, ctx->pack_b.ptr, c.N, c.K, c.ldb, ld, esize, st);
     if (rc) return rc;
     c.B = ctx->pack_b.ptr; c.ldb = ld;
+    c.operands_from_kernel = 1;
   }
 
   aiehlc_gemm_plan plan{};

@@ -65,13 +65,13 @@ struct GemmParams {
   int vec_ok;              // C (and acc_in) rows are 16-byte aligned: vector stores allowed
   int tma_store;           // results leave through shared memory and TMA tile stores (needs vec_ok)
   int* status;             // device status word (0 = ok)
-  // Tail balancing of the pair kernel: tiles >= sk_first_tile are cut into sk_parts K ranges that
-  // run on different CTA pairs.  Each range owns a share of the tile's column chunks: it deposits
-  // the int32 partial sums of the other chunks in sk_scratch, adds what the other ranges deposited
-  // to its own chunks and runs the output stage on them.  sk_parts == 1: every tile is computed whole.
-  int sk_first_tile, sk_parts;
-  int32_t* sk_scratch;     // [tail tile][depositing range][CTA rank][32-column chunk] partial sums
-  int* sk_flags;           // [tail tile][CTA rank][owning range (4 slots)] deposits so far; zero between launches
+  // Tail balancing of the pair kernel along K (int8 only): the last sk_tiles tiles are cut at K block sk_cut
+  // into two halves that run on different CTA pairs at different times; the upper half deposits its int32
+  // partial sums in the workspace, the lower half adds them in its output stage (gemm_tcgen05_pair.cuh).
+  // 0: every tile whole.
+  int sk_tiles, sk_cut;
+  int32_t* sk_scratch;     // [tail tile][CTA rank][32-column chunk] partial sums of the upper K half
+  int* sk_flags;           // [tail tile][CTA rank] epilogue warps that have deposited; zero between launches
   // Row-sharded output (EPI_I32_ACC only): rows [g * rows_per_shard, (g + 1) * rows_per_shard) of C are
   // the dense int32 matrix shard[g] (pitch N), which may lie in the memory of another GPU; results are
   // ADDED there with system-scope reductions, one 128-byte row segment per warp instruction (measured
@@ -89,13 +89,19 @@ struct GemmParams {
   // rot_first lean on different owners.  rot_shards == 0: rows in order.
   int rot_shards, rot_first, rot_blocks_per_shard;
   // The other form of tail balancing: tiles >= nt_first_tile are cut into nt_parts column ranges
-  // (narrower MMAs, no exchange between the ranges).  nt_parts == 1: off.  Never together with sk_parts > 1.
+  // (narrower MMAs, no exchange between the ranges).  nt_parts == 1: off.  Never together with sk_tiles > 0.
   int nt_first_tile, nt_parts;
   // int32 products on the int8 tensor cores (see launch_mm_i32_tensor): operands are unsigned bytes and
   // the int32 result is shifted left (wrapping) before it is stored or added.
   int unsigned_ab, out_shift;
+  // The caller has declared that A and B are not written by the kernel launched before this one in the
+  // stream.  The warps that touch nothing but the operands and on-chip state (the TMA producer and the MMA
+  // issuer) then do not wait for that kernel to drain: the first tiles are multiplied while it finishes.
+  // The epilogue warps, which read and write everything else, always wait.
+  int early_operands;
   long long* cta_times;    // kMeasure (pair kernel): global nanosecond timer at entry / exit of every CTA, or null
-  long long* trace;        // kMeasure: per-tile clock64 stamps of CTA 0 (8 slots per tile), or null
+  long long* trace;        // kMeasure: per-tile clock64 stamps of CTA trace_cta (8 slots per tile), or null
+  int trace_cta;           // kMeasure: which CTA writes the stamps (environment variable AIEHLC_TRACE_CTA, default 0)
   int debug;               // test aid: 3 = the producer neither loads nor signals, so every consumer wait
                            // runs out and the kernel leaves through its bounded-wait exit;
                            // kMeasure: 1 = no TMA loads (MMA ceiling), 2 = no MMAs (feed ceiling),
@@ -472,7 +478,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   pdl_launch_dependents();
-  pdl_wait();  // from here on global memory may be read and written
+  // from here on global memory may be read and written (operands declared ready: warps 0 and 1 go ahead)
+  if (!(p.early_operands && warp < 2)) pdl_wait();
   if (kMeasure && p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
     p.trace[5] = entry_clock;
     p.trace[7] = static_cast<long long>(entry_ns);

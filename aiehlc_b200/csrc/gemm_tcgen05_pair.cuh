@@ -43,66 +43,67 @@ struct PairSmem {
   static constexpr int kTotal = kStages * kStageBytes + kStoreStagingBytes + kBarBytes + 1024;
 };
 
-// One unit of work of a CTA pair: a whole tile, one K range of a tail tile, or one column range of a tail tile.
+// One unit of work of a CTA pair: a whole tile, one K half of a tail tile, or one column range of a tail tile.
 struct WorkUnit {
-  int tile, kb0, kb1, part, parts;
+  int tile, kb0, kb1;   // K blocks [kb0, kb1) of the tile
   int n_part, n_parts;  // column range n_part of n_parts (1 = all kBN columns)
 };
+
 // Unit number `u` of the launch (pair p runs units p, p + pairs, p + 2 pairs, ...).
+//
+// Tail balancing along K (p.sk_tiles > 0): with T = full * pairs + rem tiles and rem <= pairs / 2, the last
+// rem tiles are cut at K block p.sk_cut into two halves, and the units are ordered
+//     [upper K halves of the rem tail tiles] [their lower K halves] [the T - rem whole tiles]
+// Round-robin over the pairs, the 2 rem halves run side by side in the first round (the other pairs start
+// on whole tiles), after which every pair has `full` whole tiles left: at most full + 1/2 tile times of
+// work per pair instead of full + 1, the pairs stay within half a tile of one another, and the partial sums
+// of a tile's two halves meet in the output stage of the lower half while its pair is already multiplying
+// its next tile.
 __device__ __forceinline__ bool work_unit(int u, const GemmParams& p, int num_tiles, WorkUnit& w) {
-  if (p.nt_parts > 1) {
-    if (u < p.nt_first_tile) {
-      w = WorkUnit{u, 0, p.num_k_blocks, 0, 1, 0, 1};
+  if (p.sk_tiles > 0) {
+    const int first = num_tiles - p.sk_tiles;  // the tail tiles are the last sk_tiles tiles
+    if (u < p.sk_tiles) {
+      w = WorkUnit{first + u, p.sk_cut, p.num_k_blocks, 0, 1};
       return true;
     }
+    u -= p.sk_tiles;
+    if (u < p.sk_tiles) {
+      w = WorkUnit{first + u, 0, p.sk_cut, 0, 1};
+      return true;
+    }
+    u -= p.sk_tiles;
+    if (u >= first) return false;
+    w = WorkUnit{u, 0, p.num_k_blocks, 0, 1};
+    return true;
+  }
+  if (p.nt_parts > 1 && u >= p.nt_first_tile) {
     const int v = u - p.nt_first_tile;
-    w = WorkUnit{p.nt_first_tile + v / p.nt_parts, 0, p.num_k_blocks, 0, 1, v % p.nt_parts, p.nt_parts};
+    w = WorkUnit{p.nt_first_tile + v / p.nt_parts, 0, p.num_k_blocks, v % p.nt_parts, p.nt_parts};
     return w.tile < num_tiles;
   }
-  if (u < p.sk_first_tile) {
-    w = WorkUnit{u, 0, p.num_k_blocks, 0, 1, 0, 1};
-    return true;
-  }
-  const int v = u - p.sk_first_tile;
-  if (p.sk_parts <= 1 || v >= (num_tiles - p.sk_first_tile) * p.sk_parts) {
-    if (p.sk_parts > 1 || u >= num_tiles) return false;
-    w = WorkUnit{u, 0, p.num_k_blocks, 0, 1, 0, 1};
-    return true;
-  }
-  const int part = v % p.sk_parts;
-  w.tile = p.sk_first_tile + v / p.sk_parts;
-  w.part = part;
-  w.parts = p.sk_parts;
-  w.n_part = 0;
-  w.n_parts = 1;
-  w.kb0 = static_cast<int>(static_cast<long long>(part) * p.num_k_blocks / p.sk_parts);
-  w.kb1 = static_cast<int>(static_cast<long long>(part + 1) * p.num_k_blocks / p.sk_parts);
+  if (u >= num_tiles) return false;
+  w = WorkUnit{u, 0, p.num_k_blocks, 0, 1};
   return true;
 }
 
 constexpr int kSkChunkInts = kBlockM * 32;  // one 32-column chunk of a CTA's 128 accumulator rows
 
-// The K ranges of a tail tile share the output stage: range q owns the 32-column chunks c with
-// (c * parts) / chunks == q.  Every range deposits the chunks it does not own as raw 32-bit words,
-// then adds the other ranges' deposits to the chunks it owns and runs the output stage on them.
-// Layout of a deposited chunk: [warp quadrant][j = 0..7][lane][4 words], so that every store or
-// load instruction of a warp moves 512 contiguous bytes (the layout never leaves this file).
+// The two K halves of a tail tile meet in the output stage.  The upper half deposits its 128 x kBN int32
+// partial sums per CTA in the tile's slot of the workspace and raises the slot's counter; the lower half
+// waits for the counter (bounded), streams the slot through its warps' staging buffers with bulk copies
+// (two 4 KB pieces in flight per warp), adds it to its own accumulator chunk by chunk and runs the
+// output stage.  Integer sums: the result is the whole-tile result bit for bit.
+// Layout of a deposited chunk: [warp quadrant][j = 0..7][lane][4 words], so that every store
+// instruction of a warp moves 512 contiguous bytes and a warp's share of a chunk is 4 contiguous KB
+// (the layout never leaves this file).
 __device__ __forceinline__ void deposit_chunk(const uint32_t (&r)[32], int32_t* chunk, int quad, int lane) {
   int4* dst = reinterpret_cast<int4*>(chunk + quad * 1024) + lane;
 #pragma unroll
   for (int j = 0; j < 8; ++j) dst[j * 32] = make_int4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
 }
-// Loads only: the values are consumed an iteration later, so the round trip to L2 overlaps other work.
-__device__ __forceinline__ void load_deposited_chunk(uint32_t (&d)[32], const int32_t* chunk, int quad, int lane) {
-  const int4* src = reinterpret_cast<const int4*>(chunk + quad * 1024) + lane;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int4 v = src[j * 32];
-    d[4 * j] = v.x; d[4 * j + 1] = v.y; d[4 * j + 2] = v.z; d[4 * j + 3] = v.w;
-  }
-}
-__device__ __forceinline__ void add_deposited_chunk(uint32_t (&r)[32], const int32_t* chunk, int quad, int lane) {
-  const int4* src = reinterpret_cast<const int4*>(chunk + quad * 1024) + lane;
+// Adds this lane's words of a chunk that a bulk copy has placed in shared memory (same layout).
+__device__ __forceinline__ void add_chunk_from_smem(uint32_t (&r)[32], const uint8_t* chunk, int lane) {
+  const int4* src = reinterpret_cast<const int4*>(chunk) + lane;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int4 v = src[j * 32];
@@ -145,6 +146,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   int* sk_warps_done = reinterpret_cast<int*>(tmem_base_slot + 2);
+  uint64_t* dep_bar = reinterpret_cast<uint64_t*>(tmem_base_slot + 4);  // two per epilogue warp quadrant (tail K halves)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -164,6 +166,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
       mbar_init(smem_u32(&tmem_empty_bar[a]), 8 * kEpiGroups);  // every epilogue warp of the two CTAs
     }
+    for (int q = 0; q < 8; ++q) mbar_init(smem_u32(&dep_bar[q]), 1);
     *abort_flag = 0;
     *sk_warps_done = 0;
     fence_mbar_init();
@@ -182,8 +185,9 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   pdl_launch_dependents();
-  pdl_wait();  // from here on global memory may be read and written
-  if (kMeasure && p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+  // from here on global memory may be read and written (operands declared ready: warps 0 and 1 go ahead)
+  if (!(p.early_operands && warp < 2)) pdl_wait();
+  if (kMeasure && p.trace && blockIdx.x == p.trace_cta && threadIdx.x == 0) {
     p.trace[5] = entry_clock;
     p.trace[7] = static_cast<long long>(entry_ns);
   }
@@ -247,7 +251,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                        ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
-        if (kMeasure && p.trace && blockIdx.x == 0) p.trace[it * 8 + 0] = clock64();
+        if (kMeasure && p.trace && blockIdx.x == p.trace_cta) p.trace[it * 8 + 0] = clock64();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         const uint32_t idesc = make_idesc<kKind>(kPairM, kBN / w.n_parts) &
                                ~(p.unsigned_ab ? ((1u << 7) | (1u << 10)) : 0u);  // bits 7, 10: signed A, B
@@ -274,7 +278,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit_pair_mask(smem_u32(&tmem_full_bar[acc]), 3);
-        if (kMeasure && p.trace && blockIdx.x == 0) p.trace[it * 8 + 1] = clock64();
+        if (kMeasure && p.trace && blockIdx.x == p.trace_cta) p.trace[it * 8 + 1] = clock64();
       }
     }
   } else {
@@ -292,7 +296,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tile_coords(w.tile, p, mb, nb);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const bool tracer = kMeasure && p.trace && blockIdx.x == 0 && warp == 2 && lane == 0;
+      const bool tracer = kMeasure && p.trace && blockIdx.x == p.trace_cta && warp == 2 && lane == 0;
       if (tracer) p.trace[it * 8 + 2] = clock64();
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xFFFFFFFFu, ok);
@@ -305,7 +309,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
       sc.warp_row0 = row - lane;
       select_shard(p, mb * kPairM + static_cast<int>(rank) * kBlockM, sc);
-      if (w.parts == 1) {
+      if (w.kb0 == 0 && w.kb1 == p.num_k_blocks) {
         const int ncols = kBN / w.n_parts;
         const int n0 = nb * kBN + w.n_part * ncols;
         // each group takes half of the columns where a half is whole 64-column drain steps and whole store groups
@@ -316,78 +320,86 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         else if (group == 0)
           drain_accumulator<kBN, kEpi>(p, taddr, row, row_ok, n0, sc, ncols);
       } else if (group == 0) {
-        // tail tile cut along K; scratch is [tail tile][depositing range][CTA rank][chunk]
+        // one K half of a tail tile; workspace slots and counters are per tail tile and CTA rank
         constexpr int kChunks = kBN / 32;
         constexpr long long kCtaInts = static_cast<long long>(kChunks) * kSkChunkInts;
-        const long long part_stride = 2 * kCtaInts;
-        const int tail = w.tile - p.sk_first_tile;
-        int32_t* tile_base = p.sk_scratch + static_cast<long long>(tail) * w.parts * part_stride + rank * kCtaInts;
-        int* flags = p.sk_flags + (tail * 2 + static_cast<int>(rank)) * 4;  // one counter per owning range
-        // 1. hand the chunks owned by other ranges over
+        const int slot_id = (w.tile - (num_tiles - p.sk_tiles)) * 2 + static_cast<int>(rank);
+        int32_t* slot = p.sk_scratch + slot_id * kCtaInts;
+        if (w.kb0 > 0) {
+          // upper half: hand the partial sums over and go on
 #pragma unroll 1
-        for (int c = 0; c < kChunks; ++c) {
-          if ((c * w.parts) / kChunks == w.part) continue;
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          deposit_chunk(r, tile_base + w.part * part_stride + c * kSkChunkInts, quad, lane);
-        }
-        __syncwarp();
-        if (lane == 0)
-          for (int q = 0; q < w.parts; ++q)
-            if (q != w.part) red_release_gpu_add(flags + q, 1);  // one arrival per epilogue warp
-        if (tracer && it >= 2) p.trace[it * 8 + 5] = clock64();
-        // 2. wait (bounded) for the 4 warps of every other range of this tile and CTA rank
-        const int want = 4 * (w.parts - 1);
-        if (lane == 0) {
-          const long long t0 = clock64();
-          while (ld_acquire_gpu(flags + w.part) < want) {
-            if (*abort_flag) { ok = false; break; }
-            if (clock64() - t0 > kWaitLimitCycles) {
-              *abort_flag = 1;
-              atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
-              ok = false;
-              break;
+          for (int c = 0; c < kChunks; c += 2) {
+            uint32_t ra[32], rb[32];
+            tmem_ld_32x32b_x32(taddr + c * 32, ra);
+            tmem_ld_32x32b_x32(taddr + c * 32 + 32, rb);
+            tmem_ld_wait();
+            deposit_chunk(ra, slot + c * kSkChunkInts, quad, lane);
+            deposit_chunk(rb, slot + (c + 1) * kSkChunkInts, quad, lane);
+          }
+          fence_proxy_async_global();  // the other side reads the slot with bulk copies
+          __syncwarp();
+          if (lane == 0) red_release_gpu_add(p.sk_flags + slot_id, 1);  // one arrival per epilogue warp
+        } else {
+          // lower half: owns the tile's output stage.  The slot arrives through this warp's two staging
+          // buffers (with two epilogue groups: its own and that of the idle warp of the other group).
+          // kLand pieces in flight: both staging buffers of the warp (with two epilogue groups a warp has one)
+          constexpr int kLand = kEpiGroups == 1 ? 2 : 1;
+          uint8_t* land[2] = {stage0, stage0 + kStoreBufBytes};
+          const uint32_t bar[2] = {smem_u32(&dep_bar[quad * 2]), smem_u32(&dep_bar[quad * 2 + 1])};
+          const int32_t* src = slot + quad * 1024;
+          if (lane == 0) {
+            tma_store_wait_read<0>();   // tile stores of an earlier unit have read the staging buffers
+            const long long t0 = clock64();
+            while (ok && ld_acquire_gpu(p.sk_flags + slot_id) < 4) {   // the upper half's four epilogue warps
+              if (*abort_flag) ok = false;
+              else if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
+                ok = false;
+              }
+            }
+            if (ok) {
+              fence_proxy_async_global();
+              fence_proxy_async_smem();
+#pragma unroll
+              for (int b = 0; b < kLand; ++b) {
+                mbar_expect_tx(bar[b], 4096);
+                bulk_load_g2s(smem_u32(land[b]), src + b * kSkChunkInts, 4096, bar[b]);
+              }
             }
           }
-        }
-        ok = __all_sync(0xFFFFFFFFu, ok);
-        if (tracer && it >= 2) p.trace[it * 8 + 6] = clock64();
-        if (ok) {
-          // 3. own chunks: accumulator + the other ranges' deposits, then the output stage.  The
-          //    deposits of the next chunk are requested before the current one is processed: they come
-          //    from L2 and one round trip per chunk would otherwise be the critical path.
-          const int c_begin = (w.part * kChunks + w.parts - 1) / w.parts;
-          const int c_end = ((w.part + 1) * kChunks + w.parts - 1) / w.parts;
-          // first other range: prefetched one chunk ahead; further ranges (parts > 2): added in place
-          const int q0 = w.part == 0 ? 1 : 0;
-          const int32_t* src0 = tile_base + q0 * part_stride;
-          uint32_t dep[32], dep_next[32];
-          if (c_begin < c_end) load_deposited_chunk(dep, src0 + c_begin * kSkChunkInts, quad, lane);
+          ok = __all_sync(0xFFFFFFFFu, ok);
+          if (tracer) p.trace[it * 8 + 6] = clock64();
 #pragma unroll 1
-          for (int c = c_begin; c < c_end; ++c) {
+          for (int c = 0; ok && c < kChunks; ++c) {
+            const int b = c % kLand;
             __syncwarp();
             uint32_t r[32];
             tmem_ld_32x32b_x32(taddr + c * 32, r);
-            if (c + 1 < c_end) load_deposited_chunk(dep_next, src0 + (c + 1) * kSkChunkInts, quad, lane);
+            ok = mbar_wait(bar[b], (c / kLand) & 1, abort_flag, p.status, ST_TIMEOUT_PEER);
+            ok = __all_sync(0xFFFFFFFFu, ok);
             tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] += dep[j];
-            for (int q = 0; q < w.parts; ++q)
-              if (q != w.part && q != q0) add_deposited_chunk(r, tile_base + q * part_stride + c * kSkChunkInts, quad, lane);
-            // a K range owns only part of the tile's columns: per-thread stores, not tile stores
-            if (row_ok && nb * kBN + c * 32 < p.N)
-              store_chunk<kEpi, kBN, true>(p, r, row, nb * kBN + c * 32, row_ok, sc);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) dep[j] = dep_next[j];
+            if (!ok) break;
+            add_chunk_from_smem(r, land[b], lane);
+            __syncwarp();   // every lane has read the buffer before it is refilled
+            if (lane == 0 && c + kLand < kChunks) {
+              fence_proxy_async_smem();
+              mbar_expect_tx(bar[b], 4096);
+              bulk_load_g2s(smem_u32(land[b]), src + (c + kLand) * kSkChunkInts, 4096, bar[b]);
+            }
+            // the staging buffers are taken: per-thread stores
+            const int col0 = nb * kBN + c * 32;
+            if (row_ok && col0 < p.N) store_chunk<kEpi, kBN, true>(p, r, row, col0, row_ok, sc);
           }
-          // 4. the last of the four warps to finish puts this range's counter back to zero for the next
-          //    launch (by then every warp is past its wait).  No blocking barrier: a warp that gave up on
-          //    its wait must not be able to strand the others.
-          __syncwarp();
-          if (lane == 0 && atomicAdd(sk_warps_done, 1) == 3) {
-            *sk_warps_done = 0;
-            flags[w.part] = 0;
+          if (ok) {
+            // The last of the four warps to finish puts the counter back to zero for the next launch (by
+            // then every warp is past its wait).  No blocking barrier among the four: a warp that gave up
+            // on its wait must not be able to strand the others.
+            __syncwarp();
+            if (lane == 0 && atomicAdd(sk_warps_done, 1) == 3) {
+              *sk_warps_done = 0;
+              p.sk_flags[slot_id] = 0;
+            }
           }
         }
       }
@@ -407,7 +419,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after();
     tmem_dealloc<2>(tmem_base, kTmemCols);
   }
-  if (kMeasure && p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (kMeasure && p.trace && blockIdx.x == p.trace_cta && threadIdx.x == 0) {
     p.trace[6] = clock64();
     p.trace[15] = static_cast<long long>(globaltimer_ns());
   }

@@ -225,6 +225,7 @@ int launch_mm_i32_tensor(aiehlc_ctx* ctx, const int32_t* in, int32_t* out, int M
       c.M = M; c.N = N; c.K = (s + 1) * Kp;
       c.lda = 4LL * Kp; c.ldb = 4LL * Kp; c.ldc = N;
       c.unsigned_ab = 1;
+      c.operands_from_kernel = 1;                  // the byte planes were written by the kernels just before
       c.out_shift = 8 * s;
       if (int rc = launch_gemm(ctx, c, st)) return rc;
     }

@@ -128,7 +128,7 @@ class Context:
         _capi.check(self._lib.aiehlc_set_epilogue_groups(self._h, int(groups)))
 
     def set_split_tail(self, mode) -> None:
-        """Thin last wave: 0/False = tiles whole, 1/True = cut along K, 2 = cut into two column ranges."""
+        """Last wave at most half full: 0/False = tiles whole, 1/True = K halves, 2 = column ranges, 3 = choose (default)."""
         _capi.check(self._lib.aiehlc_set_split_tail(self._h, int(mode)))
 
     def set_group_m(self, group_m: int) -> None:
@@ -137,6 +137,11 @@ class Context:
     def set_cta_limit(self, sms: int) -> None:
         """SMs the persistent GEMM kernels may occupy (0 = all)."""
         _capi.check(self._lib.aiehlc_set_cta_limit(self._h, int(sms)))
+
+    def set_operands_ready(self, on: bool) -> None:
+        """Promise that GEMM operands are never written by the kernel just before the call in its stream: loader and
+        multiplier warps then start while that kernel drains (aiehlc_set_operands_ready)."""
+        _capi.check(self._lib.aiehlc_set_operands_ready(self._h, 1 if on else 0))
 
     def set_pdl(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_pdl(self._h, 1 if on else 0))

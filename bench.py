@@ -905,6 +905,17 @@ def main() -> int:
     value = total_ops / (res["max_ms"] * 1e-3) / 1e12
     roofline = roofline_of(env, name, wl, wk, res)
     extra.update(res["note"])
+    if kind == "i8_srs" and world == 1:
+        # the same steps with the caller's promise that no operand is written by the kernel just before (true here:
+        # the inputs are resident buffers): loader and multiplier warps of launch i+1 start while launch i drains
+        env.ctx.set_operands_ready(True)
+        try:
+            r2 = timed(env, wk, args.steps, args.warmup, mode)
+            extra["with_operands_ready"] = {"value": wk.ops_per_step * r2["steps"] / (r2["max_ms"] * 1e-3) / 1e12, "unit": wk.unit,
+                                            "ms_per_step": r2["max_ms"] / r2["steps"], "device_status": r2["status"],
+                                            "what": "aiehlc_set_operands_ready(ctx, 1): off by default, not part of the headline"}
+        finally:
+            env.ctx.set_operands_ready(False)
     if kind == "i8_srs" and env.rank == 0 and not args.no_lib:
         extra["library_int8_tops"] = library_gemm(env, "int8", wl["M"], wl["N"], wl["K"], 50)
     if kind == "bf16" and env.rank == 0 and not args.no_lib:

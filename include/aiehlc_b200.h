@@ -161,8 +161,10 @@ typedef struct {
   int b_shared_by;                   /* tiles reading the same rows of B (B is shared along the M grid dimension) */
   long long wave_footprint_bytes;    /* operand bytes the tiles of one wave touch (L2 working set) */
   double cost_units;                 /* the quantity the choice minimises: waves x tile_n / efficiency factor */
-  int split_tail_tiles;              /* tiles of a thin last wave that are cut along K (int8 pair kernel), else 0 */
-  int split_tail_parts;              /* K ranges per such tile (1 = none) */
+  int split_k_tiles;                 /* int8 CTA-pair launches whose last wave is at most half full: that many tail tiles run as
+                                        two K halves on different pairs (the upper halves first, the lower halves last, their
+                                        int32 partial sums meeting in the output stage of the lower half); 0 = none */
+  int split_k_at;                    /* the K block (of 128 bytes) where those tiles are cut */
   int narrow_tail_tiles;             /* tiles of a thin last wave that are cut into two column ranges, else 0 */
 } aiehlc_gemm_plan;
 /* kind: 0 = int8, 1 = bf16.  ctx may be NULL: the plan is then made for a 148-SM B200 with default knobs. */

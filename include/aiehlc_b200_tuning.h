@@ -42,13 +42,16 @@ int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on);
  * 1 = four warps with two staging buffers each (better where K is deep); 0 (default) = 2 up to 8 K blocks of 128 bytes for int8 operands and 4 for bf16 (and never for a
  * row-sharded output, which the wire bounds), else 1. */
 int aiehlc_set_epilogue_groups(aiehlc_ctx* ctx, int groups);
-/* Tuning knob for a thin last wave (at most half of the CTA pairs busy) of a CTA-pair launch:
- *   1 = (int8 only) its tiles are cut along K into up to 4 ranges run by otherwise idle pairs; the ranges
- *       exchange int32 partial sums through a context workspace and each runs the output stage on its
- *       share of the columns (integer sums: bit-identical results);
- *   2 = (default) its 256-column tiles are cut into two 128-column ranges run by different pairs (narrower
+/* Tuning knob for a CTA-pair launch whose last wave is at most half full:
+ *   1 = (int8, at least one full wave, K >= 2048 bytes) the tail tiles run as two K halves on different
+ *       pairs: the upper halves first, the lower halves last, so that every pair has at most half a tile
+ *       more than the full waves; the upper half leaves its int32 partial sums in a context workspace and
+ *       the lower half adds them in its output stage (integer sums: bit-identical results);
+ *   2 = the 256-column tail tiles are cut into two 128-column ranges run by different pairs (narrower
  *       MMAs, nothing to exchange; every output element is still one accumulation over K in the same
  *       order);
+ *   3 = (default) whichever of the two measured faster: 2 (the halves' meeting through L2 costs the
+ *       feed-bound main loops more than the halves save);
  *   0 = every tile computed whole. */
 int aiehlc_set_split_tail(aiehlc_ctx* ctx, int on);
 /* Tuning knob for the *_host GEMM entry points: number of row blocks of A / C that upload, kernel and
@@ -92,6 +95,16 @@ int aiehlc_set_group_m(aiehlc_ctx* ctx, int group_m);
  * k<Col,Row,...>(in, out) turns into (aiehlc_kernels.h), and it lets several contexts share one GPU
  * side by side the way partitions share the AIE array. */
 int aiehlc_set_cta_limit(aiehlc_ctx* ctx, int sms);
+/* A promise by the caller, 0 (default) = none: with 1 the caller declares that, for every GEMM call on this
+ * context from now on, the operands A and B are NOT written by the kernel that precedes the call in its
+ * stream (they come from copies, or from kernels further back).  The GEMM kernels then let their loader
+ * and multiplier warps start on the first tiles while that preceding kernel is still draining, and only
+ * the output stage -- which reads acc_in and writes C -- waits for it to complete.  Back-to-back GEMMs on
+ * independent or long-resident operands overlap by up to a tile this way.  The library switches the early
+ * start off by itself where it has just launched a kernel that writes an operand (re-pitched operands,
+ * the byte planes of the int32 product).  Breaking the promise gives undefined results, never a fault.
+ * Only with programmatic launches (aiehlc_set_pdl 1). */
+int aiehlc_set_operands_ready(aiehlc_ctx* ctx, int on);
 /* Tuning knob: 1 (default) = the tensor-core kernels are launched with programmatic stream
  * serialization, so their set-up (barriers, TMEM allocation) overlaps the tail of the kernel before
  * them in the stream; they still wait for that kernel to complete before touching global memory.

@@ -202,33 +202,59 @@ def test_split_k_in_one_launch_and_as_cascade(ctx, splitk):
     assert np.array_equal(ctx.gemm_i8_srs_cascade(dA, dB, splitk, shift=8).cpu().numpy(), unsplit)
 
 
-@pytest.mark.parametrize("shape", [(1024, 1024, 4096), (512, 768, 2048), (1000, 900, 4112), (2304, 256, 4096),
-                                   (256, 256, 8192)])
-def test_split_tail_tiles_are_bit_identical(ctx, shape):
-    """A thin last wave is cut along K across idle CTA pairs (partial sums meet in a workspace):
-    same bits as the oracle and as the uncut schedule, launch after launch (the deposit counters
-    return to zero), for the int32 and the srs output stages."""
+@pytest.mark.parametrize("shape,tile_n,sms,k_per_load", [
+    ((4096, 4096, 2048), 0, 0, 0),       # 256 tiles on 74 pairs: 3 full waves + 34 tail tiles
+    ((2560, 2560, 4096), 0, 0, 0),       # 100 tiles: one full wave + 26
+    ((2700, 2300, 2176), 0, 0, 0),       # ragged edges, 17 K blocks (odd): halves of 10 and 7
+    ((2700, 2300, 2176), 0, 0, 1),       # ... one K block per tile load
+    ((5000, 3000, 2064), 0, 0, 0),       # K not a whole number of 128-byte blocks
+    ((2048, 1536, 2048), 128, 0, 0),     # 256 x 128 tiles: 96 of them
+    ((1280, 1024, 2048), 0, 32, 0),      # 16 pairs (a launch limited to 32 SMs): 20 tiles
+    ((1536, 1792, 8192), 0, 24, 0),      # 12 pairs, 42 tiles, a deep K: 64 blocks per tile
+])
+def test_tail_tiles_as_k_halves_are_bit_identical(ctx, shape, tile_n, sms, k_per_load):
+    """A last wave at most half full runs as K halves: the upper halves first, the lower halves last, the partial
+    sums added in the lower half's output stage.  Same bits as the oracle and as the whole-tile schedule, launch
+    after launch (the deposit counters return to zero), for the int32, the accumulating and the srs output
+    stages and both store forms."""
     from aiehlc_b200.ops import plan_gemm
     M, N, K = shape
     ctx.set_cta_pair(1)
-    ctx.set_split_tail(True)
+    ctx.set_tile_n(tile_n)
+    ctx.set_cta_limit(sms)
+    ctx.set_k_per_load(k_per_load)
+    ctx.set_split_tail(1)
     try:
         plan = plan_gemm(M, N, K, ctx=ctx)
-        assert plan["split_tail_parts"] > 1, plan
+        assert 0 < plan["split_k_tiles"] <= plan["slots"] // 2 and plan["narrow_tail_tiles"] == 0, plan
+        assert 8 <= plan["split_k_at"] <= plan["k_blocks"] - 7
         A = synth.int8_uniform(6, (M, K))
         B = synth.int8_uniform(1006, (N, K))
         dA, dB = _dev(A), _dev(B)
         exp32 = O.gemm_i8_i32(A, B)
+        sv = (np.arange(N) % 13 + 3).astype(np.uint8)
         exp8 = O.gemm_i8_srs(A, B, shift=9)
-        for _ in range(3):
-            assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), exp32)
+        exp8v = O.gemm_i8_srs(A, B, shift_vec=sv, acc_in=exp32)
+        d32 = _dev(exp32)
+        for rep in range(3):
+            ctx.set_tma_store(rep)                  # 0: per-thread stores, 1: tile stores for int32, 2: for int8 too
+            got = ctx.gemm_i8_i32(dA, dB)
+            assert np.array_equal(got.cpu().numpy(), exp32)
+            ctx.gemm_i8_i32(dA, dB, out=got, accumulate=True)
+            assert np.array_equal(got.cpu().numpy(), 2 * exp32)
             assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift=9).cpu().numpy(), exp8)
-        ctx.set_split_tail(False)
-        assert plan_gemm(M, N, K, ctx=ctx)["split_tail_parts"] == 1
+            assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift_vec=_dev(sv), acc_in=d32).cpu().numpy(), exp8v)
+        ctx.set_tma_store(1)
+        ctx.set_split_tail(0)
+        assert plan_gemm(M, N, K, ctx=ctx)["split_k_tiles"] == 0
         assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), exp32)
         assert ctx.sync() == 0
     finally:
-        ctx.set_split_tail(2)
+        ctx.set_tma_store(1)
+        ctx.set_split_tail(3)
+        ctx.set_k_per_load(0)
+        ctx.set_cta_limit(0)
+        ctx.set_tile_n(0)
         ctx.set_cta_pair(-1)
 
 
@@ -252,14 +278,14 @@ def test_tail_tiles_cut_into_column_ranges(ctx, shape, k_per_load):
         ctx.set_split_tail(0)
         whole = ctx.gemm_bf16(Ab, Bb)
         ctx.set_split_tail(2)
-        assert plan_gemm(M, N, K, ctx=ctx)["narrow_tail_tiles"] > 0
+        assert plan_gemm(M, N, K, ctx=ctx)["narrow_tail_tiles"] > 0 and plan_gemm(M, N, K, ctx=ctx)["split_k_tiles"] == 0
         for _ in range(2):
             assert np.array_equal(ctx.gemm_i8_i32(dA, dB).cpu().numpy(), O.gemm_i8_i32(A, B))
             assert np.array_equal(ctx.gemm_i8_srs(dA, dB, shift=9).cpu().numpy(), O.gemm_i8_srs(A, B, shift=9))
         assert torch.equal(ctx.gemm_bf16(Ab, Bb), whole)
         assert ctx.sync() == 0
     finally:
-        ctx.set_split_tail(2)
+        ctx.set_split_tail(3)
         ctx.set_k_per_load(0)
         ctx.set_tile_n(0)
         ctx.set_cta_pair(-1)
@@ -418,6 +444,41 @@ def test_sm_limit_changes_the_schedule_not_the_result(ctx, shape):
     finally:
         ctx.set_cta_limit(0)
     assert ctx.sync() == 0
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+def test_operands_declared_ready_start_early_same_bits(ctx, pair):
+    """With the caller's promise that operands are not written by the preceding kernel, loader and multiplier
+    warps start while that kernel drains; the output stage still waits.  Back-to-back launches on rotating
+    operands, a cascade whose partial sums come from the kernel just before, and operands the library re-pitches
+    itself (where it must not start early): the same bits as without the promise."""
+    ctx.set_cta_pair(pair)
+    shapes = [(1024, 768, 1024), (2304, 2304, 512), (300, 520, 1152), (4096, 4096, 1024), (2560, 3072, 2048)]
+    try:
+        for (M, N, K) in shapes:
+            sets = [(_dev(synth.int8_uniform(70 + i, (M, K))), _dev(synth.int8_uniform(1070 + i, (N, K)))) for i in range(4)]
+            ctx.set_operands_ready(False)
+            want = [(ctx.gemm_i8_i32(a, b), ctx.gemm_i8_srs(a, b, shift=7)) for a, b in sets]
+            want_chain = ctx.gemm_i8_srs_cascade(sets[0][0], sets[0][1], stages=4, shift=9)
+            ctx.set_operands_ready(True)
+            for rep in range(5):
+                got = []
+                for a, b in sets:                      # launches queue up behind one another
+                    got.append((ctx.gemm_i8_i32(a, b), ctx.gemm_i8_srs(a, b, shift=7)))
+                for (g32, g8), (w32, w8) in zip(got, want):
+                    assert torch.equal(g32, w32) and torch.equal(g8, w8)
+                assert torch.equal(ctx.gemm_i8_srs_cascade(sets[0][0], sets[0][1], stages=4, shift=9), want_chain)
+        # K = 1001: both operands are re-pitched by a kernel of the library right before the GEMM
+        A, B = synth.int8_uniform(80, (384, 1001)), synth.int8_uniform(1080, (320, 1001))
+        for rep in range(3):
+            assert np.array_equal(ctx.gemm_i8_i32(_dev(A), _dev(B)).cpu().numpy(), O.gemm_i8_i32(A, B))
+        rng = np.random.default_rng(5)
+        inp = rng.integers(-2**31, 2**31 - 1, size=(512 + 384) * 1000, dtype=np.int64).astype(np.int32)
+        assert np.array_equal(ctx.mm_i32(_dev(inp), 512, 384, 1000).cpu().numpy(), O.mm_i32(inp, 512, 384, 1000))
+        assert ctx.sync() == 0
+    finally:
+        ctx.set_operands_ready(False)
+        ctx.set_cta_pair(-1)
 
 
 @pytest.mark.parametrize("pair", [0, 1])

@@ -62,7 +62,8 @@ def test_gemm_planner_needs_no_gpu():
     # two 128-byte K blocks per tile load: three 64 KiB stages hold what six 32 KiB stages did
     assert p["tile_k_bytes"] == 256 and p["stages"] == 3
     assert (p["a_shared_by"], p["b_shared_by"]) == (16, 16)   # A rows serve a grid row, B rows a grid column
-    assert p["split_tail_parts"] == 1 and p["narrow_tail_tiles"] == 34   # last wave: 34 tiles as 68 column ranges
+    # 3 full waves + 34 tiles: by default the 34 tail tiles run as 68 column ranges (measured faster than K halves)
+    assert p["split_k_tiles"] == 0 and p["narrow_tail_tiles"] == 34
     p = plan_gemm(64, 64, 64)                           # one tile: a single CTA, the narrowest tile
     assert (p["tile_m"], p["tile_n"], p["cta_pair"], p["tiles"], p["waves"]) == (128, 64, 0, 1, 1)
     p = plan_gemm(8192, 8192, 8192, kind="bf16")
@@ -70,6 +71,30 @@ def test_gemm_planner_needs_no_gpu():
     from aiehlc_b200 import _capi
     with pytest.raises(_capi.AiehlcError):
         plan_gemm(0, 4, 4)
+
+
+def test_k_halves_schedule_gives_every_pair_at_most_half_a_tile_more():
+    """Host logic of the tail balancing along K (the unit order the kernels walk, restated): upper halves, lower
+    halves, whole tiles, dealt round-robin -- every tile's K range is covered exactly once, the halves all run in
+    the first round, and no pair has more than full + 1/2 tile times of work."""
+    # (tiles, pairs, K blocks) of a few launches; the cut is the planner's: an even number of blocks in the lower half
+    for (T, P, nkb) in [(256, 74, 32), (100, 74, 32), (99, 74, 17), (256, 74, 16), (320, 74, 32), (20, 16, 16), (42, 12, 64)]:
+        rem, cut = T % P, (nkb // 2 + 1) & ~1
+        assert 0 < rem <= P // 2
+        first = T - rem
+        units = [(first + u, cut, nkb) for u in range(rem)] + [(first + u, 0, cut) for u in range(rem)] + \
+                [(t, 0, nkb) for t in range(first)]
+        cover = {}
+        for t, a, b in units:
+            cover.setdefault(t, []).append((a, b))
+        assert all(sorted(v) in ([(0, nkb)], [(0, cut), (cut, nkb)]) for v in cover.values()) and len(cover) == T
+        for pair in range(P):
+            mine = units[pair::P]
+            work = sum(b - a for _, a, b in mine)
+            assert work <= (T // P) * nkb + max(cut, nkb - cut)
+            halves = [i for i, (t, a, b) in enumerate(mine) if b - a < nkb]
+            assert halves in ([], [0])                 # a pair has at most one half, and it is its first unit
+        assert all(u < P for u in range(2 * rem))  # both halves of every tail tile run in the first round, side by side
 
 
 def test_tile_visiting_order_needs_no_gpu():
