@@ -57,6 +57,7 @@ SIGNATURES = {
     "aiehlc_set_k_per_load": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_shard_tile_stores": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_conv_halo": (C.c_int, [_vp, C.c_int]),
+    "aiehlc_set_conv_persistent": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_conv_wide_n": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_mm_i32_tensor": (C.c_int, [_vp, C.c_int]),
     "aiehlc_set_conv_hwio_direct": (C.c_int, [_vp, C.c_int]),
@@ -90,7 +91,7 @@ class ConvPlan(C.Structure):
     """aiehlc_conv_plan of include/aiehlc_b200.h."""
     _fields_ = [(n, C.c_int) for n in ("form", "tile_rows", "tile_width", "patch_rows", "patch_width", "m_rows_used",
                                        "cout_tile", "cin_chunk", "ctas", "tma_boxes_per_cta", "mmas_per_cta", "stages",
-                                       "smem_bytes", "launches")]
+                                       "smem_bytes", "launches", "persistent")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -258,6 +258,12 @@ int aiehlc_set_conv_hwio_direct(aiehlc_ctx* ctx, int on) {
   return AIEHLC_OK;
 }
 
+int aiehlc_set_conv_persistent(aiehlc_ctx* ctx, int on) {
+  if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  ctx->conv_persistent = on ? 1 : 0;
+  return AIEHLC_OK;
+}
+
 int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
   ctx->conv_halo = on ? 1 : 0;

@@ -61,6 +61,14 @@ struct ConvParams {
   uint32_t b_lbo_bytes;            // N-major weights: distance between the taps' column blocks
   uint32_t swizzle_code, sbo_bytes;
   uint32_t tmem_cols;
+  // Persistent form (many tiles per SM: batches): a CTA keeps its channel tile's weights -- every tap -- in
+  // shared memory for its whole life and walks spatial tiles blockIdx.x, blockIdx.x + gridDim.x, ...; input
+  // patches arrive through a ring of `stages` buffers and the accumulator is double-buffered, so the loads,
+  // the MMAs and the output stage of consecutive tiles overlap.  Patch form with one cin chunk only.
+  int persistent;
+  int spatial_tiles;               // n * tiles_h * tiles_w
+  uint32_t w_region_bytes;         // shared memory reserved for the weights (multiple of 1 KB)
+  uint32_t acc_stride;             // TMEM columns between the two accumulators
   int8_t* y;
   const uint8_t* shift_vec;
   int* status;
@@ -335,6 +343,189 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   if (tracing && threadIdx.x == 0) p.trace[6] = clock64();
 }
 
+// The persistent form of the kernel above (ConvParams::persistent): same tiles, same operand views, same
+// arithmetic; what changes is that a CTA outlives its tile.
+//   warp 0   : the channel tile's weights once, then one input patch per tile into the ring
+//   warp 1   : per tile kh * kw * chunk / 32 MMAs (every tap a view into the patch) into accumulator (tile & 1)
+//   warps 2-5: per tile the output stage (per-channel srs) of the accumulator the MMAs have left
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                            const ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* w_smem = smem;                                   // [tap][cout_tile x chunk] (or the N-major box)
+  uint8_t* patches = smem + p.w_region_bytes;               // `stages` patches of a_bytes each
+  uint8_t* bar_mem = patches + p.stages * p.a_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);
+  uint64_t* empty_bar = full_bar + kConvMaxStages;
+  uint64_t* tmem_full_bar = empty_bar + kConvMaxStages;     // two
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;             // two
+  uint64_t* w_bar = tmem_empty_bar + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(w_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  uint8_t* shift_smem = reinterpret_cast<uint8_t*>(tmem_base_slot + 2);  // this CTA's cout_tile shift bytes (<= 256)
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);  // one arrival per epilogue warp
+    }
+    mbar_init(smem_u32(w_bar), 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(tmem_base_slot), p.tmem_cols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // a weight pre-pass before this kernel has completed; global memory may be touched
+  const int co0 = blockIdx.y * p.cout_tile;
+  const int taps = p.kh * p.kw;
+  if (warp >= 2) {
+    const int i = threadIdx.x - 64;
+    for (int c = i; c < 256; c += 128) {
+      const int col = co0 + c;
+      shift_smem[c] = (c < p.cout_tile && col < p.cout) ? p.shift_vec[col] : 0;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+  }
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t wb = smem_u32(w_bar);
+      mbar_expect_tx(wb, static_cast<uint32_t>(taps) * p.w_block_bytes);
+      if (p.w_n_major) tma_load_3d(smem_u32(w_smem), &tmap_w, wb, co0, 0, 0);   // {cout, cin, tap}
+      else tma_load_3d(smem_u32(w_smem), &tmap_w, wb, 0, co0, 0);                 // {cin, cout, tap}
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += gridDim.x) {
+        int r = t;
+        const int tw = r % p.tiles_w; r /= p.tiles_w;
+        const int th = r % p.tiles_h; r /= p.tiles_h;
+        ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
+        if (!ok) break;
+        const uint32_t fb = smem_u32(&full_bar[stage]);
+        mbar_expect_tx(fb, p.tx_bytes);
+        // the whole patch; what lies outside the image reads as zero: that is the padding
+        tma_load_4d(smem_u32(patches + stage * p.a_bytes), &tmap_x, fb, 0, tw * p.wt - p.pad, th * p.rows_per_tile - p.pad, r);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+      if (!ok)
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc<KIND_I8>(kBlockM, p.cout_tile) | (p.w_n_major ? (1u << 16) : 0u);
+      bool ok = mbar_wait(smem_u32(w_bar), 0, abort_flag, p.status, ST_TIMEOUT_FULL);
+      const uint64_t b0 = make_kmajor_desc(smem_u32(w_smem), p.b_sbo_bytes, p.b_swizzle_code);
+      const uint32_t px_step = static_cast<uint32_t>(p.chunk) >> 4;
+      const uint32_t row_step = px_step * p.row_w, w_step = p.w_block_bytes >> 4;
+      const int ksteps = p.chunk / kUmmaKBytes;
+      int stage = 0, it = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), ((it >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * p.acc_stride;
+        const uint64_t a0 = make_kmajor_desc(smem_u32(patches + stage * p.a_bytes), p.sbo_bytes, p.swizzle_code);
+        uint64_t bd = b0;
+        uint32_t accum = 0u;
+        for (int fh = 0; fh < p.kh; ++fh) {
+          uint64_t ad = a0 + fh * row_step;   // tap (fh, fw) reads the patch (fh * row_w + fw) rows further on
+          for (int fw = 0; fw < p.kw; ++fw) {
+#pragma unroll 4
+            for (int k = 0; k < ksteps; ++k) {
+              umma_ss<KIND_I8, 1>(d_tmem, ad + 2 * k, bd + k * p.b_kstep, idesc, accum);
+              accum = 1u;
+            }
+            ad += px_step;
+            bd += w_step;
+          }
+        }
+        umma_commit(smem_u32(&empty_bar[stage]));     // the patch buffer is free once these MMAs have read it
+        umma_commit(smem_u32(&tmem_full_bar[acc]));
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int m = quad * 32 + lane;
+    const int mr = m / p.row_w, mc = m - mr * p.row_w;   // image row and column inside the tile
+    const bool vec = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && (p.cout % 16 == 0);
+    bool ok = true;
+    int it = 0;
+    for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += gridDim.x, ++it) {
+      int r = t;
+      const int tw = r % p.tiles_w; r /= p.tiles_w;
+      const int th = r % p.tiles_h; r /= p.tiles_h;
+      const int acc = it & 1;
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int oh = th * p.rows_per_tile + mr, ow = tw * p.wt + mc;
+      const bool pix_ok = mr < p.rows_per_tile && mc < p.wt && oh < p.h && ow < p.w;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * p.acc_stride;
+      int8_t* yrow = p.y + ((static_cast<long long>(r) * p.h + oh) * p.w + ow) * p.cout;
+      for (int c = 0; c < p.cout_tile; c += 32) {
+        __syncwarp();
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(taddr + c, v);
+        tmem_ld_wait();
+        const int col0 = co0 + c;
+        if (!pix_ok || col0 >= p.cout) continue;
+        const int ncols = min(32, min(p.cout_tile - c, p.cout - col0));
+        uint32_t packed[8];
+        int q[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int sh = static_cast<int>(shift_smem[c + j]);
+          q[j] = srs_round<true>(static_cast<int>(v[j]), sh, max(static_cast<int>((1u << sh) >> 1) - 1, 0), min(sh, 1));
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) packed[j >> 2] = pack_sat_s8x4(q[j], q[j + 1], q[j + 2], q[j + 3]);
+        if (vec && ncols == 32) {
+          *reinterpret_cast<uint4*>(yrow + col0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(yrow + col0 + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < ncols) yrow[col0 + j] = static_cast<int8_t>((packed[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+        }
+      }
+      // accumulator drained: hand it back to the MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, p.tmem_cols);
+  }
+}
+
 // HWIO [tap][cin][cout] -> [tap][cout][cin]: makes the weights K-major like every other operand.
 __global__ void conv_weight_prepack_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ wp,
                                            int taps, int cin, int cout) {
@@ -400,6 +591,8 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* weights, 
                        int wd, int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st);
 bool conv_hwio_direct(const aiehlc_ctx* ctx, const int8_t* w, int n, int h, int wd, int cin, int cout, int kh, int kw,
                       int pad);
+struct ConvParams;
+void conv_persistent_setup(const aiehlc_ctx* ctx, ConvParams& p, int n_tiles);
 
 int launch_conv2d(aiehlc_ctx* ctx, const int8_t* x, const int8_t* w, int8_t* y, int n, int h, int wd,
                   int cin, int cout, int kh, int kw, int pad, const uint8_t* shift_vec, cudaStream_t st,
@@ -511,6 +704,31 @@ void configure_conv(const aiehlc_ctx* ctx, ConvParams& p, int* n_tiles_out) {
   *n_tiles_out = n_tiles;
 }
 
+// Whether a configured convolution runs in the persistent form, and its shared-memory / TMEM layout.
+// Taken when every SM would otherwise see two or more CTAs of the one-tile kernel (batches, large images):
+// then the weights are fetched once per CTA instead of once per tile and consecutive tiles overlap.
+void conv_persistent_setup(const aiehlc_ctx* ctx, ConvParams& p, int n_tiles) {
+  p.persistent = 0;
+  p.spatial_tiles = p.n * p.tiles_h * p.tiles_w;
+  if (!ctx->conv_persistent || !p.halo || p.chunks_per_tap != 1 || p.wide_n) return;
+  if (static_cast<long long>(p.spatial_tiles) * n_tiles < 2LL * ctx->sm_count) return;
+  const int taps = p.kh * p.kw;
+  const uint32_t w_bytes = (static_cast<uint32_t>(taps) * p.w_block_bytes + 1023u) / 1024u * 1024u;
+  const int budget = 200 * 1024;
+  int stages = (budget - static_cast<int>(w_bytes)) / p.a_bytes;
+  if (stages < 2) return;                       // no room to overlap loads with MMAs: keep the one-tile form
+  if (stages > 6) stages = 6;
+  p.persistent = 1;
+  p.w_split = 0;                                // the weights arrive once, as one box
+  p.w_region_bytes = w_bytes;
+  p.stages = stages;
+  p.tx_bytes = static_cast<uint32_t>(p.chunk) * p.row_w * (p.rows_per_tile + p.kh - 1);   // one patch
+  p.acc_stride = static_cast<uint32_t>(p.cout_tile + 31) / 32u * 32u;
+  uint32_t cols = 32;
+  while (cols < 2 * p.acc_stride) cols <<= 1;
+  p.tmem_cols = cols;
+}
+
 // What launch_conv2d_packed will do, for the exported planner.
 int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, int kh, int kw, int pad,
                 aiehlc_conv_plan* out) {
@@ -545,6 +763,18 @@ int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, 
   pl.m_rows_used = p.rows_per_tile * p.row_w;
   pl.launches = (ctx->conv_hwio_direct && p.halo && (p.cout_tile == 32 || p.cout_tile == 64 || p.cout_tile == 128) &&
                  cout % p.cout_tile == 0) ? 1 : 2;
+  p.w_block_bytes = static_cast<uint32_t>(p.cout_tile) * p.chunk;
+  p.wide_n = (p.halo && ctx->conv_wide_n && kw > 1 && kw <= 4 && kw * p.cout_tile <= 256) ? 1 : 0;
+  conv_persistent_setup(ctx, p, n_tiles);
+  pl.persistent = p.persistent;
+  if (p.persistent) {
+    const int per_channel_tile = ctx->sm_count / n_tiles > 0 ? ctx->sm_count / n_tiles : 1;
+    pl.ctas = (p.spatial_tiles < per_channel_tile ? p.spatial_tiles : per_channel_tile) * n_tiles;
+    pl.stages = p.stages;
+    pl.smem_bytes = static_cast<int>(p.w_region_bytes) + p.stages * p.a_bytes + 2048;
+    pl.tma_boxes_per_cta = 1 + (p.spatial_tiles * n_tiles + pl.ctas - 1) / pl.ctas;   // the weights, then a patch per tile
+    pl.mmas_per_cta *= (p.spatial_tiles * n_tiles + pl.ctas - 1) / pl.ctas;
+  }
   *out = pl;
   return AIEHLC_OK;
 }
@@ -594,6 +824,8 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
                                      : static_cast<uint32_t>(p.cout_tile);
   while (cols < acc_cols) cols <<= 1;
   p.tmem_cols = cols;
+  // many tiles per SM: the persistent form (weights resident, patches and accumulators double-buffered)
+  conv_persistent_setup(ctx, p, n_tiles);
   p.y = y; p.shift_vec = shift_vec; p.status = ctx->d_status;
   p.trace = ctx->trace;
 
@@ -646,11 +878,17 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
     if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
   }
 
-  const int smem_bytes = p.stages * p.stage_bytes + 1024 + 8192 + 1024;
-  KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(conv2d_i8_kernel)];
-  if (int rc = ensure_dynamic_smem(ctx->device, reinterpret_cast<const void*>(conv2d_i8_kernel), smem_bytes, &ks.smem_attr))
+  const int smem_bytes = p.persistent ? static_cast<int>(p.w_region_bytes) + p.stages * p.a_bytes + 1024 + 1024
+                                      : p.stages * p.stage_bytes + 1024 + 8192 + 1024;
+  auto kern = p.persistent ? conv2d_i8_persistent_kernel : conv2d_i8_kernel;
+  KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
+  if (int rc = ensure_dynamic_smem(ctx->device, reinterpret_cast<const void*>(kern), smem_bytes, &ks.smem_attr))
     return rc;
   dim3 grid(n * p.tiles_h * p.tiles_w, n_tiles);
+  if (p.persistent) {
+    const int per_channel_tile = ctx->sm_count / n_tiles > 0 ? ctx->sm_count / n_tiles : 1;
+    grid.x = p.spatial_tiles < per_channel_tile ? p.spatial_tiles : per_channel_tile;
+  }
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -661,7 +899,7 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 1 : 0;
-  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, conv2d_i8_kernel, mx, mw, p));
+  AIEHLC_CUDA(cudaLaunchKernelEx(&cfg, kern, mx, mw, p));
   ctx->launches++;
   return AIEHLC_OK;
 }

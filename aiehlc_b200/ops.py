@@ -110,6 +110,9 @@ class Context:
     def set_conv_wide_n(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_conv_wide_n(self._h, 1 if on else 0))
 
+    def set_conv_persistent(self, on: bool) -> None:
+        _capi.check(self._lib.aiehlc_set_conv_persistent(self._h, 1 if on else 0))
+
     def set_conv_halo(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_conv_halo(self._h, 1 if on else 0))
 

@@ -57,6 +57,9 @@ WORKLOADS = {
     "shallow_k": dict(M=16384, N=4096, K=512, kind="i8_i32", scaling="weak", bound="hbm",
                       desc="int8 GEMM 16384x4096x512 -> int32: 268 MB of results over 4 K blocks, the output stage "
                            "sets the pace (two groups of epilogue warps)"),
+    "scatter_local": dict(M=16384, N=8192, K=2048, kind="i8_i32_scatter", shards=8, scaling="weak", bound="hbm",
+                          desc="int8 GEMM 16384x8192x2048 added into 8 row shards of an int32 result, all shards in this "
+                               "GPU's memory: the split-K exchange kernel (aiehlc_gemm_i8_i32_scatter_dev) without a wire"),
     "cfg5_splitk": dict(M=65536, N=8192, K=8192, kind="i8_i32_splitk", splitk=8, scaling="strong",
                         desc="int8 GEMM 65536x8192x8192 -> int32, split-K 8 over the GPUs, int32 partial sums "
                              "exchanged between the GPUs (how: splitk_exchange)"),
@@ -424,7 +427,7 @@ def make_gemm(env: Env, name: str, wl: dict, sets: int = 0) -> Work:
     else:
         row0, m_local = shard.row_shard(M, world, rank)
     esize = 2 if kind == "bf16" else (4 if kind == "mm_i32" else 1)
-    out_esize = {"i8_srs": 1, "i8_i32": 4, "bf16": 2, "mm_i32": 4}[kind]
+    out_esize = {"i8_srs": 1, "i8_i32": 4, "bf16": 2, "mm_i32": 4, "i8_i32_scatter": 4}[kind]
     set_bytes = m_local * K * esize + N * K * esize + m_local * N * out_esize
     nsets = max(1, min(8, -(-2 * L2_BYTES // set_bytes))) if set_bytes < 2 * L2_BYTES else 1
     if sets > 0:
@@ -454,6 +457,10 @@ def make_gemm(env: Env, name: str, wl: dict, sets: int = 0) -> Work:
         calls = [(lambda j=j: ctx.mm_i32(As[j], m_local, N, K, out=Cs[j])) for j in range(nsets)]
     elif kind == "bf16":
         calls = [ctx.bound_gemm_bf16(As[j], Bs[j], Cs[j]) for j in range(nsets)]
+    elif kind == "i8_i32_scatter":
+        rows = m_local // wl["shards"]
+        calls = [ctx.bound_gemm_i8_i32_scatter(As[j], Bs[j], [Cs[j][g * rows:(g + 1) * rows].data_ptr() for g in range(wl["shards"])],
+                                               rows, N, first_shard=1) for j in range(nsets)]
     else:
         calls = [ctx.bound_gemm_i8_i32(As[j], Bs[j], Cs[j]) for j in range(nsets)]
     wk.nsets = nsets
@@ -573,11 +580,12 @@ def roofline_of(env: Env, name: str, wl: dict, wk: Work, res: dict) -> dict:
     if wl.get("bound") == "hbm":
         # a product over a shallow K: the result bytes, not the MMAs, bound the launch
         m, n, k = wk.shape
-        gemm_bytes = m * k + n * k + m * n * 4
+        gemm_bytes = m * k + n * k + m * n * 4 * (2 if wk.kind == "i8_i32_scatter" else 1)   # an add reads what it writes
         gbs = gemm_bytes / (per_launch_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"], "traffic": traffic,
-                    "note": f"algorithmic bytes A + B + C(int32) = {gemm_bytes / 1e6:.1f} MB per launch; peak {peaks['source']}"}
+                    "note": f"algorithmic bytes A + B + C(int32{', read and written' if wk.kind == 'i8_i32_scatter' else ''}) = "
+                            f"{gemm_bytes / 1e6:.1f} MB per launch; peak {peaks['source']}"}
     if wk.kind == "mm_i32":
         # one int32 product costs ten int8 limb products (K + 2K + 3K + 4K bytes of depth)
         roofline["achieved"] = achieved * 10.0
@@ -853,6 +861,7 @@ def main() -> int:
     ap.add_argument("--no-configs", action="store_true", help="only the headline workload, none of the other configurations")
     ap.add_argument("--sets", type=int, default=0, help="number of rotating input sets (0 = enough to exceed L2)")
     ap.add_argument("--sustained-seconds", type=float, default=2.2)
+    ap.add_argument("--batch", type=int, default=0, help="cfg4: images per call (0 = the configuration's own 1)")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off", "gate"],
                     help="gate (auto for GEMMs, at every number of GPUs): one call per step, the first ones queued "
                          "behind a stream gate before the clock starts; on (auto for the launch-bound cfg1 and cfg4): "
@@ -896,7 +905,7 @@ def main() -> int:
                 print(json.dumps(line), flush=True)
             dist.destroy_process_group()
             return 0
-    wk = make_conv(env, wl) if kind == "conv" else make_gemm(env, name, wl, args.sets)
+    wk = make_conv(env, wl, args.batch or None) if kind == "conv" else make_gemm(env, name, wl, args.sets)
     mode = default_mode(wk, args.graph)
     res = timed(env, wk, args.steps, args.warmup, mode)
     total_ops = wk.ops_per_step * res["steps"] * world

@@ -192,6 +192,9 @@ typedef struct {
   int ctas, tma_boxes_per_cta, mmas_per_cta, stages, smem_bytes;
   int launches;              /* kernels per aiehlc_conv2d_i8_srs_dev call: 1, or 2 when the HWIO weights are re-laid first
                                 (16-byte aligned weights assumed) */
+  int persistent;            /* 1 = many tiles per SM: `ctas` persistent CTAs keep the weights in shared memory and walk
+                                the tiles (stages = input patches in flight); tma_boxes_per_cta and mmas_per_cta then
+                                count a CTA's whole walk */
 } aiehlc_conv_plan;
 int aiehlc_plan_conv2d(aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, int kh, int kw, int pad,
                        aiehlc_conv_plan* plan);

@@ -63,6 +63,11 @@ int aiehlc_set_host_blocks(aiehlc_ctx* ctx, int blocks);
  * activation box and one weight box per tap.  Filters whose taps do not fit in shared memory take the
  * second form whatever the setting. */
 int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on);
+/* Tuning knob for the convolution kernel: 1 (default) = where every SM would see two or more tiles (batches,
+ * large images; patch form, cin 32, 64 or 128) a CTA keeps its channel tile's weights in shared memory for its
+ * whole life and walks the tiles, input patches arriving through a ring of buffers and the accumulator
+ * double-buffered, so loads, MMAs and output stage of consecutive tiles overlap; 0 = always one CTA per tile. */
+int aiehlc_set_conv_persistent(aiehlc_ctx* ctx, int on);
 /* Tuning knob for aiehlc_mm_i32_*: 1 (default) = products of at least 2^24 multiply-adds (K >= 64) run on the
  * int8 tensor cores: the int32 operands are cut into unsigned bytes, four int8 GEMMs (one per power of
  * 256, operands of K, 2K, 3K and 4K bytes; K in ranges of 8192 so that no partial sum can reach 2^31) add

@@ -42,8 +42,72 @@ def test_conv2d_matches_oracle(ctx, shape, halo, direct, wide):
     finally:
         ctx.set_conv_halo(True)
         ctx.set_conv_hwio_direct(True)
-        ctx.set_conv_wide_n(True)
+        ctx.set_conv_wide_n(False)
     assert np.array_equal(got, exp)
+
+
+@pytest.mark.parametrize("n", [8, 32, 128])
+def test_conv2d_batches_of_the_benchmark_layer(ctx, n):
+    """The 56 x 56 x 64 -> 64 layer at batch 8, 32 and 128: images are independent, so every image of the batched
+    call equals the single-image call on it (itself bit-exact against the oracle), in every form; two images
+    per batch are also checked against the oracle directly."""
+    x = synth.int8_uniform(40 + n, (n, 56, 56, 64))
+    wt = synth.int8_uniform(1040 + n, (3, 3, 64, 64))
+    sv = (np.arange(64) % 7 + 3).astype(np.uint8)
+    dx, dw, dsv = _dev(x), _dev(wt), _dev(sv)
+    got = ctx.conv2d_i8_srs(dx, dw, dsv, pad=1)
+    for img in (0, n - 1):
+        assert np.array_equal(got[img].cpu().numpy(), O.conv2d_i8_srs(x[img:img + 1], wt, sv, pad=1)[0])
+    single = torch.cat([ctx.conv2d_i8_srs(dx[i:i + 1].contiguous(), dw, dsv, pad=1) for i in range(n)])
+    assert torch.equal(got, single)
+    try:
+        for halo, direct, wide, persistent in ((True, True, True, True), (True, False, False, True), (False, False, False, True),
+                                               (True, True, False, False)):
+            ctx.set_conv_halo(halo)
+            ctx.set_conv_hwio_direct(direct)
+            ctx.set_conv_wide_n(wide)
+            ctx.set_conv_persistent(persistent)
+            assert torch.equal(ctx.conv2d_i8_srs(dx, dw, dsv, pad=1), got)
+    finally:
+        ctx.set_conv_halo(True)
+        ctx.set_conv_hwio_direct(True)
+        ctx.set_conv_wide_n(False)
+        ctx.set_conv_persistent(True)
+    assert ctx.sync() == 0
+
+
+@pytest.mark.parametrize("shape,kh,pad", [((32, 56, 56, 64, 64), 3, 1),      # the benchmark layer at batch 32
+                                          ((48, 28, 28, 32, 48), 3, 1),      # weights re-laid first (channel tile 48)
+                                          ((6, 60, 60, 128, 272), 3, 1),     # 17 channel tiles of 16: the CTAs are split between them
+                                          ((8, 40, 40, 64, 64), 5, 2),       # 5 x 5 filter
+                                          ((4, 30, 300, 64, 32), 3, 1),      # images wider than a tile
+                                          ((80, 17, 23, 128, 16), 3, 1)])    # ragged tiles, few channels
+def test_conv2d_persistent_form_matches_one_tile_form(ctx, shape, kh, pad):
+    """Many tiles per SM: CTAs keep the weights in shared memory and walk the tiles.  Same bits as the one-CTA-per-tile
+    form (itself checked against the oracle shape by shape), launch after launch; the first and last image are
+    also checked against the oracle directly."""
+    from aiehlc_b200.ops import plan_conv2d
+    n, h, w, cin, cout = shape
+    x = synth.int8_uniform(31, (n, h, w, cin))
+    wt = synth.int8_uniform(1031, (kh, kh, cin, cout))
+    sv = (np.arange(cout) % 9 + 2).astype(np.uint8)
+    dx, dw, dsv = _dev(x), _dev(wt), _dev(sv)
+    try:
+        ctx.set_conv_persistent(False)
+        assert plan_conv2d(n, h, w, cin, cout, kh, kh, pad, ctx=ctx)["persistent"] == 0
+        want = ctx.conv2d_i8_srs(dx, dw, dsv, pad=pad)
+        ctx.set_conv_persistent(True)
+        plan = plan_conv2d(n, h, w, cin, cout, kh, kh, pad, ctx=ctx)
+        assert plan["persistent"] == 1 and plan["ctas"] <= ctx.sm_count, plan
+        for _ in range(3):
+            assert torch.equal(ctx.conv2d_i8_srs(dx, dw, dsv, pad=pad), want)
+        packed = ctx.conv2d_pack_weights(dw)                      # weights re-laid by the caller: the K-major operand
+        assert torch.equal(ctx.conv2d_i8_srs_packed(dx, packed, (kh, kh), dsv, pad=pad), want)
+    finally:
+        ctx.set_conv_persistent(True)
+    for img in (0, n - 1):
+        assert np.array_equal(want[img].cpu().numpy(), O.conv2d_i8_srs(x[img:img + 1], wt, sv, pad=pad)[0])
+    assert ctx.sync() == 0
 
 
 def test_conv2d_benchmark_shape_is_one_launch(ctx):
@@ -129,9 +193,18 @@ def test_gemm_bf16_within_tolerance(ctx, shape):
     assert np.array_equal(got_dev, got)
 
 
+def _bf16_tight(got_f64, ref_f64, K):
+    """Second metric, scaled to the data: with N(0,1) operands the sums have a spread of sqrt(K), so 1e-2
+    against max(|ref|, 1) is loose for outputs near zero.  A result rounded to bf16 (8 mantissa bits) from an
+    fp32 accumulation must satisfy |got - ref| <= 2^-8 |ref| + 1e-3 sqrt(K); a lost K block (an error of about
+    sqrt(128)) does not."""
+    bound = np.abs(ref_f64) / 256.0 + 1e-3 * np.sqrt(K)
+    return float(np.max(np.abs(got_f64 - ref_f64) / bound))
+
+
 def test_gemm_bf16_8192_sampled(ctx):
     """bf16 8192^3: 64 full rows + 64 full columns + 4096 random elements against the fp32-accumulated
-    oracle, tolerance 1e-2 (abs-or-rel with eps = 1)."""
+    oracle, tolerance 1e-2 (abs-or-rel with eps = 1), and the tighter data-scaled bound on the same samples."""
     M = N = K = 8192
     A = synth.normal_bf16_bits(3, (M, K))
     B = synth.normal_bf16_bits(1003, (N, K))
@@ -143,12 +216,17 @@ def test_gemm_bf16_8192_sampled(ctx):
     rows = np.sort(rng.choice(M, 64, replace=False))
     cols = np.sort(rng.choice(N, 64, replace=False))
     got_rows = C[torch.from_numpy(rows).to(DEV)].view(torch.int16).cpu().numpy().view(np.uint16)
-    assert _bf16_err(got_rows, O.gemm_bf16(A[rows], B).astype(np.float64)) <= BF16_TOL
+    ref_rows = O.gemm_bf16(A[rows], B).astype(np.float64)
+    assert _bf16_err(got_rows, ref_rows) <= BF16_TOL
+    assert _bf16_tight(synth.bf16_bits_to_f32(got_rows).astype(np.float64), ref_rows, K) <= 1.0
     got_cols = C[:, torch.from_numpy(cols).to(DEV)].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
-    assert _bf16_err(got_cols, O.gemm_bf16(A, B[cols]).astype(np.float64)) <= BF16_TOL
+    ref_cols = O.gemm_bf16(A, B[cols]).astype(np.float64)
+    assert _bf16_err(got_cols, ref_cols) <= BF16_TOL
+    assert _bf16_tight(synth.bf16_bits_to_f32(got_cols).astype(np.float64), ref_cols, K) <= 1.0
     ii, jj = rng.integers(0, M, 4096), rng.integers(0, N, 4096)
     a32 = synth.bf16_bits_to_f32(A[ii]).astype(np.float64)
     b32 = synth.bf16_bits_to_f32(B[jj]).astype(np.float64)
     ref = np.einsum("ik,ik->i", a32, b32)
     got = C[torch.from_numpy(ii).to(DEV), torch.from_numpy(jj).to(DEV)].float().cpu().numpy().astype(np.float64)
     assert float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0))) <= BF16_TOL
+    assert _bf16_tight(got, ref, K) <= 1.0
