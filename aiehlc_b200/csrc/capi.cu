@@ -260,7 +260,9 @@ int aiehlc_set_conv_hwio_direct(aiehlc_ctx* ctx, int on) {
 
 int aiehlc_set_conv_persistent(aiehlc_ctx* ctx, int on) {
   if (!ctx) return fail(AIEHLC_ERR_INVALID, "null context");
+  if (on < 0 || on > 4) return fail(AIEHLC_ERR_INVALID, "conv_persistent: 0 (off), 1 (on), 2 / 3 / 4 (on, one / two / four tiles per MMA group)");
   ctx->conv_persistent = on ? 1 : 0;
+  ctx->conv_mma_group = on >= 2 ? (on == 4 ? 4 : on - 1) : 0;
   return AIEHLC_OK;
 }
 

@@ -87,6 +87,7 @@ struct aiehlc_ctx {
   int conv_split_weights = 1;   // patch form: one weight box per filter row, each on its own barrier
   int conv_hwio_direct = 1;     // conv consumes HWIO weights as an N-major operand where it can (no re-layout launch)
   int conv_halo = 1;            // conv kernel fetches a tile's whole input patch and all taps' weights in two boxes
+  int conv_mma_group = 0;       // persistent conv: 0 choose, 1 = one tile's MMAs at a time, 2 = two tiles interleaved
   int conv_persistent = 1;      // many tiles per SM: CTAs keep the weights and walk the tiles (patches, accumulators double-buffered)
   int cta_limit = 0;            // persistent GEMM kernels occupy at most this many SMs (0 = all of them)
   int usable_sms() const { return cta_limit > 0 && cta_limit < sm_count ? cta_limit : sm_count; }

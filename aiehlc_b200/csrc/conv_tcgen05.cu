@@ -22,6 +22,7 @@ namespace aiehlc {
 
 constexpr int kConvMaxStages = 12;
 constexpr int kConvThreads = 192;
+constexpr int kConvPersistentThreads = 192;   // producer, MMA issuer, four epilogue warps
 
 struct ConvParams {
   int n, h, w, cin, cout, kh, kw, pad;
@@ -68,7 +69,9 @@ struct ConvParams {
   int persistent;
   int spatial_tiles;               // n * tiles_h * tiles_w
   uint32_t w_region_bytes;         // shared memory reserved for the weights (multiple of 1 KB)
-  uint32_t acc_stride;             // TMEM columns between the two accumulators
+  uint32_t acc_stride;             // TMEM columns between accumulators
+  int mma_group;                   // tiles whose MMAs are issued interleaved (1, 2 or 4): 2 * mma_group accumulators in TMEM
+  int srs_wide;                    // |acc| + 2^shift may reach 2^31: round in 64-bit arithmetic
   int8_t* y;
   const uint8_t* shift_vec;
   int* status;
@@ -347,8 +350,9 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 // arithmetic; what changes is that a CTA outlives its tile.
 //   warp 0   : the channel tile's weights once, then one input patch per tile into the ring
 //   warp 1   : per tile kh * kw * chunk / 32 MMAs (every tap a view into the patch) into accumulator (tile & 1)
-//   warps 2-5: per tile the output stage (per-channel srs) of the accumulator the MMAs have left
-__global__ void __launch_bounds__(kConvThreads, 1)
+//   warps 2-5: per tile the output stage (per-channel srs) of the accumulator the MMAs have left (a second group
+//              of four warps taking every other 32-column chunk was measured: no faster)
+__global__ void __launch_bounds__(kConvPersistentThreads, 1)
 conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                             const ConvParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -359,25 +363,24 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   uint8_t* bar_mem = patches + p.stages * p.a_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);
   uint64_t* empty_bar = full_bar + kConvMaxStages;
-  uint64_t* tmem_full_bar = empty_bar + kConvMaxStages;     // two
-  uint64_t* tmem_empty_bar = tmem_full_bar + 2;             // two
-  uint64_t* w_bar = tmem_empty_bar + 2;
+  uint64_t* group_full_bar = empty_bar + kConvMaxStages;    // two: the MMAs of tile group g (g & 1) have completed
+  uint64_t* tmem_empty_bar = group_full_bar + 2;            // one per accumulator (up to eight)
+  uint64_t* w_bar = tmem_empty_bar + 8;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(w_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   uint8_t* shift_smem = reinterpret_cast<uint8_t*>(tmem_base_slot + 2);  // this CTA's cout_tile shift bytes (<= 256)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const bool tracing = kMeasure && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;   // 4 stamps per tile of CTA 0
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 4);       // the four epilogue warps, once they have seen the tile's MMAs complete
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);  // one arrival per epilogue warp
-    }
+    for (int a = 0; a < 8; ++a) mbar_init(smem_u32(&tmem_empty_bar[a]), 4);  // one arrival per epilogue warp
+    for (int g = 0; g < 2; ++g) mbar_init(smem_u32(&group_full_bar[g]), 1);
     mbar_init(smem_u32(w_bar), 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -435,34 +438,50 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       const uint32_t px_step = static_cast<uint32_t>(p.chunk) >> 4;
       const uint32_t row_step = px_step * p.row_w, w_step = p.w_block_bytes >> 4;
       const int ksteps = p.chunk / kUmmaKBytes;
-      int stage = 0, it = 0;
-      uint32_t phase = 0;
-      for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += gridDim.x, ++it) {
-        const int acc = it & 1;
-        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), ((it >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-        if (!ok) break;
-        ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, ST_TIMEOUT_FULL);
+      // The MMAs of a GROUP of up to four consecutive tiles are issued interleaved, each tile into its own
+      // accumulator: back-to-back MMAs into ONE accumulator of this width run at the pipe's latency (measured:
+      // one per ~270 cycles), interleaved over two accumulators one per ~150.  One commit per group: a commit
+      // costs about as much as two such MMAs.
+      const int G = p.mma_group, accs = 2 * G;   // accumulators in TMEM: the tile with sequence number s uses s % accs
+      int seq = 0, group = 0;                    // tiles and groups this CTA has started
+      for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += G * static_cast<int>(gridDim.x), ++group) {
+        int nt = (p.spatial_tiles - t + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);   // tiles left
+        if (nt > G) nt = G;
+        uint32_t d[4];
+        uint64_t a0[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          d[j] = 0; a0[j] = 0;
+          if (j < nt && ok) {
+            const int s_ = seq + j, acc = s_ % accs, st = s_ % p.stages;   // accumulator free, patch landed
+            ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), ((s_ / accs) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+            if (ok) ok = mbar_wait(smem_u32(&full_bar[st]), (s_ / p.stages) & 1, abort_flag, p.status, ST_TIMEOUT_FULL);
+            d[j] = tmem_base + acc * p.acc_stride;
+            a0[j] = make_kmajor_desc(smem_u32(patches + st * p.a_bytes), p.sbo_bytes, p.swizzle_code);
+          }
+        }
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * p.acc_stride;
-        const uint64_t a0 = make_kmajor_desc(smem_u32(patches + stage * p.a_bytes), p.sbo_bytes, p.swizzle_code);
+        if (tracing && seq < 60) p.trace[seq * 4 + 0] = clock64();
         uint64_t bd = b0;
         uint32_t accum = 0u;
         for (int fh = 0; fh < p.kh; ++fh) {
-          uint64_t ad = a0 + fh * row_step;   // tap (fh, fw) reads the patch (fh * row_w + fw) rows further on
+          uint32_t a_off = fh * row_step;   // tap (fh, fw) reads the patch (fh * row_w + fw) rows further on
           for (int fw = 0; fw < p.kw; ++fw) {
-#pragma unroll 4
+#pragma unroll 2
             for (int k = 0; k < ksteps; ++k) {
-              umma_ss<KIND_I8, 1>(d_tmem, ad + 2 * k, bd + k * p.b_kstep, idesc, accum);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (j < nt) umma_ss<KIND_I8, 1>(d[j], a0[j] + a_off + 2 * k, bd + k * p.b_kstep, idesc, accum);
               accum = 1u;
             }
-            ad += px_step;
+            a_off += px_step;
             bd += w_step;
           }
         }
-        umma_commit(smem_u32(&empty_bar[stage]));     // the patch buffer is free once these MMAs have read it
-        umma_commit(smem_u32(&tmem_full_bar[acc]));
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        umma_commit(smem_u32(&group_full_bar[group & 1]));   // every tile of the group: accumulator ready, patch read
+        if (tracing && seq < 60) p.trace[seq * 4 + 1] = clock64();
+        seq += nt;
       }
     }
   } else {
@@ -470,17 +489,23 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     const int m = quad * 32 + lane;
     const int mr = m / p.row_w, mc = m - mr * p.row_w;   // image row and column inside the tile
     const bool vec = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && (p.cout % 16 == 0);
+    // 32-bit rounding needs |acc| + 2^shift < 2^31: the host knows the bound on |acc| (p.srs_wide), the shifts are here
+    int max_shift = 0;
+    for (int c = 0; c < p.cout_tile; ++c) max_shift = max(max_shift, static_cast<int>(shift_smem[c]));
+    const bool wide = p.srs_wide || max_shift > 29;
     bool ok = true;
     int it = 0;
     for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += gridDim.x, ++it) {
       int r = t;
       const int tw = r % p.tiles_w; r /= p.tiles_w;
       const int th = r % p.tiles_h; r /= p.tiles_h;
-      const int acc = it & 1;
-      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      const int G = p.mma_group, accs = 2 * G, acc = it % accs, group = it / G;
+      ok = mbar_wait(smem_u32(&group_full_bar[group & 1]), (group >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (lane == 0) mbar_arrive(smem_u32(&empty_bar[it % p.stages]));   // the tile's MMAs have read its patch
+      if (tracing && warp == 2 && lane == 0 && it < 60) p.trace[it * 4 + 2] = clock64();
       const int oh = th * p.rows_per_tile + mr, ow = tw * p.wt + mc;
       const bool pix_ok = mr < p.rows_per_tile && mc < p.wt && oh < p.h && ow < p.w;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * p.acc_stride;
@@ -495,10 +520,18 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
         const int ncols = min(32, min(p.cout_tile - c, p.cout - col0));
         uint32_t packed[8];
         int q[32];
+        if (wide) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int sh = static_cast<int>(shift_smem[c + j]);
-          q[j] = srs_round<true>(static_cast<int>(v[j]), sh, max(static_cast<int>((1u << sh) >> 1) - 1, 0), min(sh, 1));
+          for (int j = 0; j < 32; ++j) {
+            const int sh = static_cast<int>(shift_smem[c + j]);
+            q[j] = srs_round<true>(static_cast<int>(v[j]), sh, max(static_cast<int>((1u << sh) >> 1) - 1, 0), min(sh, 1));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int sh = static_cast<int>(shift_smem[c + j]);
+            q[j] = srs_round<false>(static_cast<int>(v[j]), sh, max(static_cast<int>((1u << sh) >> 1) - 1, 0), min(sh, 1));
+          }
         }
 #pragma unroll
         for (int j = 0; j < 32; j += 4) packed[j >> 2] = pack_sat_s8x4(q[j], q[j + 1], q[j + 2], q[j + 3]);
@@ -514,6 +547,7 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       // accumulator drained: hand it back to the MMA issuer
       tc_fence_before();
       __syncwarp();
+      if (tracing && warp == 2 && lane == 0 && it < 60) p.trace[it * 4 + 3] = clock64();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
   }
@@ -717,15 +751,21 @@ void conv_persistent_setup(const aiehlc_ctx* ctx, ConvParams& p, int n_tiles) {
   const int budget = 200 * 1024;
   int stages = (budget - static_cast<int>(w_bytes)) / p.a_bytes;
   if (stages < 2) return;                       // no room to overlap loads with MMAs: keep the one-tile form
-  if (stages > 6) stages = 6;
+  if (stages > 8) stages = 8;
   p.persistent = 1;
   p.w_split = 0;                                // the weights arrive once, as one box
   p.w_region_bytes = w_bytes;
   p.stages = stages;
   p.tx_bytes = static_cast<uint32_t>(p.chunk) * p.row_w * (p.rows_per_tile + p.kh - 1);   // one patch
   p.acc_stride = static_cast<uint32_t>(p.cout_tile + 31) / 32u * 32u;
+  // the MMAs of up to four tiles interleaved, as far as 2 G accumulators fit in TMEM and 2 G patches in the ring
+  int g = ctx->conv_mma_group > 0 ? ctx->conv_mma_group : 4;
+  while (g > 1 && (2 * g * p.acc_stride > 512 || stages < 2 * g)) g /= 2;
+  p.mma_group = g;
+  // |acc| <= taps * cin * 2^14: below 2^30 the kernel may round in 32 bits where the shifts allow it too
+  p.srs_wide = static_cast<long long>(taps) * p.cin > 65535 ? 1 : 0;
   uint32_t cols = 32;
-  while (cols < 2 * p.acc_stride) cols <<= 1;
+  while (cols < 2 * p.mma_group * p.acc_stride) cols <<= 1;
   p.tmem_cols = cols;
 }
 
@@ -894,7 +934,7 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(kConvThreads);
+  cfg.blockDim = dim3(p.persistent ? kConvPersistentThreads : kConvThreads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = st;
   cfg.attrs = attr;

@@ -110,8 +110,10 @@ class Context:
     def set_conv_wide_n(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_conv_wide_n(self._h, 1 if on else 0))
 
-    def set_conv_persistent(self, on: bool) -> None:
-        _capi.check(self._lib.aiehlc_set_conv_persistent(self._h, 1 if on else 0))
+    def set_conv_persistent(self, on) -> None:
+        """0/False: one CTA per tile; 1/True: persistent form where it applies; 2 / 3: the same with the MMAs of one tile
+        at a time / of two tiles interleaved."""
+        _capi.check(self._lib.aiehlc_set_conv_persistent(self._h, int(on)))
 
     def set_conv_halo(self, on: bool) -> None:
         _capi.check(self._lib.aiehlc_set_conv_halo(self._h, 1 if on else 0))

@@ -965,7 +965,7 @@ def main() -> int:
             try:
                 cwl = WORKLOADS[cname]
                 cwk = make_conv(env, cwl) if cwl["kind"] == "conv" else make_gemm(env, cname, cwl)
-                cmode = default_mode(cwk, "auto")
+                cmode = default_mode(cwk, args.graph)
                 r = timed(env, cwk, csteps, 3, cmode)
                 rec = sub_record(env, cname, cwl, cwk, r)
                 if cname == "cfg3" and not args.no_lib:
@@ -977,7 +977,7 @@ def main() -> int:
                     batches = {}
                     for nb in (8, 32, 128):
                         bwk = make_conv(env, cwl, nb)
-                        br = timed(env, bwk, 40, 3, default_mode(bwk, "auto"))
+                        br = timed(env, bwk, 40, 3, default_mode(bwk, args.graph))
                         per_ms = br["local_ms"] / br["steps"]
                         batches[f"n{nb}"] = {"value": bwk.ops_per_step / (per_ms * 1e-3) / 1e12, "unit": "TOPS",
                                              "us_per_call": per_ms * 1e3, "GBps": bwk.alg_bytes / (per_ms * 1e-3) / 1e9,
@@ -997,7 +997,7 @@ def main() -> int:
                 swk = make_gemm(env, "cfg2", wl, args.sets)
                 per_ms = res["local_ms"] / res["steps"]
                 n_sus = max(100, int(args.sustained_seconds * 1e3 / per_ms * 1.15))
-                r = timed(env, swk, n_sus, 3, "gate")
+                r = timed(env, swk, n_sus, 3, "plain" if args.graph == "off" else "gate")
                 rec = sub_record(env, "cfg2", wl, swk, r)
                 rec["seconds"] = r["local_ms"] / 1e3
                 configs["sustained"] = rec

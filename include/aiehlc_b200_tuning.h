@@ -66,7 +66,9 @@ int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on);
 /* Tuning knob for the convolution kernel: 1 (default) = where every SM would see two or more tiles (batches,
  * large images; patch form, cin 32, 64 or 128) a CTA keeps its channel tile's weights in shared memory for its
  * whole life and walks the tiles, input patches arriving through a ring of buffers and the accumulator
- * double-buffered, so loads, MMAs and output stage of consecutive tiles overlap; 0 = always one CTA per tile. */
+ * double-buffered, so loads, MMAs and output stage of consecutive tiles overlap; 0 = always one CTA per tile;
+ * 2 / 3 = as 1, with the MMAs of one tile at a time / of two tiles interleaved (1 chooses: two where four
+ * accumulators fit in TMEM). */
 int aiehlc_set_conv_persistent(aiehlc_ctx* ctx, int on);
 /* Tuning knob for aiehlc_mm_i32_*: 1 (default) = products of at least 2^24 multiply-adds (K >= 64) run on the
  * int8 tensor cores: the int32 operands are cut into unsigned bytes, four int8 GEMMs (one per power of

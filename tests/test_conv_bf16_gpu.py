@@ -91,6 +91,8 @@ def test_conv2d_persistent_form_matches_one_tile_form(ctx, shape, kh, pad):
     x = synth.int8_uniform(31, (n, h, w, cin))
     wt = synth.int8_uniform(1031, (kh, kh, cin, cout))
     sv = (np.arange(cout) % 9 + 2).astype(np.uint8)
+    if cout == 32:
+        sv[5] = 31                        # a shift that needs 64-bit rounding
     dx, dw, dsv = _dev(x), _dev(wt), _dev(sv)
     try:
         ctx.set_conv_persistent(False)
@@ -99,8 +101,10 @@ def test_conv2d_persistent_form_matches_one_tile_form(ctx, shape, kh, pad):
         ctx.set_conv_persistent(True)
         plan = plan_conv2d(n, h, w, cin, cout, kh, kh, pad, ctx=ctx)
         assert plan["persistent"] == 1 and plan["ctas"] <= ctx.sm_count, plan
-        for _ in range(3):
-            assert torch.equal(ctx.conv2d_i8_srs(dx, dw, dsv, pad=pad), want)
+        for mode in (2, 3, 4, 1):         # the MMAs of one tile at a time, of two, of four tiles interleaved, the default
+            ctx.set_conv_persistent(mode)
+            for _ in range(2):
+                assert torch.equal(ctx.conv2d_i8_srs(dx, dw, dsv, pad=pad), want)
         packed = ctx.conv2d_pack_weights(dw)                      # weights re-laid by the caller: the K-major operand
         assert torch.equal(ctx.conv2d_i8_srs_packed(dx, packed, (kh, kh), dsv, pad=pad), want)
     finally:
