@@ -22,7 +22,7 @@ namespace aiehlc {
 
 constexpr int kConvMaxStages = 12;
 constexpr int kConvThreads = 192;
-constexpr int kConvPersistentThreads = 192;   // producer, MMA issuer, four epilogue warps
+constexpr int kConvPersistentThreads = 320;   // producer, MMA issuer, two groups of four epilogue warps
 
 struct ConvParams {
   int n, h, w, cin, cout, kh, kw, pad;
@@ -78,6 +78,94 @@ struct ConvParams {
   long long* trace;   // kMeasure: clock64 stamps of CTA 0, or null
 };
 
+// How an epilogue warp rounds: decided once per CTA from the channel tile's shifts.
+struct SrsPlan {
+  int mode;                 // 0: one shift for every channel, 32-bit; 1: per channel, 32-bit; 2: per channel, 64-bit
+  int sh, half, mask;       // mode 0: the shift, 2^(shift-1) - 1 and 1 (0 and 0 for shift 0), kept in registers
+};
+// 32-bit rounding needs |acc| + 2^shift < 2^31: `acc_wide` says whether |acc| <= taps * cin * 2^14 can pass 2^30,
+// the shifts are read here.
+__device__ __forceinline__ SrsPlan srs_plan(const uint8_t* shift_smem, int cout_tile, bool acc_wide) {
+  int max_shift = 0, min_shift = 255;
+  for (int c = 0; c < cout_tile; ++c) {
+    const int sh = static_cast<int>(shift_smem[c]);
+    max_shift = max(max_shift, sh);
+    min_shift = min(min_shift, sh);
+  }
+  SrsPlan pl;
+  const bool wide = acc_wide || max_shift > 29;
+  pl.mode = wide ? 2 : (min_shift == max_shift ? 0 : 1);
+  pl.sh = max_shift;
+  pl.half = max_shift > 0 ? static_cast<int>((1u << (max_shift - 1)) - 1u) : 0;
+  pl.mask = min(max_shift, 1);
+  return pl;
+}
+// 32 accumulator columns of one output pixel -> srs -> int8 -> global memory.  `shifts` and `halves` point at the
+// chunk's first channel (halves[c] = 2^(shift-1) - 1, 0 for shift 0).
+__device__ __forceinline__ void conv_store_chunk(const uint32_t (&v)[32], const SrsPlan& pl, const uint8_t* shifts,
+                                                 const int* halves, int8_t* dst, int ncols, bool vec) {
+  int q[32];
+  if (pl.mode == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) q[j] = srs_round<false>(static_cast<int>(v[j]), pl.sh, pl.half, pl.mask);
+  } else if (pl.mode == 1) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int sh = static_cast<int>(shifts[j]);
+      q[j] = srs_round<false>(static_cast<int>(v[j]), sh, halves[j], min(sh, 1));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int sh = static_cast<int>(shifts[j]);
+      q[j] = srs_round<true>(static_cast<int>(v[j]), sh, halves[j], min(sh, 1));
+    }
+  }
+  uint32_t packed[8];
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) packed[j >> 2] = pack_sat_s8x4(q[j], q[j + 1], q[j + 2], q[j + 3]);
+  if (vec && ncols == 32) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) dst[j] = static_cast<int8_t>((packed[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+  }
+}
+
+// The MMAs of one tile in the patch form: for every tap and K step one MMA, the operand descriptors given as
+// their 32-bit halves (only the address field moves, and never past its 14 bits: every operand lies below
+// 256 KB).  KH, KW, KS > 0 fix the filter and the K steps per tap at compile time, so the loops unroll and the
+// offsets are a few multiples of row_step: the one issuing thread, which spends ~10 cycles on every dependent
+// instruction of its own, is left with an add and the MMA per product (measured on the 3 x 3 x 64 layer:
+// ~75 cycles per MMA instead of ~220 with 64-bit descriptor sums inside counted loops).
+// `w_row_bar` != nullptr: the weights of filter row fh arrive on their own barrier, waited for here.
+template <int KH, int KW, int KS>
+__device__ __forceinline__ bool conv_issue_tile(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t idesc, uint32_t accum, int kh, int kw, int ksteps,
+                                                uint32_t row_step, uint32_t px_step, uint32_t w_step, uint32_t b_kstep,
+                                                uint64_t* w_row_bar, volatile int* abort_flag, int* status) {
+  const int nh = KH > 0 ? KH : kh, nw = KW > 0 ? KW : kw, nk = KS > 0 ? KS : ksteps;
+#pragma unroll
+  for (int fh = 0; fh < nh; ++fh) {
+    if (w_row_bar != nullptr) {
+      if (!mbar_wait(smem_u32(&w_row_bar[fh]), 0, abort_flag, status, ST_TIMEOUT_FULL)) return false;
+      tc_fence_after();
+    }
+#pragma unroll
+    for (int fw = 0; fw < nw; ++fw) {
+#pragma unroll
+      for (int k = 0; k < nk; ++k) {
+        umma_ss_i8_halves(d, a_lo + fh * row_step + fw * px_step + 2 * k, a_hi,
+                          b_lo + (fh * nw + fw) * w_step + k * b_kstep, b_hi, idesc, accum);
+        accum = 1u;
+      }
+    }
+  }
+  return true;
+}
+
 __global__ void __launch_bounds__(kConvThreads, 1)
 conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const ConvParams p) {
@@ -94,6 +182,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   uint8_t* shift_smem = reinterpret_cast<uint8_t*>(tmem_base_slot + 2);  // this CTA's cout_tile shift bytes (<= 256)
   // wide N: rows 0 .. kw-2 of every warp's column blocks 1 .. kw-1, for the warp before it (behind the barriers' 1 KB)
   uint32_t* xchg = reinterpret_cast<uint32_t*>(bar_mem + 1024);
+  int* half_smem = reinterpret_cast<int*>(bar_mem + 1024 + 8192);   // 2^(shift-1) - 1 per channel (0 for shift 0)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -129,7 +218,9 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     const int i = threadIdx.x - 64;
     for (int c = i; c < 256; c += 128) {
       const int col = blockIdx.y * p.cout_tile + c;
-      shift_smem[c] = (c < p.cout_tile && col < p.cout) ? p.shift_vec[col] : 0;
+      const int sh = (c < p.cout_tile && col < p.cout) ? p.shift_vec[col] : 0;
+      shift_smem[c] = static_cast<uint8_t>(sh);
+      half_smem[c] = sh > 0 ? static_cast<int>((1u << (sh - 1)) - 1u) : 0;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
   }
@@ -213,29 +304,43 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           // the absolute shared-memory address and the tensor core applies it to the addresses it
           // computes, so a start that is not on an 8-row pattern boundary needs nothing else (the
           // descriptor's base-offset field stays 0; setting it to the start's phase gives wrong data).
-          // One thread issues everything: the descriptors advance by additions only.  What remains is the
-          // tensor core's own pace for such small MMAs: about 220 cycles per 128 x cout_tile x 32
-          // instruction whatever cout_tile is, also when consecutive taps go to different accumulators
-          // (measured with 1 to 4 accumulators: no difference) and also with M = 64 instead of 128
-          // (measured: same issue time, slower epilogue because only 16 lanes per warp hold rows), so
-          // kh * kw * cin / 32 instructions cost a CTA about 3-4 k cycles however the image is tiled.
+          // One thread issues everything; see conv_issue_tile for what that costs and why the common filters
+          // are unrolled.  (Also measured: consecutive taps into different accumulators, and M = 64 instead of
+          // 128: no faster.)
           const uint64_t a0 = make_kmajor_desc(sa, p.sbo_bytes, p.swizzle_code);
           uint64_t bd = make_kmajor_desc(sb, p.b_sbo_bytes, p.b_swizzle_code);
           const uint32_t px_step = static_cast<uint32_t>(p.chunk) >> 4;
           const uint32_t row_step = px_step * p.row_w, w_step = p.w_block_bytes >> 4;
           const int ksteps = p.chunk / kUmmaKBytes;
           uint32_t accum = kb != 0 ? 1u : 0u;
-          for (int fh = 0; fh < p.kh; ++fh) {
-            if (p.w_split) {
-              ok = mbar_wait(smem_u32(&w_row_bar[fh]), 0, abort_flag, p.status, ST_TIMEOUT_FULL);
-              if (!ok) break;
-              tc_fence_after();
-            }
-            uint64_t ad = a0 + fh * row_step;
-            if (p.wide_n) {
-              // all kw taps of this filter row at once: B = their kw column blocks (K-major weights: kw * cout_tile
-              // consecutive rows; N-major weights: blocks b_lbo_bytes apart, which the descriptor's
-              // leading-dimension field states)
+          if (!p.wide_n) {
+            const uint32_t a_lo = static_cast<uint32_t>(a0), a_hi = static_cast<uint32_t>(a0 >> 32);
+            const uint32_t b_lo = static_cast<uint32_t>(bd), b_hi = static_cast<uint32_t>(bd >> 32);
+            const uint32_t bk = static_cast<uint32_t>(p.b_kstep);
+            uint64_t* rows = p.w_split ? w_row_bar : nullptr;
+            if (p.kh == 3 && p.kw == 3 && ksteps == 2)
+              ok = conv_issue_tile<3, 3, 2>(tmem_base, a_lo, a_hi, b_lo, b_hi, idesc, accum, 3, 3, 2, row_step, px_step,
+                                            w_step, bk, rows, abort_flag, p.status);
+            else if (p.kh == 3 && p.kw == 3 && ksteps == 1)
+              ok = conv_issue_tile<3, 3, 1>(tmem_base, a_lo, a_hi, b_lo, b_hi, idesc, accum, 3, 3, 1, row_step, px_step,
+                                            w_step, bk, rows, abort_flag, p.status);
+            else if (p.kh == 3 && p.kw == 3 && ksteps == 4)
+              ok = conv_issue_tile<3, 3, 4>(tmem_base, a_lo, a_hi, b_lo, b_hi, idesc, accum, 3, 3, 4, row_step, px_step,
+                                            w_step, bk, rows, abort_flag, p.status);
+            else
+              ok = conv_issue_tile<0, 0, 0>(tmem_base, a_lo, a_hi, b_lo, b_hi, idesc, accum, p.kh, p.kw, ksteps, row_step,
+                                            px_step, w_step, bk, rows, abort_flag, p.status);
+          } else {
+            // all kw taps of a filter row at once: B = their kw column blocks (K-major weights: kw * cout_tile
+            // consecutive rows; N-major weights: blocks b_lbo_bytes apart, which the descriptor's
+            // leading-dimension field states)
+            for (int fh = 0; fh < p.kh; ++fh) {
+              if (p.w_split) {
+                ok = mbar_wait(smem_u32(&w_row_bar[fh]), 0, abort_flag, p.status, ST_TIMEOUT_FULL);
+                if (!ok) break;
+                tc_fence_after();
+              }
+              const uint64_t ad = a0 + fh * row_step;
               uint64_t bw = bd;
               if (p.w_n_major) bw = (bw & ~(0x3FFFull << 16)) | (static_cast<uint64_t>(p.b_lbo_bytes >> 4) << 16);
 #pragma unroll 4
@@ -244,16 +349,6 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 accum = 1u;
               }
               bd += w_step * p.kw;
-              continue;
-            }
-            for (int fw = 0; fw < p.kw; ++fw) {
-#pragma unroll 4
-              for (int k = 0; k < ksteps; ++k) {
-                umma_ss<KIND_I8, 1>(tmem_base, ad + 2 * k, bd + k * p.b_kstep, idesc, accum);
-                accum = 1u;
-              }
-              ad += px_step;
-              bd += w_step;
             }
           }
         } else {
@@ -283,12 +378,30 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
       int8_t* yrow = p.y + ((static_cast<long long>(img) * p.h + oh) * p.w + ow) * p.cout;
       const bool vec = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && (p.cout % 16 == 0);
-      for (int c = 0; c < p.cout_tile; c += 32) {
-        __syncwarp();
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c, r);
-        tmem_ld_wait();
-        if (p.wide_n) {
+      const SrsPlan plan = srs_plan(shift_smem, p.cout_tile, p.srs_wide != 0);
+      if (!p.wide_n) {
+        // 64 columns per round, both loads in flight at once
+        for (int c = 0; c < p.cout_tile; c += 64) {
+          __syncwarp();
+          uint32_t v[2][32];
+          const bool second = c + 32 < p.cout_tile;
+          tmem_ld_32x32b_x32(taddr + c, v[0]);
+          if (second) tmem_ld_32x32b_x32(taddr + c + 32, v[1]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int cc = c + hh * 32, col0 = co0 + cc;
+            if ((hh == 1 && !second) || !pix_ok || col0 >= p.cout) continue;
+            conv_store_chunk(v[hh], plan, shift_smem + cc, half_smem + cc, yrow + col0,
+                             min(32, min(p.cout_tile - cc, p.cout - col0)), vec);
+          }
+        }
+      } else {
+        for (int c = 0; c < p.cout_tile; c += 32) {
+          __syncwarp();
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
           // out[m] = sum_fw D_fw[m + fw]: column block fw of the row fw lanes further on
           for (int fw = 1; fw < p.kw; ++fw) {
             uint32_t t[32];
@@ -310,27 +423,10 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");   // before the next round overwrites the exchange rows
           }
-        }
-        const int col0 = co0 + c;
-        if (!pix_ok || col0 >= p.cout) continue;
-        const int ncols = min(32, min(p.cout_tile - c, p.cout - col0));
-        uint32_t packed[8];
-        int q[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int sh = static_cast<int>(shift_smem[c + j]);
-          q[j] = srs_round<true>(static_cast<int>(r[j]), sh, max(static_cast<int>((1u << sh) >> 1) - 1, 0), min(sh, 1));
-        }
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) packed[j >> 2] = pack_sat_s8x4(q[j], q[j + 1], q[j + 2], q[j + 3]);
-        if (vec && ncols == 32) {
-          *reinterpret_cast<uint4*>(yrow + col0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          *reinterpret_cast<uint4*>(yrow + col0 + 16) =
-              make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < ncols) yrow[col0 + j] = static_cast<int8_t>((packed[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+          const int col0 = co0 + c;
+          if (!pix_ok || col0 >= p.cout) continue;
+          conv_store_chunk(r, plan, shift_smem + c, half_smem + c, yrow + col0,
+                           min(32, min(p.cout_tile - c, p.cout - col0)), vec);
         }
       }
     }
@@ -346,12 +442,43 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   if (tracing && threadIdx.x == 0) p.trace[6] = clock64();
 }
 
+// The MMAs of one group of up to four tiles (persistent form), tile j into accumulator d[j]: for every tap and
+// K step one MMA per tile.  KH, KW, KS > 0 fix the filter and the K steps per tap at compile time: the loops
+// unroll, the operand offsets become a few multiples of row_step, and the one issuing thread (which spends
+// ~10 cycles per dependent instruction) is left with an add and the MMA per product.
+template <int KH, int KW, int KS>
+__device__ __forceinline__ void conv_issue_group(const uint32_t (&d)[4], const uint32_t (&a_lo)[4], uint32_t a_hi,
+                                                 uint32_t b_lo, uint32_t b_hi, int nt, uint32_t idesc, int kh, int kw,
+                                                 int ksteps, uint32_t row_step, uint32_t px_step, uint32_t w_step,
+                                                 uint32_t b_kstep) {
+  const int nh = KH > 0 ? KH : kh, nw = KW > 0 ? KW : kw, nk = KS > 0 ? KS : ksteps;
+  uint32_t accum = 0u;
+#pragma unroll
+  for (int fh = 0; fh < nh; ++fh) {
+#pragma unroll
+    for (int fw = 0; fw < nw; ++fw) {
+#pragma unroll
+      for (int k = 0; k < nk; ++k) {
+        // tap (fh, fw) reads the patch (fh * row_w + fw) rows further on; K step k the next 32 bytes of every row
+        const uint32_t ao = fh * row_step + fw * px_step + 2 * k;
+        const uint32_t bo = (fh * nw + fw) * w_step + k * b_kstep;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j < nt) umma_ss_i8_halves(d[j], a_lo[j] + ao, a_hi, b_lo + bo, b_hi, idesc, accum);
+        accum = 1u;
+      }
+    }
+  }
+}
+
 // The persistent form of the kernel above (ConvParams::persistent): same tiles, same operand views, same
 // arithmetic; what changes is that a CTA outlives its tile.
 //   warp 0   : the channel tile's weights once, then one input patch per tile into the ring
 //   warp 1   : per tile kh * kw * chunk / 32 MMAs (every tap a view into the patch) into accumulator (tile & 1)
-//   warps 2-5: per tile the output stage (per-channel srs) of the accumulator the MMAs have left (a second group
-//              of four warps taking every other 32-column chunk was measured: no faster)
+//   warps 2-9: two groups of four; group e takes this CTA's tiles e, e + 2, ...: the output stage (per-channel
+//              srs) of the accumulator the MMAs have left.
+// The loops carry their tile coordinates, ring positions and phases along instead of dividing: a division by a
+// run-time number costs a single thread several hundred cycles, and the issuing thread has ~80 per MMA to spare.
 __global__ void __launch_bounds__(kConvPersistentThreads, 1)
 conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                             const ConvParams p) {
@@ -369,6 +496,7 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(w_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   uint8_t* shift_smem = reinterpret_cast<uint8_t*>(tmem_base_slot + 2);  // this CTA's cout_tile shift bytes (<= 256)
+  int* half_smem = reinterpret_cast<int*>(bar_mem + 1024);               // 2^(shift-1) - 1 per channel (0 for shift 0)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -398,13 +526,26 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   const int co0 = blockIdx.y * p.cout_tile;
   const int taps = p.kh * p.kw;
   if (warp >= 2) {
-    const int i = threadIdx.x - 64;
-    for (int c = i; c < 256; c += 128) {
-      const int col = co0 + c;
-      shift_smem[c] = (c < p.cout_tile && col < p.cout) ? p.shift_vec[col] : 0;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+    const int c = threadIdx.x - 64;   // 256 epilogue threads, one channel of the tile each
+    const int col = co0 + c;
+    const int sh = (c < p.cout_tile && col < p.cout) ? p.shift_vec[col] : 0;
+    shift_smem[c] = static_cast<uint8_t>(sh);
+    half_smem[c] = sh > 0 ? static_cast<int>((1u << (sh - 1)) - 1u) : 0;
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // the epilogue warps only
   }
+  // a step of `step` tiles through (image, tile row, tile column), as carries instead of divisions
+  struct TileWalk {
+    int tw, th, img, dw, dh, dn;
+    __device__ void init(int t, int step, int tiles_w, int tiles_h) {
+      tw = t % tiles_w; t /= tiles_w; th = t % tiles_h; img = t / tiles_h;
+      dw = step % tiles_w; step /= tiles_w; dh = step % tiles_h; dn = step / tiles_h;
+    }
+    __device__ void next(int tiles_w, int tiles_h) {
+      tw += dw; th += dh; img += dn;
+      if (tw >= tiles_w) { tw -= tiles_w; ++th; }
+      if (th >= tiles_h) { th -= tiles_h; ++img; }
+    }
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -415,16 +556,16 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += gridDim.x) {
-        int r = t;
-        const int tw = r % p.tiles_w; r /= p.tiles_w;
-        const int th = r % p.tiles_h; r /= p.tiles_h;
+      TileWalk at;
+      at.init(blockIdx.x, gridDim.x, p.tiles_w, p.tiles_h);
+      for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += gridDim.x, at.next(p.tiles_w, p.tiles_h)) {
         ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
         if (!ok) break;
         const uint32_t fb = smem_u32(&full_bar[stage]);
         mbar_expect_tx(fb, p.tx_bytes);
         // the whole patch; what lies outside the image reads as zero: that is the padding
-        tma_load_4d(smem_u32(patches + stage * p.a_bytes), &tmap_x, fb, 0, tw * p.wt - p.pad, th * p.rows_per_tile - p.pad, r);
+        tma_load_4d(smem_u32(patches + stage * p.a_bytes), &tmap_x, fb, 0, at.tw * p.wt - p.pad,
+                    at.th * p.rows_per_tile - p.pad, at.img);
         if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
       if (!ok)
@@ -435,120 +576,125 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       const uint32_t idesc = make_idesc<KIND_I8>(kBlockM, p.cout_tile) | (p.w_n_major ? (1u << 16) : 0u);
       bool ok = mbar_wait(smem_u32(w_bar), 0, abort_flag, p.status, ST_TIMEOUT_FULL);
       const uint64_t b0 = make_kmajor_desc(smem_u32(w_smem), p.b_sbo_bytes, p.b_swizzle_code);
+      const uint64_t a_first = make_kmajor_desc(smem_u32(patches), p.sbo_bytes, p.swizzle_code);
+      const uint32_t b_lo = static_cast<uint32_t>(b0), b_hi = static_cast<uint32_t>(b0 >> 32);
+      const uint32_t a_hi = static_cast<uint32_t>(a_first >> 32), a_lo0 = static_cast<uint32_t>(a_first);
+      // every operand lies below 256 KB, so an offset never carries out of the descriptor's 14-bit address field
       const uint32_t px_step = static_cast<uint32_t>(p.chunk) >> 4;
-      const uint32_t row_step = px_step * p.row_w, w_step = p.w_block_bytes >> 4;
+      const uint32_t row_step = px_step * p.row_w, w_step = p.w_block_bytes >> 4, a_step = p.a_bytes >> 4;
+      const uint32_t b_kstep = static_cast<uint32_t>(p.b_kstep);
       const int ksteps = p.chunk / kUmmaKBytes;
       // The MMAs of a GROUP of up to four consecutive tiles are issued interleaved, each tile into its own
-      // accumulator: back-to-back MMAs into ONE accumulator of this width run at the pipe's latency (measured:
-      // one per ~270 cycles), interleaved over two accumulators one per ~150.  One commit per group: a commit
-      // costs about as much as two such MMAs.
+      // accumulator, with one commit and one round of barrier polls per group: what bounds this warp is the
+      // latency of its own instructions (a poll that succeeds at once still costs ~250 cycles, a commit ~450),
+      // so everything that can be shared by four tiles is.
       const int G = p.mma_group, accs = 2 * G;   // accumulators in TMEM: the tile with sequence number s uses s % accs
       int seq = 0, group = 0;                    // tiles and groups this CTA has started
-      for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += G * static_cast<int>(gridDim.x), ++group) {
-        int nt = (p.spatial_tiles - t + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);   // tiles left
-        if (nt > G) nt = G;
-        uint32_t d[4];
-        uint64_t a0[4];
+      int tiles_left = (p.spatial_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                       static_cast<int>(gridDim.x);
+      int st = 0;                                // ring position of tile seq, and the parity of its round
+      uint32_t st_phase = 0;
+      for (; ok && tiles_left > 0; ++group) {
+        const int nt = tiles_left < G ? tiles_left : G;
+        uint32_t d[4], a_lo[4], bar_acc[4], bar_patch[4], par_acc[4], par_patch[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          d[j] = 0; a0[j] = 0;
-          if (j < nt && ok) {
-            const int s_ = seq + j, acc = s_ % accs, st = s_ % p.stages;   // accumulator free, patch landed
-            ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), ((s_ / accs) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-            if (ok) ok = mbar_wait(smem_u32(&full_bar[st]), (s_ / p.stages) & 1, abort_flag, p.status, ST_TIMEOUT_FULL);
-            d[j] = tmem_base + acc * p.acc_stride;
-            a0[j] = make_kmajor_desc(smem_u32(patches + st * p.a_bytes), p.sbo_bytes, p.swizzle_code);
+          const int s_ = seq + j, acc = s_ & (accs - 1);   // G is 1, 2 or 4
+          d[j] = tmem_base + acc * p.acc_stride;
+          a_lo[j] = a_lo0 + st * a_step;
+          bar_acc[j] = smem_u32(&tmem_empty_bar[acc]);
+          par_acc[j] = (s_ & accs) ? 0u : 1u;
+          bar_patch[j] = smem_u32(&full_bar[st]);
+          par_patch[j] = st_phase;
+          if (j < nt && ++st == p.stages) { st = 0; st_phase ^= 1; }
+        }
+        // accumulators free, patches landed: all polls first (their latencies overlap), the bounded waits for
+        // whatever was not ready yet
+        bool ready = true;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j < nt) {
+            const bool r0 = mbar_try_wait(bar_acc[j], par_acc[j]);
+            const bool r1 = mbar_try_wait(bar_patch[j], par_patch[j]);
+            ready = ready && r0 && r1;
           }
+        if (!ready) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (j < nt && ok) {
+              ok = mbar_wait(bar_acc[j], par_acc[j], abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+              if (ok) ok = mbar_wait(bar_patch[j], par_patch[j], abort_flag, p.status, ST_TIMEOUT_FULL);
+            }
         }
         if (!ok) break;
         tc_fence_after();
         if (tracing && seq < 60) p.trace[seq * 4 + 0] = clock64();
-        uint64_t bd = b0;
-        uint32_t accum = 0u;
-        for (int fh = 0; fh < p.kh; ++fh) {
-          uint32_t a_off = fh * row_step;   // tap (fh, fw) reads the patch (fh * row_w + fw) rows further on
-          for (int fw = 0; fw < p.kw; ++fw) {
-#pragma unroll 2
-            for (int k = 0; k < ksteps; ++k) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                if (j < nt) umma_ss<KIND_I8, 1>(d[j], a0[j] + a_off + 2 * k, bd + k * p.b_kstep, idesc, accum);
-              accum = 1u;
-            }
-            a_off += px_step;
-            bd += w_step;
-          }
-        }
+        if (p.kh == 3 && p.kw == 3 && ksteps == 2)
+          conv_issue_group<3, 3, 2>(d, a_lo, a_hi, b_lo, b_hi, nt, idesc, 3, 3, 2, row_step, px_step, w_step, b_kstep);
+        else if (p.kh == 3 && p.kw == 3 && ksteps == 1)
+          conv_issue_group<3, 3, 1>(d, a_lo, a_hi, b_lo, b_hi, nt, idesc, 3, 3, 1, row_step, px_step, w_step, b_kstep);
+        else if (p.kh == 3 && p.kw == 3 && ksteps == 4)
+          conv_issue_group<3, 3, 4>(d, a_lo, a_hi, b_lo, b_hi, nt, idesc, 3, 3, 4, row_step, px_step, w_step, b_kstep);
+        else
+          conv_issue_group<0, 0, 0>(d, a_lo, a_hi, b_lo, b_hi, nt, idesc, p.kh, p.kw, ksteps, row_step, px_step, w_step,
+                                    b_kstep);
         umma_commit(smem_u32(&group_full_bar[group & 1]));   // every tile of the group: accumulator ready, patch read
         if (tracing && seq < 60) p.trace[seq * 4 + 1] = clock64();
         seq += nt;
+        tiles_left -= nt;
       }
     }
   } else {
-    const int quad = warp & 3;
+    const int quad = warp & 3;              // the TMEM lanes this warp may read
+    const int egroup = (warp - 2) >> 2;     // which of the two epilogue groups
     const int m = quad * 32 + lane;
     const int mr = m / p.row_w, mc = m - mr * p.row_w;   // image row and column inside the tile
     const bool vec = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && (p.cout % 16 == 0);
-    // 32-bit rounding needs |acc| + 2^shift < 2^31: the host knows the bound on |acc| (p.srs_wide), the shifts are here
-    int max_shift = 0;
-    for (int c = 0; c < p.cout_tile; ++c) max_shift = max(max_shift, static_cast<int>(shift_smem[c]));
-    const bool wide = p.srs_wide || max_shift > 29;
+    const SrsPlan plan = srs_plan(shift_smem, p.cout_tile, p.srs_wide != 0);
+    const int G = p.mma_group, accs = 2 * G, g_log2 = G == 4 ? 2 : (G == 2 ? 1 : 0);
+    const int step = 2 * static_cast<int>(gridDim.x);
+    TileWalk at;
+    at.init(static_cast<int>(blockIdx.x) + egroup * static_cast<int>(gridDim.x), step, p.tiles_w, p.tiles_h);
+    int stage = egroup % p.stages;          // ring position of tile `it`
     bool ok = true;
-    int it = 0;
-    for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += gridDim.x, ++it) {
-      int r = t;
-      const int tw = r % p.tiles_w; r /= p.tiles_w;
-      const int th = r % p.tiles_h; r /= p.tiles_h;
-      const int G = p.mma_group, accs = 2 * G, acc = it % accs, group = it / G;
+    for (int it = egroup, t = static_cast<int>(blockIdx.x) + egroup * static_cast<int>(gridDim.x); t < p.spatial_tiles;
+         it += 2, t += step, at.next(p.tiles_w, p.tiles_h)) {
+      const int acc = it & (accs - 1), group = it >> g_log2;
       ok = mbar_wait(smem_u32(&group_full_bar[group & 1]), (group >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
-      if (lane == 0) mbar_arrive(smem_u32(&empty_bar[it % p.stages]));   // the tile's MMAs have read its patch
+      if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));   // the tile's MMAs have read its patch
+      stage += 2;
+      if (stage >= p.stages) stage -= p.stages;
       if (tracing && warp == 2 && lane == 0 && it < 60) p.trace[it * 4 + 2] = clock64();
-      const int oh = th * p.rows_per_tile + mr, ow = tw * p.wt + mc;
+      const int oh = at.th * p.rows_per_tile + mr, ow = at.tw * p.wt + mc;
       const bool pix_ok = mr < p.rows_per_tile && mc < p.wt && oh < p.h && ow < p.w;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * p.acc_stride;
-      int8_t* yrow = p.y + ((static_cast<long long>(r) * p.h + oh) * p.w + ow) * p.cout;
-      for (int c = 0; c < p.cout_tile; c += 32) {
+      int8_t* yrow = p.y + ((static_cast<long long>(at.img) * p.h + oh) * p.w + ow) * p.cout;
+      // 64 columns per round: both loads in flight at once; after the last round's loads the accumulator goes
+      // back to the MMA issuer before the arithmetic starts
+      for (int c = 0; c < p.cout_tile; c += 64) {
         __syncwarp();
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + c, v);
+        uint32_t v[2][32];
+        const bool second = c + 32 < p.cout_tile;
+        tmem_ld_32x32b_x32(taddr + c, v[0]);
+        if (second) tmem_ld_32x32b_x32(taddr + c + 32, v[1]);
         tmem_ld_wait();
-        const int col0 = co0 + c;
-        if (!pix_ok || col0 >= p.cout) continue;
-        const int ncols = min(32, min(p.cout_tile - c, p.cout - col0));
-        uint32_t packed[8];
-        int q[32];
-        if (wide) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int sh = static_cast<int>(shift_smem[c + j]);
-            q[j] = srs_round<true>(static_cast<int>(v[j]), sh, max(static_cast<int>((1u << sh) >> 1) - 1, 0), min(sh, 1));
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int sh = static_cast<int>(shift_smem[c + j]);
-            q[j] = srs_round<false>(static_cast<int>(v[j]), sh, max(static_cast<int>((1u << sh) >> 1) - 1, 0), min(sh, 1));
-          }
+        if (c + 64 >= p.cout_tile) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
         }
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) packed[j >> 2] = pack_sat_s8x4(q[j], q[j + 1], q[j + 2], q[j + 3]);
-        if (vec && ncols == 32) {
-          *reinterpret_cast<uint4*>(yrow + col0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          *reinterpret_cast<uint4*>(yrow + col0 + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < ncols) yrow[col0 + j] = static_cast<int8_t>((packed[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+        for (int hh = 0; hh < 2; ++hh) {
+          const int cc = c + hh * 32, col0 = co0 + cc;
+          if ((hh == 1 && !second) || !pix_ok || col0 >= p.cout) continue;
+          conv_store_chunk(v[hh], plan, shift_smem + cc, half_smem + cc, yrow + col0,
+                           min(32, min(p.cout_tile - cc, p.cout - col0)), vec);
         }
       }
-      // accumulator drained: hand it back to the MMA issuer
-      tc_fence_before();
-      __syncwarp();
       if (tracing && warp == 2 && lane == 0 && it < 60) p.trace[it * 4 + 3] = clock64();
-      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
   }
 
@@ -744,6 +890,8 @@ void configure_conv(const aiehlc_ctx* ctx, ConvParams& p, int* n_tiles_out) {
 void conv_persistent_setup(const aiehlc_ctx* ctx, ConvParams& p, int n_tiles) {
   p.persistent = 0;
   p.spatial_tiles = p.n * p.tiles_h * p.tiles_w;
+  // |acc| <= taps * cin * 2^14: below 2^30 the kernels may round in 32 bits where the shifts allow it too
+  p.srs_wide = static_cast<long long>(p.kh) * p.kw * p.cin > 65535 ? 1 : 0;
   if (!ctx->conv_persistent || !p.halo || p.chunks_per_tap != 1 || p.wide_n) return;
   if (static_cast<long long>(p.spatial_tiles) * n_tiles < 2LL * ctx->sm_count) return;
   const int taps = p.kh * p.kw;
@@ -762,8 +910,6 @@ void conv_persistent_setup(const aiehlc_ctx* ctx, ConvParams& p, int n_tiles) {
   int g = ctx->conv_mma_group > 0 ? ctx->conv_mma_group : 4;
   while (g > 1 && (2 * g * p.acc_stride > 512 || stages < 2 * g)) g /= 2;
   p.mma_group = g;
-  // |acc| <= taps * cin * 2^14: below 2^30 the kernel may round in 32 bits where the shifts allow it too
-  p.srs_wide = static_cast<long long>(taps) * p.cin > 65535 ? 1 : 0;
   uint32_t cols = 32;
   while (cols < 2 * p.mma_group * p.acc_stride) cols <<= 1;
   p.tmem_cols = cols;
@@ -799,7 +945,7 @@ int plan_conv2d(const aiehlc_ctx* ctx, int n, int h, int wd, int cin, int cout, 
   pl.tma_boxes_per_cta = p.halo ? 2 * p.chunks_per_tap : 2 * taps * p.chunks_per_tap;
   pl.mmas_per_cta = taps * p.chunks_per_tap * (p.chunk / kUmmaKBytes);
   pl.stages = p.stages;
-  pl.smem_bytes = p.stages * p.stage_bytes + 1024 + 8192 + 1024;
+  pl.smem_bytes = p.stages * p.stage_bytes + 1024 + 8192 + 1024 + 1024;
   pl.m_rows_used = p.rows_per_tile * p.row_w;
   pl.launches = (ctx->conv_hwio_direct && p.halo && (p.cout_tile == 32 || p.cout_tile == 64 || p.cout_tile == 128) &&
                  cout % p.cout_tile == 0) ? 1 : 2;
@@ -918,8 +1064,8 @@ int launch_conv_tensor(aiehlc_ctx* ctx, const int8_t* x, const int8_t* packed, b
     if (r != CUDA_SUCCESS) return fail(AIEHLC_ERR_CUDA, "cuTensorMapEncodeTiled failed for conv weights");
   }
 
-  const int smem_bytes = p.persistent ? static_cast<int>(p.w_region_bytes) + p.stages * p.a_bytes + 1024 + 1024
-                                      : p.stages * p.stage_bytes + 1024 + 8192 + 1024;
+  const int smem_bytes = p.persistent ? static_cast<int>(p.w_region_bytes) + p.stages * p.a_bytes + 2048 + 1024
+                                      : p.stages * p.stage_bytes + 1024 + 8192 + 1024 + 1024;
   auto kern = p.persistent ? conv2d_i8_persistent_kernel : conv2d_i8_kernel;
   KernelSetup& ks = ctx->kernel_setup[reinterpret_cast<const void*>(kern)];
   if (int rc = ensure_dynamic_smem(ctx->device, reinterpret_cast<const void*>(kern), smem_bytes, &ks.smem_attr))

@@ -342,6 +342,17 @@ __device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr, uint32_
   return d;
 }
 
+// kind::i8, one CTA, descriptors given as their 32-bit halves: a loop that walks an operand changes only the
+// low half (the address field), so the issuing thread adds 32-bit numbers instead of 64-bit ones.
+__device__ __forceinline__ void umma_ss_i8_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                  uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // Instruction descriptor (dense, K-major A and B):
 //   bits [4,6) D format: 1 = f32, 2 = s32     bits [7,10) A format   bits [10,13) B format
 //   (kind::i8: 1 = signed int8; kind::f16: 1 = bf16)

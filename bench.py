@@ -38,7 +38,7 @@ sys.path.insert(0, str(ROOT))
 L2_BYTES = 126 * 1024 * 1024
 NVLINK_GBS = 770.0   # measured peer-copy bandwidth between two B200 per direction (nominal 900)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised in profiles/
-NCU_TRAFFIC_BYTES = {"cfg2": 33.7e6, "cfg3": 1.23e9, "cfg4": None, "shallow_k": None}
+NCU_TRAFFIC_BYTES = {"cfg2": 33.9e6, "cfg3": 1.229e9, "cfg4": 0.31e6, "shallow_k": 220.7e6, "scatter_local": 1.151e9}
 
 WORKLOADS = {
     "cfg2": dict(M=4096, N=4096, K=4096, kind="i8_srs", shift=8, splitk=4, scaling="weak",
@@ -404,6 +404,7 @@ def make_conv(env: Env, wl: dict, n: int | None = None) -> Work:
     wk.ys = [torch.empty((n, h, w, cout), dtype=torch.int8, device=dev) for _ in range(nsets)]
     calls = [ctx.bound_conv2d_i8_srs(wk.xs[j], wk.ws[j], wk.sv, wk.ys[j], pad=1) for j in range(nsets)]
     wk.nsets = nsets
+    wk.batch = n
     wk.step = lambda i: calls[i % nsets]()
     wk.ops_per_step = 2.0 * n * h * w * cout * 9 * cin
     wk.alg_bytes = set_bytes
@@ -563,6 +564,8 @@ def roofline_of(env: Env, name: str, wl: dict, wk: Work, res: dict) -> dict:
     achieved = wk.ops_per_step / (per_launch_ms * 1e-3) / 1e12
     traffic = NCU_TRAFFIC_BYTES.get(name)
     if wk.kind == "conv":
+        if wk.batch != wl["n"]:
+            traffic = NCU_TRAFFIC_BYTES.get(f"{name}_n{wk.batch}")
         gbs = wk.alg_bytes / (per_launch_ms * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": gbs / peaks["hbm_gbs"], "traffic": traffic,
@@ -905,6 +908,8 @@ def main() -> int:
                 print(json.dumps(line), flush=True)
             dist.destroy_process_group()
             return 0
+    if kind == "conv" and args.batch:
+        wl = dict(wl, desc=wl["desc"].replace(f"NHWC {wl['n']}x", f"NHWC {args.batch}x"))
     wk = make_conv(env, wl, args.batch or None) if kind == "conv" else make_gemm(env, name, wl, args.sets)
     mode = default_mode(wk, args.graph)
     res = timed(env, wk, args.steps, args.warmup, mode)

@@ -114,6 +114,28 @@ def test_conv2d_persistent_form_matches_one_tile_form(ctx, shape, kh, pad):
     assert ctx.sync() == 0
 
 
+@pytest.mark.parametrize("shift", [0, 1, 6, 29, 30])
+def test_conv2d_persistent_form_with_one_shift_for_every_channel(ctx, shift):
+    """One shift for the whole channel tile keeps the rounding constants in registers (up to shift 29; above that
+    the 64-bit form): same bits as the oracle and as the one-tile form."""
+    n, h, w, cin, cout = 12, 56, 56, 64, 64
+    x = synth.int8_uniform(77, (n, h, w, cin))
+    wt = synth.int8_uniform(1077, (3, 3, cin, cout))
+    sv = np.full(cout, shift, dtype=np.uint8)
+    dx, dw, dsv = _dev(x), _dev(wt), _dev(sv)
+    try:
+        ctx.set_conv_persistent(False)
+        want = ctx.conv2d_i8_srs(dx, dw, dsv, pad=1)
+        ctx.set_conv_persistent(True)
+        for _ in range(2):
+            assert torch.equal(ctx.conv2d_i8_srs(dx, dw, dsv, pad=1), want)
+    finally:
+        ctx.set_conv_persistent(True)
+    for img in (0, n - 1):
+        assert np.array_equal(want[img].cpu().numpy(), O.conv2d_i8_srs(x[img:img + 1], wt, sv, pad=1)[0])
+    assert ctx.sync() == 0
+
+
 def test_conv2d_benchmark_shape_is_one_launch(ctx):
     x = _dev(synth.int8_uniform(4, (1, 56, 56, 64)))
     wt = _dev(synth.int8_uniform(1004, (3, 3, 64, 64)))
