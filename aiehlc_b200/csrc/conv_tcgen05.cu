@@ -72,11 +72,21 @@ struct ConvParams {
   uint32_t acc_stride;             // TMEM columns between accumulators
   int mma_group;                   // tiles whose MMAs are issued interleaved (1, 2 or 4): 2 * mma_group accumulators in TMEM
   int srs_wide;                    // |acc| + 2^shift may reach 2^31: round in 64-bit arithmetic
+  // tile index -> (image, tile row, tile column) without dividing: floor(2^32 / d) + 1 for d = tiles_w and
+  // tiles_h, exact while index * d < 2^32; 0 where that cannot be promised (the kernels divide then)
+  uint32_t magic_w, magic_h;
   int8_t* y;
   const uint8_t* shift_vec;
   int* status;
   long long* trace;   // kMeasure: clock64 stamps of CTA 0, or null
 };
+
+// n / d for 0 <= n, d >= 1 with the host's multiplier (ConvParams::magic_w): a division by a run-time number costs
+// the thread that does it several hundred cycles, and in a 4 us kernel the first tile load waits for it.
+__device__ __forceinline__ int fast_div(int n, int d, uint32_t magic) {
+  if (d == 1) return n;
+  return magic != 0u ? static_cast<int>(__umulhi(static_cast<uint32_t>(n), magic)) : n / d;
+}
 
 // How an epilogue warp rounds: decided once per CTA from the channel tile's shifts.
 struct SrsPlan {
@@ -214,6 +224,7 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     p.trace[1] = clock64();
   }
   // the epilogue warps fetch the per-channel shifts once; they are needed only after the main loop
+  SrsPlan plan{};
   if (warp >= 2) {
     const int i = threadIdx.x - 64;
     for (int c = i; c < 256; c += 128) {
@@ -223,13 +234,14 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       half_smem[c] = sh > 0 ? static_cast<int>((1u << (sh - 1)) - 1u) : 0;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+    plan = srs_plan(shift_smem, p.cout_tile, p.srs_wide != 0);   // while the loads and the MMAs run
   }
 
   // tile -> (image, first output row, first output column, first output channel)
-  int t = blockIdx.x;
-  const int tw = t % p.tiles_w; t /= p.tiles_w;
-  const int th = t % p.tiles_h; t /= p.tiles_h;
-  const int img = t;
+  const int t_row = fast_div(blockIdx.x, p.tiles_w, p.magic_w);
+  const int tw = static_cast<int>(blockIdx.x) - t_row * p.tiles_w;
+  const int img = fast_div(t_row, p.tiles_h, p.magic_h);
+  const int th = t_row - img * p.tiles_h;
   const int oh0 = th * p.rows_per_tile;
   const int ow0 = tw * p.wt;
   const int co0 = blockIdx.y * p.cout_tile;
@@ -378,7 +390,6 @@ conv2d_i8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
       int8_t* yrow = p.y + ((static_cast<long long>(img) * p.h + oh) * p.w + ow) * p.cout;
       const bool vec = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && (p.cout % 16 == 0);
-      const SrsPlan plan = srs_plan(shift_smem, p.cout_tile, p.srs_wide != 0);
       if (!p.wide_n) {
         // 64 columns per round, both loads in flight at once
         for (int c = 0; c < p.cout_tile; c += 64) {
@@ -536,9 +547,11 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   // a step of `step` tiles through (image, tile row, tile column), as carries instead of divisions
   struct TileWalk {
     int tw, th, img, dw, dh, dn;
-    __device__ void init(int t, int step, int tiles_w, int tiles_h) {
-      tw = t % tiles_w; t /= tiles_w; th = t % tiles_h; img = t / tiles_h;
-      dw = step % tiles_w; step /= tiles_w; dh = step % tiles_h; dn = step / tiles_h;
+    __device__ void init(int t, int step, const ConvParams& p) {
+      int r = fast_div(t, p.tiles_w, p.magic_w);
+      tw = t - r * p.tiles_w; img = fast_div(r, p.tiles_h, p.magic_h); th = r - img * p.tiles_h;
+      r = fast_div(step, p.tiles_w, p.magic_w);
+      dw = step - r * p.tiles_w; dn = fast_div(r, p.tiles_h, p.magic_h); dh = r - dn * p.tiles_h;
     }
     __device__ void next(int tiles_w, int tiles_h) {
       tw += dw; th += dh; img += dn;
@@ -557,7 +570,7 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       uint32_t phase = 0;
       bool ok = true;
       TileWalk at;
-      at.init(blockIdx.x, gridDim.x, p.tiles_w, p.tiles_h);
+      at.init(blockIdx.x, gridDim.x, p);
       for (int t = blockIdx.x; ok && t < p.spatial_tiles; t += gridDim.x, at.next(p.tiles_w, p.tiles_h)) {
         ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY);
         if (!ok) break;
@@ -654,7 +667,7 @@ conv2d_i8_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     const int G = p.mma_group, accs = 2 * G, g_log2 = G == 4 ? 2 : (G == 2 ? 1 : 0);
     const int step = 2 * static_cast<int>(gridDim.x);
     TileWalk at;
-    at.init(static_cast<int>(blockIdx.x) + egroup * static_cast<int>(gridDim.x), step, p.tiles_w, p.tiles_h);
+    at.init(static_cast<int>(blockIdx.x) + egroup * static_cast<int>(gridDim.x), step, p);
     int stage = egroup % p.stages;          // ring position of tile `it`
     bool ok = true;
     for (int it = egroup, t = static_cast<int>(blockIdx.x) + egroup * static_cast<int>(gridDim.x); t < p.spatial_tiles;
@@ -890,6 +903,13 @@ void configure_conv(const aiehlc_ctx* ctx, ConvParams& p, int* n_tiles_out) {
 void conv_persistent_setup(const aiehlc_ctx* ctx, ConvParams& p, int n_tiles) {
   p.persistent = 0;
   p.spatial_tiles = p.n * p.tiles_h * p.tiles_w;
+  // the largest number divided is below 2 * spatial_tiles (a tile index, or the persistent form's step)
+  auto magic = [&](int d) -> uint32_t {
+    if (d <= 1 || 2LL * p.spatial_tiles * d >= (1LL << 32)) return 0u;
+    return static_cast<uint32_t>((1ULL << 32) / static_cast<uint32_t>(d)) + 1u;
+  };
+  p.magic_w = magic(p.tiles_w);
+  p.magic_h = magic(p.tiles_h);
   // |acc| <= taps * cin * 2^14: below 2^30 the kernels may round in 32 bits where the shifts allow it too
   p.srs_wide = static_cast<long long>(p.kh) * p.kw * p.cin > 65535 ? 1 : 0;
   if (!ctx->conv_persistent || !p.halo || p.chunks_per_tap != 1 || p.wide_n) return;
