@@ -4,6 +4,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/aiehlc_b200_tuning.h"
 #include "context.h"
@@ -617,7 +618,16 @@ static int host_gemm_pipelined(aiehlc_ctx* ctx, const void* A, const void* B, vo
   int b_rows = ((N + blocks - 1) / blocks + 255) / 256 * 256;
   if (K == 0 || static_cast<size_t>(a_rows) * K * in_esize < (1u << 20)) a_rows = M;
   if (K == 0 || static_cast<size_t>(b_rows) * K * in_esize < (1u << 20)) b_rows = N;
-  const int na = (M + a_rows - 1) / a_rows, nb = (N + b_rows - 1) / b_rows;
+  // block boundaries.  What follows the LAST upload cannot overlap any copy in the other direction's shadow: the
+  // kernel on the block just uploaded and the download of its rows of C.  That last upload is a block of A (see
+  // the order below), so A's last block gives up all but one row of tiles to a block of its own before it.
+  std::vector<int> a_cut{0}, b_cut{0};
+  for (int r = a_rows; r < M; r += a_rows) a_cut.push_back(r);
+  for (int r = b_rows; r < N; r += b_rows) b_cut.push_back(r);
+  if (a_cut.size() > 1 && M - a_cut.back() >= 512) a_cut.push_back((M - 1) / 256 * 256);
+  a_cut.push_back(M);
+  b_cut.push_back(N);
+  const int na = static_cast<int>(a_cut.size()) - 1, nb = static_cast<int>(b_cut.size()) - 1;
   uint8_t* da = static_cast<uint8_t*>(ctx->buf_a.ptr);
   uint8_t* db = static_cast<uint8_t*>(ctx->buf_b.ptr);
   uint8_t* dc = static_cast<uint8_t*>(ctx->buf_c.ptr);
@@ -649,23 +659,21 @@ static int host_gemm_pipelined(aiehlc_ctx* ctx, const void* A, const void* B, vo
                                   static_cast<size_t>(rows) * K * in_esize, cudaMemcpyHostToDevice, ctx->stream_up));
     return AIEHLC_OK;
   };
-  auto a_end = [&](int i) { return (i + 1) * a_rows < M ? (i + 1) * a_rows : M; };
-  auto b_end = [&](int j) { return (j + 1) * b_rows < N ? (j + 1) * b_rows : N; };
   int ia = 0, ib = 0;  // blocks of A and of B on the device so far
-  if (int rc = upload(da, A, 0, a_end(0))) return rc;
-  if (int rc = upload(db, B, 0, b_end(0))) return rc;
+  if (int rc = upload(da, A, 0, a_cut[1])) return rc;
+  if (int rc = upload(db, B, 0, b_cut[1])) return rc;
   ia = ib = 1;
-  if (int rc = rect(0, a_end(0), 0, b_end(0))) return rc;
+  if (int rc = rect(0, a_cut[1], 0, b_cut[1])) return rc;
   while (ia < na || ib < nb) {
     // the operand that is further behind goes next; on a tie B, so that the last piece of C is whole rows
-    const bool take_b = ib < nb && (ia >= na || ib * na <= ia * nb);
+    const bool take_b = ib < nb && (ia >= na || static_cast<long long>(b_cut[ib]) * M <= static_cast<long long>(a_cut[ia]) * N);
     if (take_b) {
-      if (int rc = upload(db, B, ib * b_rows, b_end(ib) - ib * b_rows)) return rc;
-      if (int rc = rect(0, a_end(ia - 1), ib * b_rows, b_end(ib))) return rc;
+      if (int rc = upload(db, B, b_cut[ib], b_cut[ib + 1] - b_cut[ib])) return rc;
+      if (int rc = rect(0, a_cut[ia], b_cut[ib], b_cut[ib + 1])) return rc;
       ++ib;
     } else {
-      if (int rc = upload(da, A, ia * a_rows, a_end(ia) - ia * a_rows)) return rc;
-      if (int rc = rect(ia * a_rows, a_end(ia), 0, b_end(ib - 1))) return rc;
+      if (int rc = upload(da, A, a_cut[ia], a_cut[ia + 1] - a_cut[ia])) return rc;
+      if (int rc = rect(a_cut[ia], a_cut[ia + 1], 0, b_cut[ib])) return rc;
       ++ia;
     }
   }

@@ -55,7 +55,8 @@ struct ConvParams {
   uint32_t w_row_bytes;            // bytes of one filter row's box: kw taps
   // Patch form, wide N: the kw taps of a filter row become ONE MMA with N = kw * cout_tile (the taps' weight
   // blocks lie side by side in shared memory), so a CTA issues kh * cin / 32 instructions instead of
-  // kh * kw * cin / 32 -- small MMAs cost about 200 cycles each whatever their N.  Tap fw's product of patch
+  // kh * kw * cin / 32 (an option kept from the time each small MMA cost the issuing thread ~200 cycles; with
+  // the unrolled issue loops it is no faster, and its output stage is heavier).  Tap fw's product of patch
   // row m belongs to output row m - fw: the epilogue adds column block fw of row m + fw to block 0 of row m
   // (neighbouring lanes by shuffle, the first rows of the next warp through shared memory).
   int wide_n;
@@ -485,7 +486,8 @@ __device__ __forceinline__ void conv_issue_group(const uint32_t (&d)[4], const u
 // The persistent form of the kernel above (ConvParams::persistent): same tiles, same operand views, same
 // arithmetic; what changes is that a CTA outlives its tile.
 //   warp 0   : the channel tile's weights once, then one input patch per tile into the ring
-//   warp 1   : per tile kh * kw * chunk / 32 MMAs (every tap a view into the patch) into accumulator (tile & 1)
+//   warp 1   : per tile kh * kw * chunk / 32 MMAs (every tap a view into the patch); the MMAs of up to four
+//              consecutive tiles are issued interleaved, each tile into its own accumulator (2 x 4 in TMEM)
 //   warps 2-9: two groups of four; group e takes this CTA's tiles e, e + 2, ...: the output stage (per-channel
 //              srs) of the accumulator the MMAs have left.
 // The loops carry their tile coordinates, ring positions and phases along instead of dividing: a division by a

@@ -39,7 +39,8 @@ int aiehlc_set_tma_store(aiehlc_ctx* ctx, int on);
 /* Tuning knob for the CTA-pair kernel: groups of four epilogue warps per CTA.  2 = the two warps of a
  * TMEM lane quarter each drain half of a tile's columns (one staging buffer per warp; more accumulator
  * reads, proxy fences and tile stores in flight: pays where the output stage sets the pace, K <= 1024 bytes);
- * 1 = four warps with two staging buffers each (better where K is deep); 0 (default) = 2 up to 8 K blocks of 128 bytes for int8 operands and 4 for bf16 (and never for a
+ * 1 = four warps with two staging buffers each (better where K is deep); 0 (default) = 2 up to 8 K blocks of 128
+ * bytes for int8 operands and 4 for bf16 (and never for a
  * row-sharded output, which the wire bounds), else 1. */
 int aiehlc_set_epilogue_groups(aiehlc_ctx* ctx, int groups);
 /* Tuning knob for a CTA-pair launch whose last wave is at most half full:
@@ -67,8 +68,9 @@ int aiehlc_set_conv_halo(aiehlc_ctx* ctx, int on);
  * large images; patch form, cin 32, 64 or 128) a CTA keeps its channel tile's weights in shared memory for its
  * whole life and walks the tiles, input patches arriving through a ring of buffers and the accumulator
  * double-buffered, so loads, MMAs and output stage of consecutive tiles overlap; 0 = always one CTA per tile;
- * 2 / 3 = as 1, with the MMAs of one tile at a time / of two tiles interleaved (1 chooses: two where four
- * accumulators fit in TMEM). */
+ * 2 / 3 / 4 = as 1, with the MMAs of one tile at a time / of two / of four tiles issued interleaved before one
+ * commit (1 chooses four where eight accumulators fit in TMEM and the ring holds eight patches, else two, else
+ * one). */
 int aiehlc_set_conv_persistent(aiehlc_ctx* ctx, int on);
 /* Tuning knob for aiehlc_mm_i32_*: 1 (default) = products of at least 2^24 multiply-adds (K >= 64) run on the
  * int8 tensor cores: the int32 operands are cut into unsigned bytes, four int8 GEMMs (one per power of
@@ -127,13 +129,16 @@ int aiehlc_set_pdl(aiehlc_ctx* ctx, int on);
  * stream the operands (operand-feed ceiling), 4 = int32 results are staged in shared memory but their
  * tile stores are not issued, 5 = the output stage is skipped after the accumulator reads. */
 int aiehlc_set_debug(aiehlc_ctx* ctx, int mode);
-/* Measurement aid (AIEHLC_MEASURE builds only): while `device_buffer` is non-NULL, the first CTA of every GEMM launch writes
+/* Measurement aid (AIEHLC_MEASURE builds only): while `device_buffer` is non-NULL, the first CTA of every GEMM
+ * launch writes
  * clock64() stamps for each of its tiles into it, 8 int64 slots per tile: [0] MMA loop start,
  * [1] MMA loop issued, [2] epilogue starts waiting, [3] accumulator ready, [4] epilogue done;
  * tile 0 also holds [5] kernel entry, [6] kernel exit (clock64) and [7] / word 15 the global
- * nanosecond timer at entry / exit.  The buffer must hold 8 * max(2, tiles per CTA) words.  NULL switches the stamps off. */
+ * nanosecond timer at entry / exit.  The buffer must hold 8 * max(2, tiles per CTA) words.  NULL switches the
+ * stamps off. */
 int aiehlc_set_trace(aiehlc_ctx* ctx, long long* device_buffer);
-/* Measurement aid (AIEHLC_MEASURE builds only): while `device_buffer` is non-NULL, every CTA of a CTA-pair GEMM launch writes the
+/* Measurement aid (AIEHLC_MEASURE builds only): while `device_buffer` is non-NULL, every CTA of a CTA-pair GEMM
+ * launch writes the
  * global nanosecond timer at its entry and exit into words [2 * CTA] and [2 * CTA + 1] (the buffer
  * must hold 2 * 148 words): shows which pairs finish last.  NULL switches it off. */
 int aiehlc_set_cta_times(aiehlc_ctx* ctx, long long* device_buffer);
