@@ -38,7 +38,8 @@ sys.path.insert(0, str(ROOT))
 L2_BYTES = 126 * 1024 * 1024
 NVLINK_GBS = 770.0   # measured peer-copy bandwidth between two B200 per direction (nominal 900)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised in profiles/
-NCU_TRAFFIC_BYTES = {"cfg2": 33.9e6, "cfg3": 1.229e9, "cfg4": 0.31e6, "shallow_k": 220.7e6, "scatter_local": 1.151e9}
+NCU_TRAFFIC_BYTES = {"cfg2": 33.9e6, "cfg3": 1.229e9, "cfg4": 0.33e6, "cfg4_n128": 25.9e6, "shallow_k": 220.7e6,
+                     "scatter_local": 1.151e9}
 
 WORKLOADS = {
     "cfg2": dict(M=4096, N=4096, K=4096, kind="i8_srs", shift=8, splitk=4, scaling="weak",
@@ -986,6 +987,8 @@ def main() -> int:
                         per_ms = br["local_ms"] / br["steps"]
                         batches[f"n{nb}"] = {"value": bwk.ops_per_step / (per_ms * 1e-3) / 1e12, "unit": "TOPS",
                                              "us_per_call": per_ms * 1e3, "GBps": bwk.alg_bytes / (per_ms * 1e-3) / 1e9,
+                                             "frac_of_hbm_peak": bwk.alg_bytes / (per_ms * 1e-3) / 1e9 / env.peaks["hbm_gbs"],
+                                             "traffic": NCU_TRAFFIC_BYTES.get(f"cfg4_n{nb}"),
                                              "launch": br["launch"], "l2": bwk.l2_note}
                         release(bwk)
                     rec["batches"] = batches
