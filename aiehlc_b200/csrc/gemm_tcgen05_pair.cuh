@@ -51,27 +51,26 @@ struct WorkUnit {
 
 // Unit number `u` of the launch (pair p runs units p, p + pairs, p + 2 pairs, ...).
 //
-// Tail balancing along K (p.sk_tiles > 0): with T = full * pairs + rem tiles and rem <= pairs / 2, the last
-// rem tiles are cut at K block p.sk_cut into two halves, and the units are ordered
-//     [upper K halves of the rem tail tiles] [their lower K halves] [the T - rem whole tiles]
-// Round-robin over the pairs, the 2 rem halves run side by side in the first round (the other pairs start
-// on whole tiles), after which every pair has `full` whole tiles left: at most full + 1/2 tile times of
-// work per pair instead of full + 1, the pairs stay within half a tile of one another, and the partial sums
-// of a tile's two halves meet in the output stage of the lower half while its pair is already multiplying
-// its next tile.
-__device__ __forceinline__ bool work_unit(int u, const GemmParams& p, int num_tiles, WorkUnit& w) {
+// Tail balancing along K (p.sk_tiles > 0): with T = full * pairs + rem tiles, full >= 1 and rem <= pairs / 2,
+// the last rem tiles are cut at K block p.sk_cut into two halves, and the units are ordered
+//     [upper K halves of the rem tail tiles] [pairs whole tiles] [their lower K halves] [the other whole tiles]
+// Dealt round-robin over the pairs: pairs 0 .. rem-1 start with an upper half, pairs rem .. 2 rem - 1 take the
+// lower half of the same tile as their SECOND unit, after a whole tile -- by then the upper half's partial sums
+// have long been deposited, so the output stage of the lower half never waits for them (with both halves in the
+// first round it waited 11 k cycles and held its accumulator for 24 k, which stalled the pair's third unit).
+// Every pair has at most full + 1/2 tile times of work instead of full + 1.
+__device__ __forceinline__ bool work_unit(int u, const GemmParams& p, int num_tiles, int num_pairs, WorkUnit& w) {
   if (p.sk_tiles > 0) {
-    const int first = num_tiles - p.sk_tiles;  // the tail tiles are the last sk_tiles tiles
-    if (u < p.sk_tiles) {
+    const int n = p.sk_tiles, first = num_tiles - n;  // the tail tiles are the last n tiles
+    if (u < n) {
       w = WorkUnit{first + u, p.sk_cut, p.num_k_blocks, 0, 1};
       return true;
     }
-    u -= p.sk_tiles;
-    if (u < p.sk_tiles) {
-      w = WorkUnit{first + u, 0, p.sk_cut, 0, 1};
+    if (u >= num_pairs + n && u < num_pairs + 2 * n) {
+      w = WorkUnit{first + (u - num_pairs - n), 0, p.sk_cut, 0, 1};
       return true;
     }
-    u -= p.sk_tiles;
+    u -= u < num_pairs + n ? n : 2 * n;
     if (u >= first) return false;
     w = WorkUnit{u, 0, p.num_k_blocks, 0, 1};
     return true;
@@ -201,7 +200,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       WorkUnit w;
-      for (int u = pair_id; ok && work_unit(u, p, num_tiles, w); u += num_pairs) {
+      for (int u = pair_id; ok && work_unit(u, p, num_tiles, num_pairs, w); u += num_pairs) {
         int mb, nb;
         tile_coords(w.tile, p, mb, nb);
         for (int kb = w.kb0; kb < w.kb1; kb += kKPer) {
@@ -244,7 +243,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int it = 0;
       bool ok = true;
       WorkUnit w;
-      for (int u = pair_id; ok && work_unit(u, p, num_tiles, w); u += num_pairs, ++it) {
+      for (int u = pair_id; ok && work_unit(u, p, num_tiles, num_pairs, w); u += num_pairs, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status,
@@ -291,7 +290,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     int it = 0;
     bool ok = true;
     WorkUnit w;
-    for (int u = pair_id; ok && work_unit(u, p, num_tiles, w); u += num_pairs, ++it) {
+    for (int u = pair_id; ok && work_unit(u, p, num_tiles, num_pairs, w); u += num_pairs, ++it) {
       int mb, nb;
       tile_coords(w.tile, p, mb, nb);
       const int acc = it & 1;

@@ -74,16 +74,17 @@ def test_gemm_planner_needs_no_gpu():
 
 
 def test_k_halves_schedule_gives_every_pair_at_most_half_a_tile_more():
-    """Host logic of the tail balancing along K (the unit order the kernels walk, restated): upper halves, lower
-    halves, whole tiles, dealt round-robin -- every tile's K range is covered exactly once, the halves all run in
-    the first round, and no pair has more than full + 1/2 tile times of work."""
+    """Host logic of the tail balancing along K (the unit order the kernels walk, restated): upper halves, one
+    whole tile per pair, lower halves, the other whole tiles, dealt round-robin -- every tile's K range is covered
+    exactly once, a lower half is the SECOND unit of its pair (its upper half, the first unit of another pair, is
+    done by then), and no pair has more than full + 1/2 tile times of work."""
     # (tiles, pairs, K blocks) of a few launches; the cut is the planner's: an even number of blocks in the lower half
     for (T, P, nkb) in [(256, 74, 32), (100, 74, 32), (99, 74, 17), (256, 74, 16), (320, 74, 32), (20, 16, 16), (42, 12, 64)]:
         rem, cut = T % P, (nkb // 2 + 1) & ~1
         assert 0 < rem <= P // 2
         first = T - rem
-        units = [(first + u, cut, nkb) for u in range(rem)] + [(first + u, 0, cut) for u in range(rem)] + \
-                [(t, 0, nkb) for t in range(first)]
+        units = [(first + u, cut, nkb) for u in range(rem)] + [(t, 0, nkb) for t in range(P)] + \
+                [(first + u, 0, cut) for u in range(rem)] + [(t, 0, nkb) for t in range(P, first)]
         cover = {}
         for t, a, b in units:
             cover.setdefault(t, []).append((a, b))
@@ -92,9 +93,13 @@ def test_k_halves_schedule_gives_every_pair_at_most_half_a_tile_more():
             mine = units[pair::P]
             work = sum(b - a for _, a, b in mine)
             assert work <= (T // P) * nkb + max(cut, nkb - cut)
-            halves = [i for i, (t, a, b) in enumerate(mine) if b - a < nkb]
-            assert halves in ([], [0])                 # a pair has at most one half, and it is its first unit
-        assert all(u < P for u in range(2 * rem))  # both halves of every tail tile run in the first round, side by side
+            halves = [(i, a) for i, (t, a, b) in enumerate(mine) if b - a < nkb]
+            assert halves in ([], [(0, cut)], [(1, 0)])     # an upper half first, or a lower half second
+        # the upper half of a tile is in the first round, its lower half in the second, on another pair
+        where = {(t, a): i for i, (t, a, b) in enumerate(units) if b - a < nkb}
+        for u in range(rem):
+            up, lo = where[(first + u, cut)], where[(first + u, 0)]
+            assert up < P <= lo < 2 * P and up % P != lo % P
 
 
 def test_tile_visiting_order_needs_no_gpu():
