@@ -81,7 +81,9 @@ def test_conv2d_batches_of_the_benchmark_layer(ctx, n):
                                           ((6, 60, 60, 128, 272), 3, 1),     # 17 channel tiles of 16: the CTAs are split between them
                                           ((8, 40, 40, 64, 64), 5, 2),       # 5 x 5 filter
                                           ((4, 30, 300, 64, 32), 3, 1),      # images wider than a tile
-                                          ((80, 17, 23, 128, 16), 3, 1)])    # ragged tiles, few channels
+                                          ((80, 17, 23, 128, 16), 3, 1),     # ragged tiles, few channels
+                                          ((48, 28, 28, 64, 128), 3, 1),     # 128 channels: two tiles per MMA group at most
+                                          ((48, 28, 28, 32, 256), 3, 1)])    # 256 channels: one accumulator pair fills TMEM
 def test_conv2d_persistent_form_matches_one_tile_form(ctx, shape, kh, pad):
     """Many tiles per SM: CTAs keep the weights in shared memory and walk the tiles.  Same bits as the one-CTA-per-tile
     form (itself checked against the oracle shape by shape), launch after launch; the first and last image are
